@@ -1,0 +1,204 @@
+"""`LLMEngine`: model folder in, generated tokens out.
+
+The surface is the reference's (pagedllm/engine.py:105-234): `LLMEngine(model,
+config=None, **overrides)`, `add_request`, `abort_request`, `step`, `generate`,
+`has_unfinished_requests`, `stats`; `RequestOutput`, `StepOutput` and
+`EngineStats` carry the same fields.  Prompts are lists of token ids, or text if
+the model folder has tokenizer files.
+"""
+
+from __future__ import annotations
+
+import logging
+import os
+import time
+from dataclasses import dataclass, field
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..cache.storage import CacheStorage
+from ..config.engine import EngineConfig
+from ..config.sampling import SamplingParams
+from ..sampling.sampler import Sampler
+from ..weights.loader import load_model, read_hf_config
+from .runner import ModelRunner
+from .scheduler import Scheduler
+from .sequence import Sequence
+
+log = logging.getLogger("paged_llm_b200")
+
+
+@dataclass
+class StepOutput:
+    seq_id: int
+    new_token: int | None
+    finished: bool
+
+
+@dataclass
+class RequestOutput:
+    seq_id: int
+    prompt_token_ids: list[int]
+    token_ids: list[int]            # generated tokens only
+    text: str
+    finish_reason: str              # "stop" | "length" | "abort"
+    num_cached_tokens: int
+    num_preemptions: int
+
+
+@dataclass
+class EngineStats:
+    num_steps: int = 0
+    num_prefill_tokens: int = 0
+    num_decode_tokens: int = 0
+    num_preemptions: int = 0
+    step_times: list[float] = field(default_factory=list)
+
+
+_FINISH = {"FINISHED_STOPPED": "stop", "FINISHED_LENGTH": "length", "FINISHED_ABORTED": "abort"}
+_TOKENIZER_FILES = ("tokenizer.json", "tokenizer.model", "tokenizer_config.json")
+
+
+def _load_tokenizer(path: str):
+    if not any(os.path.exists(os.path.join(path, f)) for f in _TOKENIZER_FILES):
+        return None
+    from transformers import AutoTokenizer       # tokenizer only, as in the reference (engine.py:112-114)
+    return AutoTokenizer.from_pretrained(path)
+
+
+def _eos_from_config(hf_config: dict):
+    eos = hf_config.get("eos_token_id")
+    if isinstance(eos, list):
+        eos = eos[0] if eos else None
+    return eos
+
+
+class LLMEngine:
+    def __init__(self, model: str, config: EngineConfig | None = None, ops=None, **overrides):
+        self.config = cfg = config or EngineConfig(**overrides)
+        self.device = torch.device(cfg.device)
+        if not os.path.isdir(model):
+            raise FileNotFoundError(f"{model!r} is not a model folder (config.json + *.safetensors); "
+                                    "downloading from a hub is not supported")
+        if ops is None:
+            from ..kernels.ops import CudaOps
+            ops = CudaOps(self.device)
+        self.ops = ops
+        self.tokenizer = _load_tokenizer(model)
+        hf_config = read_hf_config(model)
+        t0 = time.perf_counter()
+        self.model, self.model_config, self.dtype = load_model(model, cfg.dtype, self.device)
+        ops.set_compute_dtype(self.dtype)
+        self.model.prepare(cfg.max_model_len, self.device, ops)
+        log.info("loaded %s in %.1fs (dtype=%s)", model, time.perf_counter() - t0, self.dtype)
+
+        slots = self.model.cache_slots()
+        has_state = any(type(s.requirement).__name__ == "FixedState" for s in slots)
+        num_blocks = cfg.num_gpu_blocks or self._size_pool(slots)
+        self.kv_cache = CacheStorage(slots, num_blocks, cfg.block_size, self.dtype, self.device,
+                                     num_state_slots=cfg.max_num_seqs if has_state else 0)
+        self.block_manager = CacheManager(self.kv_cache.group_specs() or num_blocks, cfg.block_size,
+                                          cfg.enable_prefix_caching, num_state_slots=self.kv_cache.num_state_slots)
+        eos = self.tokenizer.eos_token_id if self.tokenizer is not None else _eos_from_config(hf_config)
+        self.scheduler = Scheduler(cfg, self.block_manager, eos)
+        self.sampler = Sampler(ops, cfg.seed)
+        self.runner = ModelRunner(self.model, self.kv_cache, self.block_manager, cfg, ops, self.sampler)
+        self.stats = EngineStats()
+        self._seqs: dict[int, Sequence] = {}
+        log.info("KV cache: %d blocks x %d tokens = %d tokens (%.2f GiB)", num_blocks, cfg.block_size,
+                 num_blocks * cfg.block_size, num_blocks * self.kv_cache.page_bytes() / 2 ** 30)
+
+    # ---- sizing -------------------------------------------------------------------
+    def _size_pool(self, slots) -> int:
+        """Pages that fit in `gpu_memory_utilization` of the device after the
+        weights and a reserve for one step's activations.  The reference measures
+        the activation peak with a dummy forward (engine.py:161-179); here it is
+        computed from the sizes: the widest buffers of a step of
+        `max_num_batched_tokens` tokens."""
+        cfg = self.config
+        page_bytes = CacheStorage.page_bytes_for(slots, cfg.block_size, self.dtype)
+        if self.device.type != "cuda" or page_bytes == 0:
+            return max(64, cfg.max_model_len * 4 // cfg.block_size)
+        free, total = torch.cuda.mem_get_info(self.device)
+        used_by_others = total - free - torch.cuda.memory_allocated(self.device)
+        widest = max(getattr(self.model_config, "intermediate_size", 0) * 3, self.model_config.hidden_size * 8)
+        activations = cfg.max_num_batched_tokens * widest * 4 * 2 + cfg.max_num_seqs * self.model_config.vocab_size * 4 * 3
+        budget = int(total * cfg.gpu_memory_utilization) - used_by_others - torch.cuda.memory_allocated(self.device) \
+            - activations
+        num_blocks = budget // page_bytes
+        # no request can use more than max_model_len tokens: more pages than every
+        # running request at full length would never be touched
+        num_blocks = min(num_blocks, cfg.max_num_seqs * (-(-cfg.max_model_len // cfg.block_size)) + 16)
+        if num_blocks < 16:
+            raise RuntimeError(f"not enough GPU memory for the KV cache ({num_blocks} blocks); lower "
+                               "max_num_batched_tokens or raise gpu_memory_utilization")
+        return int(num_blocks)
+
+    # ---- requests -----------------------------------------------------------------
+    def add_request(self, prompt: str | list[int], sampling_params: SamplingParams | None = None) -> int:
+        if isinstance(prompt, str):
+            if self.tokenizer is None:
+                raise ValueError("this model folder has no tokenizer files; pass prompts as lists of token ids")
+            ids = self.tokenizer.encode(prompt)
+        else:
+            ids = [int(t) for t in prompt]
+        vocab = self.model_config.vocab_size
+        bad = [t for t in ids if not 0 <= t < vocab]
+        if bad:
+            raise ValueError(f"token ids {bad[:5]} are outside the vocabulary of {vocab}")
+        seq = Sequence(ids, sampling_params or SamplingParams())
+        self.scheduler.add(seq)
+        self._seqs[seq.seq_id] = seq
+        return seq.seq_id
+
+    def abort_request(self, seq_id: int) -> None:
+        self.scheduler.abort(seq_id)
+
+    @property
+    def has_unfinished_requests(self) -> bool:
+        return self.scheduler.has_unfinished
+
+    def step(self) -> list[StepOutput]:
+        t0 = time.perf_counter()
+        out = self.scheduler.schedule()
+        if out.is_empty:
+            if self.scheduler.has_unfinished:
+                raise RuntimeError("no request can be scheduled although some are unfinished: the cache pool is "
+                                   "too small for the oldest waiting request")
+            return []
+        sampled = self.runner.run(out)
+        finished = {s.seq_id for s in self.scheduler.update(out, sampled)}
+        st = self.stats
+        st.num_steps += 1
+        st.num_prefill_tokens += out.num_prefill_tokens
+        st.num_decode_tokens += out.num_decode_tokens
+        st.num_preemptions += len(out.preempted)
+        st.step_times.append(time.perf_counter() - t0)
+        return [StepOutput(i.seq.seq_id, sampled.get(i.seq.seq_id), i.seq.seq_id in finished) for i in out.scheduled]
+
+    def _to_output(self, seq: Sequence) -> RequestOutput:
+        text = ""
+        if self.tokenizer is not None:
+            text = self.tokenizer.decode(seq.output_token_ids, skip_special_tokens=True)
+        return RequestOutput(seq.seq_id, seq.prompt_token_ids, seq.output_token_ids, text,
+                             _FINISH[seq.status.name], seq.num_cached_tokens, seq.num_preemptions)
+
+    def generate(self, prompts, sampling_params: SamplingParams | list[SamplingParams] | None = None,
+                 use_tqdm: bool = False) -> list[RequestOutput]:
+        if not isinstance(sampling_params, list):
+            sampling_params = [sampling_params or SamplingParams()] * len(prompts)
+        if len(sampling_params) != len(prompts):
+            raise ValueError("one SamplingParams per prompt, or one for all")
+        ids = [self.add_request(p, sp) for p, sp in zip(prompts, sampling_params)]
+        bar = None
+        if use_tqdm:
+            from tqdm import tqdm
+            bar = tqdm(total=len(ids), desc="requests")
+        while self.has_unfinished_requests:
+            for o in self.step():
+                if o.finished and bar is not None:
+                    bar.update(1)
+        if bar is not None:
+            bar.close()
+        return [self._to_output(self._seqs.pop(i)) for i in ids]

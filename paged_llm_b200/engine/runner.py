@@ -1,0 +1,281 @@
+"""The step function: a batch of (request, its next tokens) in, logits out.
+
+One step takes any list of (request, number of new tokens): portions of prompts
+beside single decoded tokens, cut anywhere.  It runs only those tokens, as one
+token-major batch with no padding, against what earlier steps left in the
+cache, and returns float32 logits at the places that were asked for
+(reference: `ModelRunner.build_inputs` / `run`, pagedllm/engine.py:51-102, which
+returns logits only for the last token of requests that sample).
+
+Metadata is gathered on the host into one pinned int32 buffer and reaches the
+device in a single copy.  Decode-only steps (every request brings one token) are
+replayed from CUDA graphs, one per batch-size bucket, unless `enforce_eager`.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager
+from ..cache.storage import CacheStorage
+from ..config.engine import EngineConfig
+from .context import AttentionPlan, HostBatch, StepContext
+from .sequence import Sequence
+
+
+@dataclass
+class StepItem:
+    seq: Sequence
+    num_new_tokens: int
+    want: tuple[int, ...] = ()      # places among this step's tokens whose logits are wanted
+
+
+def _align(n: int, a: int = 4) -> int:
+    return -(-n // a) * a
+
+
+class _Packer:
+    """Lays int32 sections out in one buffer, 16-byte aligned each."""
+
+    def __init__(self):
+        self.sections: list[tuple[str, int, np.ndarray]] = []
+        self.size = 0
+
+    def add(self, name: str, data: np.ndarray, capacity: int | None = None) -> None:
+        data = np.ascontiguousarray(data, dtype=np.int32).reshape(-1)
+        cap = max(int(capacity or 0), data.size, 1)
+        self.sections.append((name, self.size, data))
+        self.size += _align(cap)
+
+
+class ModelRunner:
+    GRAPH_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+
+    def __init__(self, model, storage: CacheStorage, cache_manager: CacheManager, config: EngineConfig, ops,
+                 sampler=None):
+        self.model, self.storage, self.cm, self.config, self.ops = model, storage, cache_manager, config, ops
+        self.sampler = sampler
+        self.device = storage.device
+        self.page_size = storage.page_size
+        self.plan_keys = sorted({k for k in (getattr(b.mixer, "attention_plan_key", lambda: None)()
+                                             for b in model.blocks) if k is not None},
+                                key=lambda k: tuple(v or 0 for v in k))
+        self._host_ring: list = []
+        self._ring_pos = 0
+        self._dev_meta = None
+        self._graphs: dict[int, object] = {}
+        self.use_graphs = (not config.enforce_eager) and self.device.type == "cuda" and getattr(ops, "supports_graphs", False)
+        self.num_graph_steps = 0
+        self.num_eager_steps = 0
+
+    # ------------------------------------------------------------------ metadata
+    def _gather(self, items: list[StepItem], pad_to: int | None = None, table_stride: int | None = None):
+        """Host side of a step: numpy sections and the HostBatch.  With `pad_to`
+        (graph replay) token and request counts are padded to the bucket."""
+        S = len(items)
+        q_lens = [it.num_new_tokens for it in items]
+        starts = [it.seq.num_computed_tokens for it in items]
+        T = sum(q_lens)
+        ids = np.empty(T, np.int32)
+        pos = np.empty(T, np.int32)
+        tseq = np.empty(T, np.int32)
+        want = []
+        o = 0
+        for s, it in enumerate(items):
+            n, st = q_lens[s], starts[s]
+            if n < 1:
+                raise ValueError("a step item needs at least one new token")
+            toks = it.seq.token_ids[st:st + n]
+            if len(toks) != n:
+                raise ValueError(f"request {it.seq.seq_id} has {len(it.seq.token_ids)} tokens, step asks for "
+                                 f"{st}..{st + n}")
+            ids[o:o + n] = toks
+            pos[o:o + n] = np.arange(st, st + n, dtype=np.int32)
+            tseq[o:o + n] = s
+            for w in it.want:
+                if not 0 <= w < n:
+                    raise ValueError(f"wanted place {w} is outside the {n} tokens of this step")
+                want.append(o + w)
+            o += n
+        S_pad = pad_to or S
+        T_pad = pad_to or T
+        host = HostBatch(q_lens, starts, [(-1 if it.seq.state_slot is None else it.seq.state_slot) for it in items],
+                         [it.seq.seq_id for it in items])
+        cu = np.zeros(S_pad + 1, np.int32)
+        cu[1:S + 1] = np.cumsum(q_lens)
+        cu[S + 1:] = T
+        klen = np.zeros(S_pad, np.int32)
+        klen[:S] = host.k_lens
+        slots = np.full(S_pad, -1, np.int32)
+        slots[:S] = host.state_slots
+        if T_pad > T:
+            ids = np.concatenate([ids, np.zeros(T_pad - T, np.int32)])
+            pos = np.concatenate([pos, np.zeros(T_pad - T, np.int32)])
+            tseq = np.concatenate([tseq, np.full(T_pad - T, -1, np.int32)])
+        pk = _Packer()
+        pk.add("ids", ids)
+        pk.add("pos", pos)
+        pk.add("tseq", tseq)
+        pk.add("cu", cu)
+        pk.add("klen", klen)
+        pk.add("slots", slots)
+        L_pad = pad_to or len(want)
+        lidx = np.zeros(max(L_pad, 1), np.int32)
+        lidx[:len(want)] = want
+        pk.add("lidx", lidx)
+        strides = []
+        for g in range(self.storage.num_groups):
+            tables = [it.seq.block_tables[g] if g < len(it.seq.block_tables) else [] for it in items]
+            stride = table_stride or _align(max([len(t) for t in tables] + [1]))
+            bt = np.zeros((S_pad, stride), np.int32)
+            for s, t in enumerate(tables):
+                if len(t) > stride:
+                    raise ValueError("block table longer than the captured stride")
+                bt[s, :len(t)] = t
+            strides.append(stride)
+            pk.add(f"bt{g}", bt)
+        plans = {}
+        for key in self.plan_keys:
+            plan = self.ops.plan_attention(q_lens, host.k_lens, *key, pad_requests=S_pad,
+                                           fixed_capacity=pad_to is not None)
+            plans[key] = plan
+            pk.add(f"small{key}", plan["small"])
+            pk.add(f"large{key}", plan["large"])
+            pk.add(f"splits{key}", plan["splits"])
+        return pk, host, dict(T=T_pad, S=S_pad, L=len(want), L_pad=L_pad, strides=strides, plans=plans,
+                              max_q=max(q_lens))
+
+    def _host_buffer(self, n: int):
+        """A pinned staging buffer that no copy in flight still reads."""
+        if not self._host_ring:
+            self._host_ring = [[None, None] for _ in range(4)]
+        slot = self._host_ring[self._ring_pos % len(self._host_ring)]
+        self._ring_pos += 1
+        if slot[1] is not None:
+            slot[1].synchronize()
+            slot[1] = None
+        if slot[0] is None or slot[0].numel() < n:
+            slot[0] = torch.empty(max(2 * n, 1 << 14), dtype=torch.int32, pin_memory=self.device.type == "cuda")
+        return slot[0], slot
+
+    def _upload(self, pk: _Packer, dev: torch.Tensor | None = None) -> torch.Tensor:
+        host, slot = self._host_buffer(pk.size)
+        hv = host.numpy()
+        for _, off, data in pk.sections:
+            hv[off:off + data.size] = data
+        if dev is None:
+            if self._dev_meta is None or self._dev_meta.numel() < pk.size:
+                self._dev_meta = torch.empty(max(pk.size * 2, 1 << 16), dtype=torch.int32, device=self.device)
+            dev = self._dev_meta
+        dev[:pk.size].copy_(host[:pk.size], non_blocking=True)
+        if self.device.type == "cuda":
+            ev = torch.cuda.Event()
+            ev.record()
+            slot[1] = ev
+        return dev
+
+    def _context(self, pk: _Packer, dev: torch.Tensor, host: HostBatch, info: dict) -> StepContext:
+        off = {name: (o, d.size) for name, o, d in pk.sections}
+
+        def view(name, n=None):
+            o, size = off[name]
+            return dev[o:o + (size if n is None else n)]
+
+        S, T = info["S"], info["T"]
+        tables = [view(f"bt{g}").view(S, info["strides"][g]) for g in range(self.storage.num_groups)]
+        plans = {}
+        for key, p in info["plans"].items():
+            ns = len(p["small"]) // 4
+            nl = len(p["large"]) // 4
+            plans[key] = AttentionPlan(
+                small=view(f"small{key}", ns * 4).view(ns, 4) if ns else None,
+                large=view(f"large{key}", nl * 4).view(nl, 4) if nl else None,
+                splits=view(f"splits{key}"), n_small=ns, n_large=nl, max_splits=p["max_splits"])
+        return StepContext(
+            ops=self.ops, num_tokens=T, num_seqs=S, num_logits=info["L_pad"],
+            input_ids=view("ids"), positions=view("pos"), token_seq=view("tseq"), cu_seqlens_q=view("cu"),
+            seq_lens_k=view("klen"), state_slots=view("slots"), logits_indices=view("lidx", max(info["L_pad"], 1)),
+            block_tables=tables, layer_caches=self.storage.layer_caches, page_size=self.page_size,
+            max_q_len=info["max_q"], host=host, attention_plans=plans)
+
+    # ------------------------------------------------------------------ the step
+    @torch.no_grad()
+    def step(self, items: list[StepItem]) -> torch.Tensor | None:
+        """Runs the items' tokens as one batch.  Returns float32 logits
+        [wanted places, vocab] in the order of the items and of their `want`, or
+        None if nothing is wanted.  The caller has made the block tables cover
+        the new tokens (`CacheManager.allocate_slots`) and advances the
+        watermarks afterwards."""
+        if not items:
+            return None
+        self.storage.apply_copies(self.cm.take_pending_copies(), self.ops)
+        for it in items:
+            if it.seq.state_slot is not None and it.seq.num_computed_tokens == 0:
+                self.storage.zero_state(it.seq.state_slot)
+        if self._graph_eligible(items):
+            return self._graph_step(items)
+        pk, host, info = self._gather(items)
+        dev = self._upload(pk)
+        ctx = self._context(pk, dev, host, info)
+        self.num_eager_steps += 1
+        return self.model.forward(ctx)
+
+    # ------------------------------------------------------------------ CUDA graphs for decode
+    def _graph_eligible(self, items: list[StepItem]) -> bool:
+        if not self.use_graphs or len(items) > self.GRAPH_BUCKETS[-1]:
+            return False
+        if self.cm.num_state_slots:
+            return False
+        return all(it.num_new_tokens == 1 and it.want == (0,) for it in items)
+
+    def _table_stride(self) -> int:
+        return _align(-(-self.config.max_model_len // self.page_size))
+
+    def _graph_step(self, items: list[StepItem]) -> torch.Tensor:
+        B = next(b for b in self.GRAPH_BUCKETS if b >= len(items))
+        pk, host, info = self._gather(items, pad_to=B, table_stride=self._table_stride())
+        entry = self._graphs.get(B)
+        if entry is None:
+            entry = self._capture(B, pk, host, info)
+        dev, graph, logits, size = entry
+        if pk.size != size:
+            raise RuntimeError("metadata layout changed between capture and replay")
+        self._upload(pk, dev)
+        graph.replay()
+        self.num_graph_steps += 1
+        return logits[:len(items)]
+
+    def _capture(self, B: int, pk: _Packer, host: HostBatch, info: dict):
+        dev = torch.empty(pk.size, dtype=torch.int32, device=self.device)
+        self._upload(pk, dev)
+        ctx = self._context(pk, dev, host, info)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):                       # warm-up: library workspaces, lazy module loads
+                self.model.forward(ctx)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = self.model.forward(ctx)
+        entry = (dev, graph, logits, pk.size)
+        self._graphs[B] = entry
+        return entry
+
+    # ------------------------------------------------------------------ scheduler-facing
+    @torch.no_grad()
+    def run(self, out) -> dict[int, int]:
+        """One scheduled step: runs it and samples where a request reached its
+        last known token (reference: pagedllm/engine.py:93-102)."""
+        items = [StepItem(s.seq, s.num_new_tokens, (s.num_new_tokens - 1,) if s.needs_sampling else ())
+                 for s in out.scheduled]
+        logits = self.step(items)
+        if logits is None:
+            return {}
+        sampled = [s.seq for s in out.scheduled if s.needs_sampling]
+        tokens = self.sampler.sample(logits, sampled)
+        return {seq.seq_id: int(tok) for seq, tok in zip(sampled, tokens)}

@@ -1,0 +1,205 @@
+"""Continuous batching with a token budget, chunked prefill and preemption by
+recompute.  The rules are the reference's (pagedllm/scheduler.py:53-187):
+
+* every step has `max_num_batched_tokens` tokens to give out; a decoding request
+  takes one, a request still in its prompt takes what is left of the prompt or
+  of the budget (prompts are cut purely by the budget, not at page edges);
+* running requests are served first, in admission order; if pages run out, the
+  most recently admitted running request is preempted (its pages are freed, its
+  generated tokens are kept, it goes to the FRONT of the waiting queue and is
+  later recomputed as a longer prompt) until the allocation succeeds or the
+  request itself was the victim;
+* then waiting requests are admitted strictly first-in first-out while budget,
+  `max_num_seqs` and pages allow; admission stops at the first that does not fit;
+* a request samples in the step that computes its last known token.
+
+Decided here, where the reference leaves a trap: a request that could never
+fit the pool (more pages than exist), or never fit a step with chunking off, is
+refused by `add` with an error instead of spinning forever; `max_tokens` is
+clamped on the request, never on the caller's `SamplingParams` object.
+"""
+
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+
+from ..cache.manager import CacheManager
+from ..config.engine import EngineConfig
+from .sequence import Sequence, SequenceStatus
+
+
+@dataclass
+class ScheduledSequence:
+    seq: Sequence
+    num_new_tokens: int
+    needs_sampling: bool = field(init=False)    # fixed when scheduled
+
+    def __post_init__(self) -> None:
+        self.needs_sampling = self.seq.num_computed_tokens + self.num_new_tokens == self.seq.num_tokens
+
+
+@dataclass
+class SchedulerOutput:
+    scheduled: list[ScheduledSequence] = field(default_factory=list)
+    preempted: list[Sequence] = field(default_factory=list)
+    num_prefill_tokens: int = 0
+    num_decode_tokens: int = 0
+
+    @property
+    def is_empty(self) -> bool:
+        return not self.scheduled
+
+    @property
+    def total_tokens(self) -> int:
+        return self.num_prefill_tokens + self.num_decode_tokens
+
+
+class Scheduler:
+    def __init__(self, config: EngineConfig, block_manager: CacheManager, eos_token_id: int | None):
+        self.config = config
+        self.bm = block_manager
+        self.eos_token_id = eos_token_id
+        self.waiting: deque[Sequence] = deque()
+        self.running: list[Sequence] = []
+        self.finished: list[Sequence] = []
+        self.num_preemptions = 0
+
+    # ---- queues ------------------------------------------------------------------
+    def add(self, seq: Sequence) -> None:
+        cfg = self.config
+        n = seq.num_prompt_tokens
+        if n >= cfg.max_model_len:
+            raise ValueError(f"prompt has {n} tokens, max_model_len={cfg.max_model_len}")
+        if not cfg.enable_chunked_prefill and n > cfg.max_num_batched_tokens:
+            raise ValueError("prompt longer than max_num_batched_tokens; enable chunked prefill")
+        seq.max_tokens = seq.sampling_params.max_tokens
+        if n + seq.max_tokens > cfg.max_model_len:
+            seq.max_tokens = max(1, cfg.max_model_len - n)
+        # The longest this request can get must fit the pool on its own, else it
+        # would preempt itself for ever.
+        longest = n + seq.max_tokens
+        if not cfg.enable_chunked_prefill:
+            # a preempted request comes back as prompt + generated tokens in one portion
+            longest_portion = longest - 1
+            if longest_portion > cfg.max_num_batched_tokens:
+                seq.max_tokens = max(1, cfg.max_num_batched_tokens - n + 1)
+                longest = n + seq.max_tokens
+        capacity = self.bm.max_tokens_per_request()
+        if longest - 1 > capacity:
+            if n > capacity:
+                raise ValueError(f"prompt of {n} tokens can never fit the cache pool of {capacity} tokens")
+            seq.max_tokens = max(1, capacity - n + 1)
+        seq.status = SequenceStatus.WAITING
+        self.waiting.append(seq)
+
+    def abort(self, seq_id: int) -> None:
+        for queue in (self.waiting, self.running):
+            for seq in list(queue):
+                if seq.seq_id == seq_id:
+                    queue.remove(seq)
+                    self.bm.free(seq)
+                    seq.status = SequenceStatus.FINISHED_ABORTED
+                    self.finished.append(seq)
+                    return
+
+    @property
+    def has_unfinished(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    @property
+    def num_unfinished(self) -> int:
+        return len(self.waiting) + len(self.running)
+
+    # ---- one step's decisions ----------------------------------------------------
+    def _preempt(self, seq: Sequence, out: SchedulerOutput) -> None:
+        self.running.remove(seq)
+        self.bm.free(seq)
+        seq.reset_for_recompute()
+        self.waiting.appendleft(seq)
+        out.preempted.append(seq)
+        self.num_preemptions += 1
+
+    def schedule(self) -> SchedulerOutput:
+        out = SchedulerOutput()
+        budget = self.config.max_num_batched_tokens
+        chunked = self.config.enable_chunked_prefill
+
+        # running requests first, in admission order
+        for seq in list(self.running):
+            if budget == 0:
+                break
+            if seq.status is not SequenceStatus.RUNNING:
+                continue                              # preempted earlier in this loop
+            want = seq.num_uncomputed_tokens
+            assert want >= 1
+            if want > budget:
+                if not chunked:
+                    continue
+                want = budget
+            while self.bm.allocate_slots(seq, want) is None:
+                victim = self.running[-1]
+                self._preempt(victim, out)
+                if victim is seq:
+                    break
+            if seq.status is not SequenceStatus.RUNNING:
+                continue
+            budget -= want
+            decoding = seq.is_prefill_done
+            out.scheduled.append(ScheduledSequence(seq, want))
+            if decoding:
+                out.num_decode_tokens += want
+            else:
+                out.num_prefill_tokens += want
+
+        # then admit from the waiting queue, strictly in order
+        while self.waiting and budget > 0 and len(self.running) < self.config.max_num_seqs:
+            seq = self.waiting[0]
+            hits, num_cached = self.bm.get_computed_blocks(seq)
+            want = seq.num_tokens - num_cached
+            assert want >= 1
+            if want > budget:
+                if not chunked:
+                    break
+                want = budget
+            if not self.bm.acquire_state_slot(seq):
+                break
+            if self.bm.allocate_slots(seq, want, hits) is None:
+                self.bm.release_state_slot(seq)
+                break                                  # pool full: keep the order, try next step
+            self.waiting.popleft()
+            seq.num_computed_tokens = num_cached
+            seq.num_cached_tokens = num_cached
+            seq.status = SequenceStatus.RUNNING
+            self.running.append(seq)
+            budget -= want
+            out.scheduled.append(ScheduledSequence(seq, want))
+            out.num_prefill_tokens += want
+        return out
+
+    # ---- after the step ----------------------------------------------------------
+    def update(self, out: SchedulerOutput, sampled: dict[int, int]) -> list[Sequence]:
+        """Advance watermarks, register full pages, append sampled tokens, retire
+        what finished (scheduler.py:161-187).  Returns the requests that finished."""
+        done: list[Sequence] = []
+        for item in out.scheduled:
+            seq = item.seq
+            before = seq.num_computed_tokens
+            seq.num_computed_tokens = before + item.num_new_tokens
+            self.bm.cache_full_blocks(seq, before, seq.num_computed_tokens)
+            self.bm.release_behind_window(seq)
+            if not item.needs_sampling:
+                continue
+            token = sampled[seq.seq_id]
+            seq.append_token(token)
+            sp = seq.sampling_params
+            if (not sp.ignore_eos and token == self.eos_token_id) or token in sp.stop_token_ids:
+                seq.status = SequenceStatus.FINISHED_STOPPED
+            elif seq.num_generated_tokens >= seq.max_tokens or seq.num_tokens >= self.config.max_model_len:
+                seq.status = SequenceStatus.FINISHED_LENGTH
+            if seq.is_finished:
+                self.running.remove(seq)
+                self.bm.free(seq)
+                done.append(seq)
+        self.finished.extend(done)
+        return done

@@ -1,0 +1,75 @@
+"""Work lists for the attention kernels, made on the host once per step.
+
+A request with nq new tokens and G query heads per kv head has nq*G query rows
+per kv head (row r = token r // G, head r % G).  Requests with at most
+`small_rows` rows (decoding, or a portion of a very few tokens) go to the
+split-context kernel: their keys are cut into `splits` ranges that run in
+separate thread blocks and are merged afterwards, so that a few long requests
+still fill the machine (the reference runs one program per query tile and never
+splits the context: pagedllm/attention/triton_kernel.py:10-12, :120).  The
+others are cut into tiles of `large_rows` rows.
+
+An item is four int32: (request, tile or scratch base, split, splits).  For a
+fixed request count and fixed lengths the plan is deterministic, so replaying a
+step reproduces its logits bit for bit.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+
+
+def wanted_splits(num_small: int, num_kv_heads: int, num_sms: int, max_splits: int) -> int:
+    """Splits per request so that requests x kv heads x splits is about two
+    thread blocks per SM."""
+    if num_small <= 0:
+        return 1
+    target_items = -(-2 * num_sms // max(num_kv_heads, 1))
+    return int(min(max_splits, max(1, -(-target_items // num_small))))
+
+
+def plan_attention(q_lens, k_lens, group_size: int, num_kv_heads: int, window: int | None, *, small_rows: int,
+                   large_rows: int, min_split_keys: int, num_sms: int, max_splits: int = 32,
+                   pad_requests: int | None = None, fixed_capacity: bool = False) -> dict:
+    S = len(q_lens)
+    S_pad = pad_requests or S
+    small_ids = [s for s in range(S) if q_lens[s] * group_size <= small_rows]
+    n_small = S_pad if fixed_capacity else len(small_ids)
+    want = wanted_splits(n_small, num_kv_heads, num_sms, max_splits)
+    splits = np.ones((S_pad, 2), np.int32)
+    splits[:, 1] = 0
+    small = []
+    scratch_base = 0
+    for s in small_ids:
+        nq, lk = q_lens[s], k_lens[s]
+        first_pos = lk - nq
+        lo = max(0, first_pos - window + 1) if window else 0
+        n_keys = lk - lo
+        ns = max(1, min(want, -(-n_keys // min_split_keys)))
+        splits[s] = (ns, scratch_base)
+        for j in range(ns):
+            small.append((s, scratch_base, j, ns))
+        scratch_base += nq
+    large = []
+    for s in range(S):
+        rows = q_lens[s] * group_size
+        if rows <= small_rows:
+            continue
+        tiles = -(-rows // large_rows)
+        for t in range(tiles):
+            last_tok = min(rows - 1, (t + 1) * large_rows - 1) // group_size
+            large.append((k_lens[s] - q_lens[s] + last_tok, s, t))
+    large.sort(key=lambda x: -x[0])                       # longest first
+    small_arr = np.array(small, np.int32).reshape(-1, 4)
+    if fixed_capacity:
+        cap = S_pad * want
+        pad = np.full((cap - len(small_arr), 4), -1, np.int32)
+        small_arr = np.concatenate([small_arr, pad]) if len(pad) else small_arr
+    large_arr = np.array([(s, t, 0, 1) for _, s, t in large], np.int32).reshape(-1, 4)
+    return {
+        "small": small_arr.reshape(-1),
+        "large": large_arr.reshape(-1),
+        "splits": splits.reshape(-1),
+        "max_splits": int(want),
+        "num_small_tokens": int(scratch_base) if not fixed_capacity else int(S_pad),
+    }
