@@ -1,0 +1,306 @@
+// Paged attention in bfloat16 on the tensor cores (mma.sync m16n8k16, float32
+// accumulation), one instantiation per padded head size PL_DPAD.
+//
+// A thread block takes one item of the work list for one kv head: a tile of
+// query rows (row = token * G + head within the group, so the G query heads that
+// share a kv head sit in the same tile and read each key once) and a range of
+// keys.  Keys and values are fetched page by page through the block table with
+// cp.async into double-buffered shared memory, zero-filled outside the range, so
+// stale or poisoned pages never reach a product.  Scores, running maximum, sum
+// and the output accumulator are float32; probabilities are rounded to bfloat16
+// for the second product, as the reference's kernel does
+// (xiyiji/paged-llm pagedllm/attention/triton_kernel.py:76-89).
+//
+// Two shapes: "large" (4 warps x 16 rows, 64 keys per iteration) for prefill
+// portions, and "small" (16 rows, 4 warps that each take other keys and are
+// merged at the end) for decoding, where a split range per block keeps the
+// machine busy on few requests.
+#pragma once
+
+#include "attention_common.cuh"
+
+namespace {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm volatile("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int DPAD, int MW, int NW, int KPW>
+struct AttnShape {
+    static constexpr int BM = 16 * MW, BN = KPW * NW, PITCH = DPAD + 8, THREADS = 32 * MW * NW;
+    static constexpr int SMEM_BYTES = (BM + 4 * BN) * PITCH * 2;
+};
+
+template <int DPAD, int MW, int NW, int KPW>
+__global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
+    using Shape = AttnShape<DPAD, MW, NW, KPW>;
+    constexpr int BM = Shape::BM, BN = Shape::BN, PITCH = Shape::PITCH, THREADS = Shape::THREADS;
+    constexpr int CH = DPAD / 8;                          // 16-byte chunks per row
+    constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
+    const AttnItem it = attn_decode_item(p, blockIdx.x, BM, BN);
+    if (!it.valid) return;
+
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+    __nv_bfloat16* Ks = Qs + BM * PITCH;                   // [2][BN][PITCH]
+    __nv_bfloat16* Vs = Ks + 2 * BN * PITCH;               // [2][BN][PITCH]
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wm = warp % MW, wn = warp / MW;
+    const int d = p.d, kvh = blockIdx.y, G = p.nh / p.nkv;
+    const __nv_bfloat16* q = (const __nv_bfloat16*)p.q;
+    const __nv_bfloat16* kv = (const __nv_bfloat16*)p.kv;
+    const int* bt = p.block_table + (size_t)it.seq * p.bt_stride;
+    const size_t v_off = (size_t)p.nkv * p.ps * d;
+
+    for (int e = tid; e < BM * CH; e += THREADS) {
+        const int r = e / CH, c8 = e - r * CH;
+        const int R = it.row_base + r;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (R < it.rows_total && c8 * 8 < d)
+            v = *reinterpret_cast<const uint4*>(q + (size_t)(it.q0 + R / G) * p.q_stride + (kvh * G + R % G) * d + c8 * 8);
+        *reinterpret_cast<uint4*>(Qs + r * PITCH + c8 * 8) = v;
+    }
+
+    auto load_tile = [&](int stage, int kt) {
+        __nv_bfloat16* kd = Ks + stage * BN * PITCH;
+        __nv_bfloat16* vd = Vs + stage * BN * PITCH;
+        for (int e = tid; e < BN * CH; e += THREADS) {
+            const int j = e / CH, c8 = e - j * CH;
+            const int n = kt + j;
+            bool ok = n < it.key_hi && c8 * 8 < d;
+            int page = ok ? bt[n / p.ps] : -1;
+            ok = ok && page >= 0;
+            const __nv_bfloat16* src =
+                ok ? kv + ((((size_t)page * 2) * p.nkv + kvh) * p.ps + n % p.ps) * d + c8 * 8 : kv;
+            cp_async16(kd + j * PITCH + c8 * 8, src, ok ? 16 : 0);
+            cp_async16(vd + j * PITCH + c8 * 8, ok ? src + v_off : kv, ok ? 16 : 0);
+        }
+        cp_async_commit();
+    };
+
+    const int g = lane >> 2, t4 = lane & 3;
+    int pos[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int R = it.row_base + wm * 16 + g + 8 * h;
+        pos[h] = R < it.rows_total ? it.lk - it.nq + R / G : -1;
+    }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float oacc[DPAD / 8][4];
+#pragma unroll
+    for (int j = 0; j < DPAD / 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) oacc[j][e] = 0.f;
+    const float scale_log2 = p.scale * LOG2E;
+
+    const int n_tiles = (it.key_hi - it.key_lo + BN - 1) / BN;
+    if (n_tiles > 0) load_tile(0, it.key_lo);
+    for (int t = 0; t < n_tiles; ++t) {
+        if (t + 1 < n_tiles) {
+            load_tile((t + 1) & 1, it.key_lo + (t + 1) * BN);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const __nv_bfloat16* kst = Ks + (t & 1) * BN * PITCH + wn * KPW * PITCH;
+        const __nv_bfloat16* vst = Vs + (t & 1) * BN * PITCH + wn * KPW * PITCH;
+        const int kbase = it.key_lo + t * BN + wn * KPW;
+        if (kbase < it.key_hi) {                               // uniform per warp
+            float sacc[KPW / 8][4];
+#pragma unroll
+            for (int j = 0; j < KPW / 8; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) sacc[j][e] = 0.f;
+#pragma unroll
+            for (int kk = 0; kk < DPAD / 16; ++kk) {
+                uint32_t a[4];
+                ldmatrix_x4(a, Qs + (wm * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * PITCH + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+                for (int n2 = 0; n2 < KPW / 16; ++n2) {
+                    uint32_t b[4];
+                    ldmatrix_x4(b, kst + (n2 * 16 + (lane & 7) + (lane >> 4) * 8) * PITCH + kk * 16 + ((lane >> 3) & 1) * 8);
+                    mma_bf16(sacc[2 * n2], a, b[0], b[1]);
+                    mma_bf16(sacc[2 * n2 + 1], a, b[2], b[3]);
+                }
+            }
+            // scale, mask, running maximum
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < KPW / 8; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int n = kbase + 8 * j + 2 * t4 + (e & 1);
+                    const int pr = pos[e >> 1];
+                    const bool vis = n < it.key_hi && n <= pr && (p.window <= 0 || n > pr - p.window);
+                    const float s = vis ? sacc[j][e] * scale_log2 : -INFINITY;
+                    sacc[j][e] = s;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], s);
+                }
+            float alpha[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+                const float m_new = fmaxf(m_run[h], mx[h]);
+                alpha[h] = m_run[h] == -INFINITY ? 0.f : fast_exp2(m_run[h] - m_new);
+                m_run[h] = m_new;
+                l_run[h] *= alpha[h];
+            }
+            uint32_t pa[KPW / 16][4];
+#pragma unroll
+            for (int j = 0; j < KPW / 8; ++j) {
+                float pv[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float s = sacc[j][e];
+                    pv[e] = s == -INFINITY ? 0.f : fast_exp2(s - m_run[e >> 1]);
+                    l_run[e >> 1] += pv[e];
+                }
+                pa[j >> 1][(j & 1) * 2 + 0] = pack_bf16(pv[0], pv[1]);
+                pa[j >> 1][(j & 1) * 2 + 1] = pack_bf16(pv[2], pv[3]);
+            }
+#pragma unroll
+            for (int j = 0; j < DPAD / 8; ++j) {
+                oacc[j][0] *= alpha[0];
+                oacc[j][1] *= alpha[0];
+                oacc[j][2] *= alpha[1];
+                oacc[j][3] *= alpha[1];
+            }
+#pragma unroll
+            for (int k2 = 0; k2 < KPW / 16; ++k2) {
+#pragma unroll
+                for (int d2 = 0; d2 < DPAD / 16; ++d2) {
+                    uint32_t b[4];
+                    ldmatrix_x4_trans(b, vst + (k2 * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * PITCH + d2 * 16 + (lane >> 4) * 8);
+                    mma_bf16(oacc[2 * d2], pa[k2], b[0], b[1]);
+                    mma_bf16(oacc[2 * d2 + 1], pa[k2], b[2], b[3]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+
+    // merge the warps that took different keys, then write
+    __syncthreads();          // the Q region is reused below, also when no key tile ran
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+    }
+    float* red_ml = reinterpret_cast<float*>(smem_raw);                     // [NW][BM][2] in the Q region
+    float* red_o = reinterpret_cast<float*>(smem_raw + BM * PITCH * 2);     // [NW][BM][DPAD] in the K/V region
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = wm * 16 + g + 8 * h;
+        if (t4 == 0) {
+            red_ml[(wn * BM + r) * 2 + 0] = m_run[h];
+            red_ml[(wn * BM + r) * 2 + 1] = l_run[h];
+        }
+#pragma unroll
+        for (int j = 0; j < DPAD / 8; ++j) {
+            float2 v = make_float2(oacc[j][2 * h], oacc[j][2 * h + 1]);
+            *reinterpret_cast<float2*>(red_o + ((size_t)(wn * BM + r)) * DPAD + 8 * j + 2 * t4) = v;
+        }
+    }
+    __syncthreads();
+    for (int e = tid; e < BM * (DPAD / 2); e += THREADS) {
+        const int r = e / (DPAD / 2), c = (e - r * (DPAD / 2)) * 2;
+        const int R = it.row_base + r;
+        if (R >= it.rows_total || c >= d) continue;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) M = fmaxf(M, red_ml[(w * BM + r) * 2]);
+        float L = 0.f, o0 = 0.f, o1 = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+            const float mw = red_ml[(w * BM + r) * 2];
+            if (mw == -INFINITY) continue;
+            const float f = NW == 1 ? 1.f : fast_exp2(mw - M);
+            L += red_ml[(w * BM + r) * 2 + 1] * f;
+            const float2 v = *reinterpret_cast<const float2*>(red_o + ((size_t)(w * BM + r)) * DPAD + c);
+            o0 += v.x * f;
+            o1 += v.y * f;
+        }
+        const int tok = R / G, head = kvh * G + R % G;
+        if (it.splits <= 1) {
+            const float inv = L > 0.f ? 1.0f / L : 0.f;
+            __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)(it.q0 + tok) * p.out_stride + head * d + c;
+            *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(o0 * inv, o1 * inv);
+        } else {
+            float* part = attn_partial(p, it.scratch_base + tok, head, it.split);
+            if (c == 0) {
+                part[0] = M == -INFINITY ? -INFINITY : M * LN2;
+                part[1] = L;
+            }
+            part[2 + c] = o0;
+            part[3 + c] = o1;
+        }
+    }
+}
+
+template <int DPAD, int MW, int NW, int KPW>
+int launch_attn_bf16(const AttnParams& p, cudaStream_t stream) {
+    using Shape = AttnShape<DPAD, MW, NW, KPW>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        PL_CUDA(cudaFuncSetAttribute(attn_bf16_kernel<DPAD, MW, NW, KPW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     Shape::SMEM_BYTES));
+        attr_set = true;
+    }
+    attn_bf16_kernel<DPAD, MW, NW, KPW><<<dim3(p.n_work, p.nkv), Shape::THREADS, Shape::SMEM_BYTES, stream>>>(p);
+    PL_LAUNCHED("attention_bf16");
+    return 0;
+}
+
+}  // namespace
+
+#define PL_CAT_(a, b) a##b
+#define PL_CAT(a, b) PL_CAT_(a, b)
+
+// Tile rows of the two shapes, so that the host plans with the same numbers.
+PL_EXPORT int PL_CAT(pl_attention_bf16_rows_d, PL_DPAD)(int small) { return small ? 16 : 64; }
+
+PL_EXPORT int PL_CAT(pl_attention_bf16_d, PL_DPAD)(const AttnParams* params, cudaStream_t stream) {
+    AttnParams p = *params;
+    if (p.n_work == 0) return 0;
+    PL_REQUIRE(p.nh > 0 && p.nkv > 0 && p.nh % p.nkv == 0, "attention_bf16: %d query heads on %d kv heads", p.nh, p.nkv);
+    PL_REQUIRE(p.d % 16 == 0 && p.d > 0 && p.d <= PL_DPAD, "attention_bf16: head_dim=%d does not fit this build (%d)",
+               p.d, PL_DPAD);
+    PL_REQUIRE(p.q_stride % 8 == 0 && p.out_stride % 2 == 0, "attention_bf16: row strides must keep 16-byte alignment");
+    PL_REQUIRE(((uintptr_t)p.q & 15) == 0 && ((uintptr_t)p.kv & 15) == 0, "attention_bf16: q and kv must be 16-byte aligned");
+    constexpr int KPW_SMALL = PL_DPAD <= 64 ? 64 : (PL_DPAD == 128 ? 32 : 16);
+    if (p.is_small) return launch_attn_bf16<PL_DPAD, 1, 4, KPW_SMALL>(p, stream);
+    return launch_attn_bf16<PL_DPAD, 4, 1, 64>(p, stream);
+}

@@ -1,0 +1,62 @@
+// What the attention kernels of both precisions share: how an item of the work
+// list becomes query rows and a key range, and the layout of split partials.
+//
+// Semantics (xiyiji/paged-llm pagedllm/attention/reference.py:23-55 and
+// triton_kernel.py:22-93): request s has nq new query tokens and a context of Lk
+// keys that includes them; query token i sits at position Lk - nq + i and sees
+// keys 0..position (with a window w: the last w of them); query head h reads kv
+// head h / (heads / kv_heads); keys and values are read through the block table.
+#pragma once
+
+#include "common.cuh"
+
+struct AttnItem {
+    int seq, nq, lk, q0;     // request, its new tokens, its context length, its first row in the batch
+    int row_base;            // first packed row (token * G + head in group) of this tile
+    int rows_total;          // nq * G
+    int key_lo, key_hi;      // keys [key_lo, key_hi) are this item's share
+    int split, splits;
+    int scratch_base;        // first scratch row of the request (split items)
+    bool valid;
+};
+
+__device__ __forceinline__ AttnItem attn_decode_item(const AttnParams& p, int idx, int block_rows, int key_align) {
+    AttnItem it;
+    it.valid = false;
+    if (idx >= p.n_work) return it;
+    const int4 w = p.work[idx];
+    if (w.x < 0) return it;
+    const int G = p.nh / p.nkv;
+    it.seq = w.x;
+    it.q0 = p.cu_q[w.x];
+    it.nq = p.cu_q[w.x + 1] - it.q0;
+    it.lk = p.k_lens[w.x];
+    it.rows_total = it.nq * G;
+    it.row_base = p.is_small ? 0 : w.y * block_rows;
+    it.scratch_base = p.is_small ? w.y : 0;
+    it.split = w.z;
+    it.splits = w.w;
+    if (it.nq <= 0 || it.row_base >= it.rows_total) return it;
+    const int last_row = min(it.rows_total, it.row_base + block_rows) - 1;
+    const int pos_first = it.lk - it.nq + it.row_base / G;
+    const int pos_last = it.lk - it.nq + last_row / G;
+    int lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    int hi = pos_last + 1;
+    if (it.splits > 1) {
+        int chunk = (hi - lo + it.splits - 1) / it.splits;
+        chunk = (chunk + key_align - 1) / key_align * key_align;
+        lo = lo + it.split * chunk;
+        hi = min(hi, lo + chunk);
+    }
+    it.key_lo = lo;
+    it.key_hi = max(hi, lo);
+    it.valid = true;
+    return it;
+}
+
+// Partial result of (scratch row, head, split): [m, l, acc[0..d)] with m the
+// running maximum of the scaled scores (natural-log units) and acc, l not yet
+// divided.
+__device__ __forceinline__ float* attn_partial(const AttnParams& p, int scratch_row, int head, int split) {
+    return p.scratch + (((size_t)scratch_row * p.nh + head) * p.max_splits + split) * (size_t)(p.d + 2);
+}

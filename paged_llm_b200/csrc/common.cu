@@ -1,0 +1,18 @@
+// Error reporting of the kernel library; compiled into every module.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "common.cuh"
+
+static thread_local char g_error[512] = "";
+
+int pl_fail(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return 1;
+}
+
+PL_EXPORT const char* pl_last_error() { return g_error; }
+PL_EXPORT int pl_abi_version() { return 1; }

@@ -1,0 +1,86 @@
+// Shared declarations of the kernel library: dtype codes, error reporting,
+// conversions.  Every exported function is extern "C", takes raw device
+// pointers, sizes and a CUDA stream, allocates nothing, and returns 0 or a
+// non-zero code after storing a message that pl_last_error() returns.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define PL_EXPORT extern "C" __attribute__((visibility("default")))
+
+enum PlDtype { PL_F32 = 0, PL_BF16 = 1 };
+
+int pl_fail(const char* fmt, ...);
+
+#define PL_REQUIRE(cond, ...)                 \
+    do {                                      \
+        if (!(cond)) return pl_fail(__VA_ARGS__); \
+    } while (0)
+
+#define PL_LAUNCHED(name)                                                        \
+    do {                                                                         \
+        cudaError_t e__ = cudaGetLastError();                                    \
+        if (e__ != cudaSuccess) return pl_fail("%s: %s", name, cudaGetErrorString(e__)); \
+    } while (0)
+
+#define PL_CUDA(expr)                                                            \
+    do {                                                                         \
+        cudaError_t e__ = (expr);                                                \
+        if (e__ != cudaSuccess) return pl_fail("%s: %s", #expr, cudaGetErrorString(e__)); \
+    } while (0)
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide sum for up to 1024 threads; `red` holds 32 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_sum(v);
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    const int nw = (blockDim.x + 31) >> 5;
+    float t = (threadIdx.x < nw) ? red[threadIdx.x] : 0.f;
+    if (warp == 0) {
+        t = warp_sum(t);
+        if (lane == 0) red[0] = t;
+    }
+    __syncthreads();
+    t = red[0];
+    __syncthreads();
+    return t;
+}
+
+// Parameters of the paged attention kernels (both precisions).
+struct AttnParams {
+    const void* q;          // [T, q_stride] rows; head h of token t at t*q_stride + h*d
+    const void* kv;         // one layer of a pool: [pages, 2, kv_heads, page_size, d]
+    void* out;              // [T, out_stride]
+    const int* block_table; // [S, bt_stride]
+    const int* cu_q;        // [S+1]
+    const int* k_lens;      // [S]
+    const int4* work;       // items (request, tile | scratch base, split, splits); request < 0: none
+    float* scratch;         // partial results of split items
+    long long scratch_floats;
+    int q_stride, out_stride, bt_stride;
+    int n_work, max_splits;
+    int nh, nkv, d, ps;
+    int window;             // 0: none
+    int is_small;           // items are (request, scratch base, split, splits), one tile per request
+    float scale;
+};

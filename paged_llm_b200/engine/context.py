@@ -50,6 +50,7 @@ class AttentionPlan:
     n_small: int
     n_large: int
     max_splits: int
+    small_tokens: int = 0            # tokens of the requests in `small` (scratch rows)
 
 
 @dataclass

@@ -193,7 +193,8 @@ class ModelRunner:
             plans[key] = AttentionPlan(
                 small=view(f"small{key}", ns * 4).view(ns, 4) if ns else None,
                 large=view(f"large{key}", nl * 4).view(nl, 4) if nl else None,
-                splits=view(f"splits{key}"), n_small=ns, n_large=nl, max_splits=p["max_splits"])
+                splits=view(f"splits{key}"), n_small=ns, n_large=nl, max_splits=p["max_splits"],
+                small_tokens=p["num_small_tokens"])
         return StepContext(
             ops=self.ops, num_tokens=T, num_seqs=S, num_logits=info["L_pad"],
             input_ids=view("ids"), positions=view("pos"), token_seq=view("tseq"), cu_seqlens_q=view("cu"),

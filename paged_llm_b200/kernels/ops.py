@@ -1,0 +1,291 @@
+"""The kernel library as the parts see it: `CudaOps`.
+
+Every method launches hand-written CUDA kernels of `csrc/` (compiled for
+sm_100a at first use, called through ctypes on the current stream) on torch
+tensors.  There is no CPU fallback: without a CUDA device or without nvcc the
+constructor raises.  The only library calls are the bfloat16 matrix products
+(cuBLAS through torch), where the reference's engine also calls a library
+(`nn.Linear`, pagedllm/model/llama.py:141-144); float32 products use this
+package's own CUDA-core kernel so that no reduced-precision mode can slip in.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import numpy as np
+import torch
+
+from ..csrc import build
+from . import plan as planning
+
+PL_F32, PL_BF16 = 0, 1
+_DTYPE_CODE = {torch.float32: PL_F32, torch.bfloat16: PL_BF16}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+class AttnParams(ctypes.Structure):
+    _fields_ = [
+        ("q", c_void_p), ("kv", c_void_p), ("out", c_void_p), ("block_table", c_void_p), ("cu_q", c_void_p),
+        ("k_lens", c_void_p), ("work", c_void_p), ("scratch", c_void_p), ("scratch_floats", c_longlong),
+        ("q_stride", c_int), ("out_stride", c_int), ("bt_stride", c_int), ("n_work", c_int), ("max_splits", c_int),
+        ("nh", c_int), ("nkv", c_int), ("d", c_int), ("ps", c_int), ("window", c_int), ("is_small", c_int),
+        ("scale", c_float),
+    ]
+
+
+_LIBS: dict[str, ctypes.CDLL] = {}
+
+
+def load_module(name: str) -> ctypes.CDLL:
+    """The compiled module `name`, built first if need be."""
+    lib = _LIBS.get(name)
+    if lib is None:
+        path = build.build_module(name)
+        lib = ctypes.CDLL(path)
+        lib.pl_last_error.restype = ctypes.c_char_p
+        _LIBS[name] = lib
+    return lib
+
+
+def _check(lib, rc: int) -> None:
+    if rc != 0:
+        raise KernelError(lib.pl_last_error().decode())
+
+
+def head_dim_build(d: int) -> int:
+    if d % 16 or d <= 0:
+        raise KernelError(f"head_dim={d}: the attention kernels take head sizes in steps of 16")
+    for b in build.HEAD_DIM_BUILDS:
+        if d <= b:
+            return b
+    raise KernelError(f"head_dim={d} is larger than the largest attention build ({build.HEAD_DIM_BUILDS[-1]})")
+
+
+class CudaOps:
+    supports_graphs = True
+    SMALL_ROWS = 16
+    MIN_SPLIT_KEYS = 128
+    MAX_SPLITS = 32
+
+    def __init__(self, device="cuda"):
+        self.device = torch.device(device)
+        if self.device.type != "cuda" or not torch.cuda.is_available():
+            raise KernelError("paged_llm_b200 runs on a CUDA device only (no CPU path); none is available")
+        major, minor = torch.cuda.get_device_capability(self.device)
+        if major < 10:
+            raise KernelError(f"the kernels are built for sm_100a (B200); this device is sm_{major}{minor}")
+        self.core = load_module("core")
+        self.compute_dtype = torch.bfloat16
+        self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self._scratch: list[torch.Tensor] = []
+        self._attn_lib = None
+        self._attn_fn = None
+        self.launches = 0                 # kernels of this package launched so far
+        # the library matrix products must not reduce in bfloat16
+        torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+
+    def set_compute_dtype(self, dtype: torch.dtype) -> None:
+        if dtype not in _DTYPE_CODE:
+            raise KernelError(f"compute dtype {dtype} is not supported (bfloat16 or float32)")
+        self.compute_dtype = dtype
+
+    @property
+    def _stream(self):
+        return c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    @staticmethod
+    def _p(t: torch.Tensor | None):
+        return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
+
+    def _code(self, t: torch.Tensor) -> int:
+        try:
+            return _DTYPE_CODE[t.dtype]
+        except KeyError:
+            raise KernelError(f"tensor of dtype {t.dtype} where float32 or bfloat16 is expected") from None
+
+    # ---- embedding, norms, activation ------------------------------------------
+    def embedding(self, table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+        T, (V, H) = ids.numel(), table.shape
+        out = torch.empty((T, H), dtype=torch.float32, device=self.device)
+        _check(self.core, self.core.pl_embedding(self._p(table), self._code(table), self._p(ids), self._p(out),
+                                                 T, H, V, self._stream))
+        self.launches += 1
+        return out
+
+    def rms_norm(self, x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+        return self._norm(x, None, w, eps)
+
+    def add_rms_norm(self, x: torch.Tensor, branch: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+        return self._norm(x, branch, w, eps)
+
+    def _norm(self, x, branch, w, eps):
+        assert x.dtype == torch.float32 and x.is_contiguous(), "the residual stream is contiguous float32"
+        rows, H = x.shape
+        y = torch.empty((rows, H), dtype=self.compute_dtype, device=self.device)
+        if branch is not None:
+            assert branch.shape == x.shape and branch.is_contiguous()
+        bcode = self._code(branch) if branch is not None else PL_F32
+        _check(self.core, self.core.pl_rmsnorm(self._p(x), self._p(branch), bcode, self._p(w), self._code(w),
+                                               self._p(y), self._code(y), rows, H, c_float(eps), self._stream))
+        self.launches += 1
+        return y
+
+    def silu_mul(self, gate_up: torch.Tensor) -> torch.Tensor:
+        rows, two_i = gate_up.shape
+        assert gate_up.is_contiguous() and two_i % 2 == 0
+        out = torch.empty((rows, two_i // 2), dtype=gate_up.dtype, device=self.device)
+        _check(self.core, self.core.pl_silu_mul(self._p(gate_up), self._p(out), self._code(gate_up), rows, two_i // 2,
+                                                self._stream))
+        self.launches += 1
+        return out
+
+    def gather_rows(self, x: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+        n, H = idx.numel(), x.shape[1]
+        assert x.is_contiguous()
+        out = torch.empty((n, H), dtype=x.dtype, device=self.device)
+        _check(self.core, self.core.pl_gather_rows(self._p(x), self._p(idx), self._p(out), self._code(x), n, H,
+                                                   x.shape[0], self._stream))
+        self.launches += 1
+        return out
+
+    # ---- matrix products ---------------------------------------------------------
+    def linear(self, h: torch.Tensor, w: torch.Tensor, out_float32: bool = False) -> torch.Tensor:
+        """h [M, K] @ w[N, K]^T.  float32: this package's CUDA-core kernel;
+        bfloat16: the library product with float32 accumulation."""
+        M, K = h.shape
+        N = w.shape[0]
+        assert w.shape[1] == K and h.is_contiguous() and w.is_contiguous()
+        if h.dtype == torch.float32:
+            assert w.dtype == torch.float32
+            out = torch.empty((M, N), dtype=torch.float32, device=self.device)
+            _check(self.core, self.core.pl_gemm_f32(self._p(h), self._p(w), self._p(out), M, N, K, K, K, N,
+                                                    self._stream))
+            self.launches += 1
+            return out
+        assert h.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+        if out_float32:
+            return torch.mm(h, w.t(), out_dtype=torch.float32)
+        return torch.nn.functional.linear(h, w)
+
+    # ---- positions ---------------------------------------------------------------
+    def rope_table(self, inv_freq: torch.Tensor, max_positions: int) -> torch.Tensor:
+        inv_freq = inv_freq.to(device=self.device, dtype=torch.float32).contiguous()
+        half = inv_freq.numel()
+        table = torch.empty((max_positions, half, 2), dtype=torch.float32, device=self.device)
+        _check(self.core, self.core.pl_rope_table(self._p(inv_freq), self._p(table), max_positions, half, self._stream))
+        self.launches += 1
+        return table
+
+    def rope_kv_write(self, qkv, nh, nkv, d, position, ctx, kv, block_table, write=True):
+        T = ctx.num_tokens
+        assert qkv.is_contiguous() and qkv.shape[0] == T
+        if position is not None:
+            table, table_len, rd = position.table, position.table.shape[0], position.rotary_dim
+            inter = 1 if position.pairing == "interleaved" else 0
+        else:
+            table, table_len, rd, inter = None, 0, 0, 0
+        num_pages, ps = kv.shape[0], kv.shape[3]
+        assert kv.dtype == qkv.dtype and kv.is_contiguous()
+        _check(self.core, self.core.pl_rope_kv_write(
+            self._p(qkv), self._code(qkv), T, qkv.shape[1], self._p(table), table_len, rd, inter,
+            self._p(ctx.positions), self._p(ctx.token_seq), self._p(block_table), block_table.shape[1],
+            self._p(kv), num_pages, nh, nkv, d, ps, 1 if write else 0, self._stream))
+        self.launches += 1
+
+    # ---- attention ---------------------------------------------------------------
+    def _large_rows(self) -> int:
+        return 64 if self.compute_dtype == torch.bfloat16 else 16
+
+    def plan_attention(self, q_lens, k_lens, group_size, num_kv_heads, window, pad_requests=None,
+                       fixed_capacity=False) -> dict:
+        return planning.plan_attention(
+            q_lens, k_lens, group_size, num_kv_heads, window, small_rows=self.SMALL_ROWS,
+            large_rows=self._large_rows(), min_split_keys=self.MIN_SPLIT_KEYS, num_sms=self.num_sms,
+            max_splits=self.MAX_SPLITS, pad_requests=pad_requests, fixed_capacity=fixed_capacity)
+
+    def _scratch_for(self, floats: int) -> torch.Tensor:
+        """Scratch for split partials.  Grown by allocating anew and keeping the
+        old buffers, since captured graphs hold their addresses."""
+        if not self._scratch or self._scratch[-1].numel() < floats:
+            self._scratch.append(torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=self.device))
+        return self._scratch[-1]
+
+    def _attention_bf16(self, d: int):
+        b = head_dim_build(d)
+        lib = load_module(f"attn_bf16_d{b}")
+        return lib, getattr(lib, f"pl_attention_bf16_d{b}")
+
+    def paged_attention(self, qkv, nh, nkv, d, kv, block_table, ctx, scale, window):
+        T = ctx.num_tokens
+        plan = ctx.attention_plans[(nh // nkv, nkv, window)]
+        out = torch.empty((T, nh * d), dtype=qkv.dtype, device=self.device)
+        if T > sum(ctx.host.q_lens):
+            out.zero_()                                   # padded rows of a graph bucket
+        p = AttnParams()
+        p.q, p.kv, p.out = qkv.data_ptr(), kv.data_ptr(), out.data_ptr()
+        p.block_table, p.cu_q, p.k_lens = block_table.data_ptr(), ctx.cu_seqlens_q.data_ptr(), ctx.seq_lens_k.data_ptr()
+        p.q_stride, p.out_stride, p.bt_stride = qkv.shape[1], nh * d, block_table.shape[1]
+        p.nh, p.nkv, p.d, p.ps = nh, nkv, d, kv.shape[3]
+        p.window, p.scale, p.max_splits = int(window or 0), float(scale), plan.max_splits
+        bf16 = qkv.dtype == torch.bfloat16
+        if bf16:
+            lib, fn = self._attention_bf16(d)
+        else:
+            lib, fn = self.core, self.core.pl_attention_f32
+        if plan.n_small:
+            floats = max(plan.small_tokens, 1) * nh * plan.max_splits * (d + 2)
+            scratch = self._scratch_for(floats)
+            p.scratch, p.scratch_floats = scratch.data_ptr(), scratch.numel()
+            p.work, p.n_work, p.is_small = plan.small.data_ptr(), plan.n_small, 1
+            _check(lib, fn(ctypes.byref(p), self._stream))
+            self.launches += 1
+            if plan.max_splits > 1:
+                _check(self.core, self.core.pl_attention_combine(ctypes.byref(p), self._code(out), self._stream))
+                self.launches += 1
+        if plan.n_large:
+            p.scratch, p.scratch_floats = 0, 0
+            p.work, p.n_work, p.is_small = plan.large.data_ptr(), plan.n_large, 0
+            p.max_splits = 1
+            _check(lib, fn(ctypes.byref(p), self._stream))
+            self.launches += 1
+        return out
+
+    # ---- cache -------------------------------------------------------------------
+    def copy_pages(self, pool: torch.Tensor, pairs) -> None:
+        layers, pages = pool.shape[0], pool.shape[1]
+        page_bytes = pool[0, 0].numel() * pool.element_size()
+        for src, dst in pairs:
+            _check(self.core, self.core.pl_copy_page(self._p(pool), layers, c_longlong(pages), c_longlong(page_bytes),
+                                                     int(src), int(dst), self._stream))
+            self.launches += 1
+
+    # ---- sampling ----------------------------------------------------------------
+    def argmax(self, logits: torch.Tensor) -> torch.Tensor:
+        rows, V = logits.shape
+        assert logits.dtype == torch.float32 and logits.stride(1) == 1
+        out = torch.empty(rows, dtype=torch.int32, device=self.device)
+        _check(self.core, self.core.pl_argmax(self._p(logits), self._p(out), rows, V, c_longlong(logits.stride(0)),
+                                              self._stream))
+        self.launches += 1
+        return out
+
+    def sample(self, logits, temps, top_k, top_p, seeds, counters) -> torch.Tensor:
+        rows, V = logits.shape
+        assert logits.dtype == torch.float32 and logits.stride(1) == 1
+        dev = self.device
+        t = torch.from_numpy(np.ascontiguousarray(temps, np.float32)).to(dev)
+        k = torch.from_numpy(np.ascontiguousarray(top_k, np.int32)).to(dev)
+        pp = torch.from_numpy(np.ascontiguousarray(top_p, np.float32)).to(dev)
+        s = torch.from_numpy(np.ascontiguousarray(seeds, np.uint64).view(np.int64)).to(dev)
+        c = torch.from_numpy(np.ascontiguousarray(counters, np.uint64).view(np.int64)).to(dev)
+        out = torch.empty(rows, dtype=torch.int32, device=dev)
+        _check(self.core, self.core.pl_sample(self._p(logits), self._p(out), rows, V, c_longlong(logits.stride(0)),
+                                              self._p(t), self._p(k), self._p(pp), self._p(s), self._p(c),
+                                              self._stream))
+        self.launches += 1
+        return out
