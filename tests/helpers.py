@@ -1,0 +1,45 @@
+"""Shared helpers of the GPU tests."""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from tests import plain_llama
+from tests.tiny import TINIES, make_folder, random_tokens, read_folder
+
+# Tolerances (never widened to make a test pass):
+#  float32: the engine and the plain implementation differ by summation order only.
+#  bfloat16: activations are rounded to 8 bits of mantissa between kernels; the
+#  bound is relative to the largest logit of the model.
+F32_TOL = 2e-5
+BF16_REL_TOL = 3e-2
+
+
+def model_folder(tmp_path_factory, name: str, dtype: str = "float32"):
+    hf, init = TINIES[name]
+    d = tmp_path_factory.mktemp(f"tiny{name}_{dtype}")
+    make_folder(d, hf, init, dtype=dtype)
+    return str(d)
+
+
+def plain_logits(folder: str, tokens) -> np.ndarray:
+    cfg, w = read_folder(folder)
+    return plain_llama.forward_logits(cfg, w, tokens).numpy()
+
+
+def assert_logits_close(got: np.ndarray, want: np.ndarray, dtype: str, what: str = ""):
+    assert got.shape == want.shape, f"{what}: shape {got.shape} != {want.shape}"
+    assert np.isfinite(got).all(), f"{what}: non-finite logits"
+    err = np.abs(got - want)
+    if dtype == "float32":
+        tol = F32_TOL * max(1.0, float(np.abs(want).max()))
+    else:
+        tol = BF16_REL_TOL * float(np.abs(want).max())
+    worst = np.unravel_index(err.argmax(), err.shape)
+    assert err.max() <= tol, (f"{what}: max |diff| {err.max():.3e} > {tol:.3e} at position {worst[0]}, "
+                              f"token {worst[1]}; first bad position {int(np.argmax(err.max(axis=1) > tol))}")
+
+
+def requests_for(vocab: int, lengths, seed: int = 0) -> dict[str, list[int]]:
+    return {f"r{i}": random_tokens(vocab, n, seed * 100 + i) for i, n in enumerate(lengths)}
