@@ -1,0 +1,165 @@
+"""The engine's host logic (runner metadata, cache, scheduler, replay, entry
+point) on the CPU, with the kernel library replaced by tests/torch_ops.py:
+tokens must equal the plain implementation's under chunking, mixing, preemption,
+prefix hits and fork, and every page must come back."""
+
+import numpy as np
+import pytest
+import torch
+
+from paged_llm_b200 import EngineConfig, LLMEngine, SamplingParams
+from paged_llm_b200.engine.replay import TraceReplayer
+from paged_llm_b200.engine.runner import StepItem
+from paged_llm_b200.engine.sequence import Sequence
+from tests import plain_llama, schedules
+from tests.tiny import TINIES, make_folder, random_tokens, read_folder
+from tests.torch_ops import TorchOps
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    out = {}
+    for name, (hf, init) in TINIES.items():
+        d = tmp_path_factory.mktemp(f"tiny{name}")
+        make_folder(d, hf, init)
+        out[name] = str(d)
+    return out
+
+
+def engine(folder, **kw):
+    cfg = dict(dtype="float32", device="cpu", block_size=8, num_gpu_blocks=64, max_model_len=128,
+               max_num_batched_tokens=24)
+    cfg.update(kw)
+    return LLMEngine(folder, ops=TorchOps(), **cfg)
+
+
+def plain_greedy(folder, prompt, n):
+    cfg, w = read_folder(folder)
+    return plain_llama.greedy_generate(cfg, w, prompt, n)
+
+
+def test_chunked_and_mixed_generation_equals_plain(folders):
+    eng = engine(folders["A"])
+    prompts = [random_tokens(256, n, n) for n in (5, 30, 13, 41)]
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=10))
+    for p, o in zip(prompts, outs):
+        assert o.token_ids == plain_greedy(folders["A"], p, 10) and o.finish_reason == "length"
+    assert eng.block_manager.num_free_blocks == 64
+    assert eng.stats.num_prefill_tokens == sum(map(len, prompts)) and eng.stats.num_decode_tokens == 4 * 9
+
+
+def test_prefix_hit(folders):
+    eng = engine(folders["B"], max_num_batched_tokens=128)
+    shared = random_tokens(509, 24, 7)
+    prompts = [shared + [3, 4], shared + [5, 6, 7, 8]]
+    first = eng.generate([prompts[0]], SamplingParams(temperature=0.0, max_tokens=6))[0]
+    second = eng.generate([prompts[1]], SamplingParams(temperature=0.0, max_tokens=6))[0]
+    assert first.num_cached_tokens == 0 and second.num_cached_tokens == 24
+    assert first.token_ids == plain_greedy(folders["B"], prompts[0], 6)
+    assert second.token_ids == plain_greedy(folders["B"], prompts[1], 6)
+
+
+def test_preemption_is_lossless(folders):
+    eng = engine(folders["A"], num_gpu_blocks=14, enable_prefix_caching=False)
+    prompts = [random_tokens(256, n, 40 + n) for n in (20, 22, 18, 25)]
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=16))
+    assert eng.stats.num_preemptions > 0 and sum(o.num_preemptions for o in outs) == eng.stats.num_preemptions
+    for p, o in zip(prompts, outs):
+        assert o.token_ids == plain_greedy(folders["A"], p, 16)
+    assert eng.block_manager.num_free_blocks == 14
+
+
+def test_fork_copies_the_shared_page(folders):
+    eng = engine(folders["A"], enable_prefix_caching=False, num_gpu_blocks=32)
+    sched, cm, runner = eng.scheduler, eng.block_manager, eng.runner
+    base = random_tokens(256, 11, 3)                        # one full page and 3 slots of the next
+    root = Sequence(base, SamplingParams(temperature=0.0, max_tokens=100))
+    sched.add(root)
+    out = sched.schedule(); sched.update(out, runner.run(out))
+    children = []
+    for tok in (50, 60):
+        child = Sequence(base, SamplingParams(temperature=0.0, max_tokens=3))
+        cm.fork(root, child)
+        child.token_ids = base + [tok]
+        child.status = root.status
+        sched.running.append(child)
+        children.append(child)
+    sched.abort(root.seq_id)
+    assert cm.blocks[children[0].block_table[1]].ref_count == 2
+    while sched.has_unfinished:
+        out = sched.schedule(); sched.update(out, runner.run(out))
+    assert eng.ops.calls.get("copy_pages", 0) >= 1
+    for child, tok in zip(children, (50, 60)):
+        assert child.output_token_ids == [tok] + plain_greedy(folders["A"], base + [tok], 2)
+    assert cm.num_free_blocks == 32
+
+
+def test_text_prompt_without_tokenizer_and_bad_ids(folders):
+    eng = engine(folders["A"])
+    with pytest.raises(ValueError, match="tokenizer"):
+        eng.add_request("hello")
+    with pytest.raises(ValueError, match="vocabulary"):
+        eng.add_request([1, 2, 999])
+    with pytest.raises(ValueError, match="empty prompt"):
+        eng.add_request([])
+
+
+def test_pool_too_small_is_an_error_not_a_hang(folders):
+    eng = engine(folders["A"], num_gpu_blocks=2)
+    with pytest.raises(ValueError, match="never fit"):
+        eng.generate([random_tokens(256, 40, 1)], SamplingParams(max_tokens=4))
+
+
+def test_temperature_sampling_is_reproducible_and_batch_independent(folders):
+    prompts = [random_tokens(509, n, n) for n in (1, 9, 40, 64, 100)]
+    sp = [SamplingParams(temperature=0.7, max_tokens=12, seed=3 + i) for i in range(5)]
+    together = engine(folders["B"], num_gpu_blocks=24, max_model_len=256).generate(prompts, sp)
+    assert sum(o.num_preemptions for o in together) > 0           # 24 pages of 8 force preemption
+    alone = [engine(folders["B"], num_gpu_blocks=24, max_model_len=256).generate([p], [s])[0]
+             for p, s in zip(prompts, sp)]
+    assert [o.token_ids for o in together] == [o.token_ids for o in alone]
+    other = engine(folders["B"], max_model_len=256).generate(
+        prompts[:1], [SamplingParams(temperature=0.7, max_tokens=12, seed=99)])
+    assert other[0].token_ids != together[0].token_ids
+
+
+@pytest.mark.parametrize("schedule", ["whole", "tail", "portions", "mixed"])
+def test_replay_schedules_on_the_host(folders, schedule):
+    hf, _ = TINIES["C"]
+    reqs = {f"r{i}": random_tokens(hf["vocab_size"], n, i) for i, n in enumerate((3, 70, 90, 48, 33))}
+    steps, max_tokens = getattr(schedules, schedule)(reqs)
+    rp = TraceReplayer(folders["C"], "float32", max_tokens, device="cpu", ops=TorchOps(), block_size=16,
+                       poison=float("nan"))
+    outputs = {rec["step"]: out for rec in steps if (out := rp.step(rec)) is not None}
+    got = schedules.collect(steps, outputs)
+    cfg, w = read_folder(folders["C"])
+    for rid, toks in reqs.items():
+        want = plain_llama.forward_logits(cfg, w, toks).numpy()
+        assert np.abs(got[rid] - want).max() < 2e-5, (schedule, rid)
+    assert rp.cm.num_free_blocks == rp.cm.num_blocks
+
+
+def test_replay_reports_a_pool_that_is_too_small(folders):
+    rp = TraceReplayer(folders["A"], "float32", 32, device="cpu", ops=TorchOps())
+    with pytest.raises(RuntimeError, match="max-tokens"):
+        rp.step({"step": 0, "entries": [{"id": "a", "tokens": list(range(40)), "want": []}], "end": []})
+
+
+def test_toy_architecture_with_state_steps_on_the_host(tmp_path):
+    """A mixer with state of its own, a layer run twice and a run that reads
+    another run's cache: registered by the test, no change to the package."""
+    from paged_llm_b200.weights import write_model_folder
+    from tests.toy_parts import TOY, ToyConfig, plain_toy_logits
+
+    write_model_folder(str(tmp_path), ToyConfig.from_hf_dict(TOY), seed=4, std=0.1, norm_std=0.05)
+    cfg, w = read_folder(tmp_path)
+    reqs = {"a": random_tokens(61, 50, 1), "b": random_tokens(61, 37, 2), "c": random_tokens(61, 64, 3)}
+    steps, max_tokens = schedules.mixed(reqs, live=2, seed=4)
+    rp = TraceReplayer(str(tmp_path), "float32", max_tokens, device="cpu", ops=TorchOps())
+    assert rp.storage.num_state_slots > 0 and rp.storage.num_groups == 1
+    assert len(rp.storage.pools[0]) == 1                     # two runs of the attention layer share one cache
+    outputs = {rec["step"]: out for rec in steps if (out := rp.step(rec)) is not None}
+    got = schedules.collect(steps, outputs)
+    for rid, toks in reqs.items():
+        assert np.abs(got[rid] - plain_toy_logits(cfg, w, toks).numpy()).max() < 2e-5, rid
+    assert rp.cm.num_free_state_slots == rp.cm.num_state_slots
