@@ -1,0 +1,131 @@
+"""Generation through the Python entry point and the command line on the GPU:
+greedy tokens against the plain implementation, long decoding, the first tokens
+of a sequence, temperature sampling, preemption, prefix hits."""
+
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from tests import plain_llama
+from tests.helpers import assert_logits_close, model_folder, plain_logits
+from tests.tiny import TINIES, random_tokens, read_folder
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    return {name: model_folder(tmp_path_factory, name) for name in TINIES}
+
+
+def plain_greedy(folder, prompt, n):
+    cfg, w = read_folder(folder)
+    return plain_llama.greedy_generate(cfg, w, prompt, n)
+
+
+@pytest.mark.parametrize("name,block,blocks", [("A", 16, 32), ("B", 8, 24)])
+def test_greedy_generation_float32(folders, name, block, blocks):
+    from paged_llm_b200 import LLMEngine, SamplingParams
+    hf, _ = TINIES[name]
+    lengths = (5, 17, 33) if name == "A" else (1, 9, 40, 64, 100)
+    prompts = [random_tokens(hf["vocab_size"], n, 10 + n) for n in lengths]
+    eng = LLMEngine(folders[name], dtype="float32", block_size=block, num_gpu_blocks=blocks, max_model_len=128,
+                    max_num_batched_tokens=32)
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8))
+    for p, o in zip(prompts, outs):
+        assert o.token_ids == plain_greedy(folders[name], p, 8)
+    if name == "B":
+        assert eng.stats.num_preemptions > 0, "24 pages of 8 tokens cannot hold all five requests"
+    assert eng.block_manager.num_free_blocks == blocks
+    assert eng.runner.num_graph_steps > 0 and eng.ops.launches > 0
+
+
+def test_greedy_generation_bfloat16_follows_the_plain_model(folders):
+    """bfloat16 may flip a near-tie; every generated token must be the argmax or
+    within rounding of it in the plain model's logits for the same prefix."""
+    from paged_llm_b200 import LLMEngine, SamplingParams
+    hf, _ = TINIES["C"]
+    prompts = [random_tokens(hf["vocab_size"], n, 20 + n) for n in (3, 30, 77)]
+    eng = LLMEngine(folders["C"], dtype="bfloat16", num_gpu_blocks=64, max_model_len=256)
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=10))
+    for p, o in zip(prompts, outs):
+        seq = list(p)
+        for tok in o.token_ids:
+            ref = plain_logits(folders["C"], seq)[-1]
+            assert ref.max() - ref[tok] <= 3e-2 * np.abs(ref).max()
+            seq.append(tok)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(folders, dtype):
+    """300 decoded tokens from a short prompt, teacher-forced, against the plain logits."""
+    from paged_llm_b200.engine.replay import TraceReplayer
+    hf, _ = TINIES["C"]
+    toks = random_tokens(hf["vocab_size"], 305, 77)
+    rp = TraceReplayer(folders["C"], dtype, 320)
+    rows = [rp.step({"step": 0, "entries": [{"id": "a", "tokens": toks[:5], "want": [4]}], "end": []})[0]]
+    for i in range(5, 305):
+        rows.append(rp.step({"step": i, "entries": [{"id": "a", "tokens": [toks[i]], "want": [0]}], "end": []})[0])
+    assert_logits_close(np.stack(rows), plain_logits(folders["C"], toks)[4:], dtype, "long decoding")
+    assert rp.runner.num_graph_steps == 300
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_of_a_sequence(folders, dtype):
+    """A prompt of one token, then single tokens: positions 0, 1, 2, ... each on their own."""
+    from paged_llm_b200.engine.replay import TraceReplayer
+    hf, _ = TINIES["B"]
+    toks = random_tokens(hf["vocab_size"], 12, 5)
+    rp = TraceReplayer(folders["B"], dtype, 64, block_size=8)
+    rows = [rp.step({"step": i, "entries": [{"id": "a", "tokens": [t], "want": [0]}], "end": []})[0]
+            for i, t in enumerate(toks)]
+    assert_logits_close(np.stack(rows), plain_logits(folders["B"], toks), dtype, "first tokens")
+
+
+def test_temperature_sampling_follows_the_plain_draw(folders):
+    """Tiny B, temperature 0.7: each sampled token is what the plain sampler draws
+    from the plain logits with the same stream."""
+    from paged_llm_b200 import LLMEngine, SamplingParams
+    from tests.plain_sampling import gumbel_scores
+    hf, _ = TINIES["B"]
+    prompts = [random_tokens(hf["vocab_size"], n, n) for n in (1, 9, 40)]
+    sps = [SamplingParams(temperature=0.7, max_tokens=12, seed=3 + i) for i in range(3)]
+    eng = LLMEngine(folders["B"], dtype="float32", block_size=8, num_gpu_blocks=24, max_model_len=256)
+    outs = eng.generate(prompts, sps)
+    for p, sp, o in zip(prompts, sps, outs):
+        seq = list(p)
+        for tok in o.token_ids:
+            scores = gumbel_scores(plain_logits(folders["B"], seq)[-1], 0.7, -1, 1.0, sp.seed, len(seq))
+            assert scores.max() - scores[tok] < 1e-3
+            seq.append(tok)
+    again = LLMEngine(folders["B"], dtype="float32", block_size=8, num_gpu_blocks=24, max_model_len=256).generate(prompts, sps)
+    assert [o.token_ids for o in again] == [o.token_ids for o in outs]
+
+
+def test_prefix_hit_and_stats(folders):
+    from paged_llm_b200 import LLMEngine, SamplingParams
+    hf, _ = TINIES["A"]
+    shared = random_tokens(hf["vocab_size"], 48, 1)
+    eng = LLMEngine(folders["A"], dtype="float32", num_gpu_blocks=32, max_model_len=128)
+    a = eng.generate([shared + [1, 2]], SamplingParams(temperature=0.0, max_tokens=4))[0]
+    b = eng.generate([shared + [3, 4, 5]], SamplingParams(temperature=0.0, max_tokens=4))[0]
+    assert a.num_cached_tokens == 0 and b.num_cached_tokens == 48
+    assert b.token_ids == plain_greedy(folders["A"], shared + [3, 4, 5], 4)
+    assert eng.block_manager.num_cache_hits == 1
+
+
+def test_command_line(folders):
+    proc = subprocess.run(
+        [sys.executable, os.path.join(ROOT, "examples", "generate.py"), "--model", folders["A"], "--dtype", "float32",
+         "--max-tokens", "5", "--temperature", "0.0", "--prompt-ids", "5,17,3", "--prompt-ids", "9", "--num-blocks", "32",
+         "--max-model-len", "128"],
+        capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    want = [plain_greedy(folders["A"], p, 5) for p in ([5, 17, 3], [9])]
+    for w in want:
+        assert str(w) in proc.stdout, proc.stdout
+    assert "steps=" in proc.stdout and "preemptions=0" in proc.stdout
