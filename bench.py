@@ -1,0 +1,444 @@
+"""Headline benchmark: decode tokens per second of the TinyLlama-1.1B-sized Llama
+(random bfloat16 weights) at batch 8 with 512-token prompts, on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one decode step.  The timed region is exactly K steps after W warm-up
+steps, timed with CUDA events on the launching stream.  One JSON line is
+printed; beside `value` (device-timed loop: tokens stay on the device) it holds
+
+* `e2e`: the same through `LLMEngine.step()`: host token ids in, host token ids
+  out, every step (metadata host-to-device from pinned memory, sampled ids
+  device-to-host);
+* `prefill`: one step of a 2,048-token prompt, with the fraction of the bf16 peak;
+* `roofline`: bytes a decode step must read (weights once, the live cache)
+  divided by its time, against the measured HBM bandwidth;
+* `points`: decode tokens per second at batch 1 and 64;
+* `clocks`: SM clock and throttle reasons sampled during the timed region;
+* `gpu_launches`: kernels of this package launched in the timed region.
+
+Weights (2.2 GB) are larger than the 126 MB L2, so every step re-reads them from
+HBM; no L2 flush is needed between iterations.
+
+`--impl reference` runs the unmodified reference (xiyiji/paged-llm, installed
+under baseline/_ref) through its own `LLMEngine` on the same model folder and
+prints the same line with "impl": "reference".
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+SIZES = {
+    # BASELINE.json configs[2]: TinyLlama 1.1B layer sizes
+    "tinyllama-1.1b": dict(vocab_size=32000, hidden_size=2048, intermediate_size=5632, num_hidden_layers=22,
+                           num_attention_heads=32, num_key_value_heads=4, head_dim=64, rope_theta=10000.0,
+                           rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=2048),
+    # for trying the script out on small hardware; never the default
+    "tiny-a": dict(vocab_size=256, hidden_size=64, intermediate_size=172, num_hidden_layers=2,
+                   num_attention_heads=4, num_key_value_heads=2, head_dim=16, max_position_embeddings=4096),
+}
+PROMPT_LEN, DECODE_LEN, PREFILL_TOKENS, BLOCK_SIZE = 512, 256, 2048, 16
+
+
+def load_peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                raw = json.load(f)
+            flat = {}
+
+            def walk(d):
+                for k, v in d.items():
+                    if isinstance(v, dict):
+                        walk(v)
+                    elif isinstance(v, (int, float)):
+                        flat.setdefault(k, float(v))
+            walk(raw)
+            out = {"source": "measured"}
+            out["hbm_gbs"] = flat.get("hbm_gbs") or FALLBACK_PEAKS["hbm_gbs"]
+            out["bf16_tflops"] = flat.get("bf16_tflops") or FALLBACK_PEAKS["bf16_tflops"]
+            if "bf16_tflops_sustained" in flat:
+                out["bf16_tflops_sustained"] = flat["bf16_tflops_sustained"]
+            return out
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """nvidia-smi in a loop during the timed region (reads settings, changes none)."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int = 0):
+        self.proc = None
+        self.path = None
+        self.uuid = None
+        try:
+            import torch
+            self.uuid = "GPU-" + str(torch.cuda.get_device_properties(device_index).uuid)
+        except Exception:
+            self.uuid = None
+
+    def __enter__(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            cmd = ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"]
+            if self.uuid:
+                cmd += ["-i", self.uuid]
+            self.proc = subprocess.Popen(cmd, stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            with open(self.path) as f:
+                for line in f:
+                    parts = [p.strip() for p in line.split(",")]
+                    if len(parts) < 7:
+                        continue
+                    try:
+                        sm.append(float(parts[0]))
+                        mx.append(float(parts[1]))
+                    except ValueError:
+                        continue
+                    for name, flag in zip(names, parts[3:7]):
+                        if flag.lower().startswith("active"):
+                            reasons.add(name)
+            os.unlink(self.path)
+        except (OSError, TypeError):
+            pass
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def write_tokenizer(folder: str, vocab: int) -> None:
+    """A word-level tokenizer over token names t0..tN, only so that the
+    reference's engine, which loads a tokenizer unconditionally, starts."""
+    from tokenizers import Tokenizer, models, pre_tokenizers
+
+    tok = Tokenizer(models.WordLevel({f"t{i}": i for i in range(vocab)}, unk_token="t0"))
+    tok.pre_tokenizer = pre_tokenizers.Whitespace()
+    tok.save(os.path.join(folder, "tokenizer.json"))
+    with open(os.path.join(folder, "tokenizer_config.json"), "w") as f:
+        json.dump({"tokenizer_class": "PreTrainedTokenizerFast", "unk_token": "t0", "eos_token": "t1"}, f)
+
+
+def make_model(folder: str, size: str, layers: int | None, with_tokenizer: bool = False):
+    from paged_llm_b200.config import LlamaConfig
+    from paged_llm_b200.weights import write_model_folder
+
+    hf = {"architectures": ["LlamaForCausalLM"], **SIZES[size]}
+    full_layers = hf["num_hidden_layers"]
+    if layers:
+        hf["num_hidden_layers"] = layers
+    cfg = LlamaConfig.from_hf_dict(hf)
+    write_model_folder(folder, cfg, seed=0, std=0.02, dtype="bfloat16")
+    if with_tokenizer:
+        write_tokenizer(folder, cfg.vocab_size)
+    return cfg, full_layers
+
+
+def prompts_for(vocab: int, batch: int, length: int, seed: int = 0):
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (length,), generator=g).tolist() for _ in range(batch)]
+
+
+def step_flops(cfg, tokens: int, context_start: int = 0) -> float:
+    """Multiply-adds x 2 of one step of `tokens` new tokens of one request."""
+    h, d = cfg.hidden_size, cfg.head_dim
+    per_layer = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * d * h + cfg.num_attention_heads * d * h \
+        + 3 * cfg.intermediate_size * h
+    gemm = 2.0 * tokens * per_layer * cfg.num_hidden_layers + 2.0 * cfg.vocab_size * h
+    keys = sum(context_start + i + 1 for i in range(tokens))
+    attn = 4.0 * cfg.num_attention_heads * d * keys * cfg.num_hidden_layers
+    return gemm + attn
+
+
+# ------------------------------------------------------------------------------ ours
+
+def device_decode_loop(engine, batch: int, steps: int, warmup: int, prompt_len: int):
+    """Prefills `batch` requests, then times `steps` decode steps on the device:
+    sampled tokens stay on the device and feed the next step.  Returns
+    (ms per step, launches per step, context length at the middle of the run)."""
+    import torch
+    from paged_llm_b200.config import SamplingParams
+    from paged_llm_b200.engine.runner import StepItem
+    from paged_llm_b200.engine.sequence import Sequence
+
+    cm, runner, ops = engine.block_manager, engine.runner, engine.ops
+    vocab = engine.model_config.vocab_size
+    seqs = [Sequence(p, SamplingParams(temperature=0.0, max_tokens=steps + warmup + 2))
+            for p in prompts_for(vocab, batch, prompt_len, seed=batch)]
+    chunk = max(1, engine.config.max_num_batched_tokens // prompt_len)
+    for i in range(0, batch, chunk):
+        group = seqs[i:i + chunk]
+        for s in group:
+            assert cm.allocate_slots(s, prompt_len) is not None, "pool too small for the benchmark"
+        logits = runner.step([StepItem(s, prompt_len, (prompt_len - 1,)) for s in group])
+        toks = ops.argmax(logits).tolist()
+        for s, t in zip(group, toks):
+            s.num_computed_tokens = prompt_len
+            s.append_token(t)
+    items = [StepItem(s, 1, (0,)) for s in seqs]
+
+    def one_step(first: bool):
+        for s in seqs:
+            assert cm.allocate_slots(s, 1) is not None
+        logits = runner.step(items)
+        nxt = ops.argmax(logits)
+        for s in seqs:
+            s.num_computed_tokens += 1
+            s.token_ids.append(0)            # the id lives on the device; the host list only keeps the length
+        return nxt
+
+    # device-resident feedback: the ids section of the next step's metadata is overwritten on the device
+    def run(n):
+        nonlocal last
+        for _ in range(n):
+            if last is not None:
+                runner.next_ids_override = last
+            last = one_step(False)
+
+    last = None
+    run(warmup)
+    torch.cuda.synchronize()
+    launches0 = ops.launches + runner.graph_launches
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ctx_mid = seqs[0].num_computed_tokens + steps // 2
+    start.record()
+    run(steps)
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / steps
+    launches = (ops.launches + runner.graph_launches - launches0) / steps
+    for s in seqs:
+        cm.free(s)
+    return ms, launches, ctx_mid
+
+
+def e2e_decode(engine, batch: int, steps: int, warmup: int, prompt_len: int):
+    """The same decode steps through the public `LLMEngine.step()`: token ids
+    come back to the host every step."""
+    import torch
+    from paged_llm_b200.config import SamplingParams
+
+    vocab = engine.model_config.vocab_size
+    sp = SamplingParams(temperature=0.0, max_tokens=steps + warmup + 1, ignore_eos=True)
+    for p in prompts_for(vocab, batch, prompt_len, seed=100 + batch):
+        engine.add_request(p, sp)
+    while any(not s.is_prefill_done or s.num_generated_tokens == 0 for s in engine.scheduler.running) \
+            or engine.scheduler.waiting:
+        engine.step()
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    h2d0 = engine.runner.h2d_bytes
+    t0 = time.perf_counter()
+    n_tokens = 0
+    for _ in range(steps):
+        n_tokens += sum(1 for o in engine.step() if o.new_token is not None)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    h2d = (engine.runner.h2d_bytes - h2d0) / steps
+    while engine.has_unfinished_requests:
+        engine.step()
+    return n_tokens / dt, h2d, batch * 4
+
+
+def prefill_once(engine, tokens: int, iters: int = 5, warmup: int = 3):
+    import torch
+    from paged_llm_b200.config import SamplingParams
+    from paged_llm_b200.engine.runner import StepItem
+    from paged_llm_b200.engine.sequence import Sequence
+
+    cm, runner = engine.block_manager, engine.runner
+    vocab = engine.model_config.vocab_size
+    times = []
+    for i in range(warmup + iters):
+        seq = Sequence(prompts_for(vocab, 1, tokens, seed=7 + i)[0], SamplingParams())
+        assert cm.allocate_slots(seq, tokens) is not None
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        runner.step([StepItem(seq, tokens, (tokens - 1,))])
+        end.record()
+        torch.cuda.synchronize()
+        if i >= warmup:
+            times.append(start.elapsed_time(end))
+        cm.free(seq)
+    return statistics.median(times)
+
+
+def run_ours(args) -> dict:
+    import torch
+    from paged_llm_b200 import EngineConfig, LLMEngine
+
+    peaks = load_peaks()
+    with tempfile.TemporaryDirectory() as folder:
+        cfg, full_layers = make_model(folder, args.size, args.layers)
+        max_len = max(PROMPT_LEN + args.steps + args.warmup + DECODE_LEN, PREFILL_TOKENS) + 64
+        engine = LLMEngine(folder, EngineConfig(
+            dtype="bfloat16", block_size=BLOCK_SIZE, max_model_len=max_len, max_num_seqs=64,
+            max_num_batched_tokens=max(2048, PREFILL_TOKENS), enable_prefix_caching=False,
+            num_gpu_blocks=64 * (-(-max_len // BLOCK_SIZE)) + 64))
+    B = args.batch
+    weight_bytes = engine.model.weight_bytes_per_step()
+    kv_bytes_per_token = engine.kv_cache.page_bytes() // BLOCK_SIZE
+
+    with ClockSampler() as clocks:
+        ms, launches, ctx_mid = device_decode_loop(engine, B, args.steps, args.warmup, PROMPT_LEN)
+    clock_summary = clocks.summary()
+    value = B * 1000.0 / ms
+    step_bytes = weight_bytes + B * ctx_mid * kv_bytes_per_token
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+
+    e2e_value, h2d, d2h = e2e_decode(engine, B, args.steps, args.warmup, PROMPT_LEN)
+    points = {}
+    for b in (1, 64):
+        pms, _, _ = device_decode_loop(engine, b, min(args.steps, 128), args.warmup, PROMPT_LEN)
+        points[f"decode_b{b}"] = round(b * 1000.0 / pms, 1)
+    pre_ms = prefill_once(engine, PREFILL_TOKENS)
+    flops = step_flops(cfg, PREFILL_TOKENS)
+    peak_flops = peaks["bf16_tflops"] * 1e12
+
+    return {
+        "metric": "decode tok/s at batch 8 (TinyLlama 1.1B sizes, 512-token prompts, bf16, one B200)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random weights N(0, 0.02) seed 0, uniform random token ids",
+        "impl": "ours",
+        "config": {
+            "model": "TinyLlama-1.1B layer sizes" if args.size == "tinyllama-1.1b" else args.size,
+            "global_batch": B, "seq_len": PROMPT_LEN + DECODE_LEN, "prompt_len": PROMPT_LEN,
+            "decode_len": DECODE_LEN, "parallelism": "single GPU", "layers": cfg.num_hidden_layers,
+            "layers_full": full_layers, "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads,
+            "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size,
+            "vocab": cfg.vocab_size, "block_size": BLOCK_SIZE, "params": cfg.num_parameters,
+            "l2": "weights (2.2 GB) exceed the 126 MB L2: no flush between iterations",
+            "peaks": peaks["source"], "cuda_graphs": not engine.config.enforce_eager,
+        },
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
+                "d2h_bytes_per_step": int(d2h)},
+        "gpu_launches": int(round(launches * args.steps)),
+        "clocks": clock_summary,
+        "prefill": {"value": round(PREFILL_TOKENS * 1000.0 / pre_ms, 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(pre_ms, 3), "frac": round(flops / (pre_ms * 1e-3) / peak_flops, 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peaks["hbm_gbs"], 4)},
+        "points": points,
+    }
+
+
+# ------------------------------------------------------------------------------ reference
+
+def run_reference(args) -> dict:
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "pagedllm")):
+        return {"impl": "reference", "unavailable": "baseline/_ref holds no installed reference (pip install --target failed or was not run)"}
+    try:
+        import torch
+        if not torch.cuda.is_available():
+            return {"impl": "reference", "unavailable": "no CUDA device"}
+        sys.path.insert(0, ref_dir)
+        from pagedllm import EngineConfig, SamplingParams
+        from pagedllm.engine import LLMEngine
+    except Exception as e:                                            # noqa: BLE001
+        return {"impl": "reference", "unavailable": f"import of the reference failed: {type(e).__name__}: {e}"[:300]}
+    B = args.batch
+    try:
+        with tempfile.TemporaryDirectory() as folder:
+            cfg, full_layers = make_model(folder, args.size, args.layers, with_tokenizer=True)
+            max_len = PROMPT_LEN + args.steps + args.warmup + DECODE_LEN + 64
+            engine = LLMEngine(folder, EngineConfig(
+                dtype="bfloat16", block_size=BLOCK_SIZE, max_model_len=max_len, max_num_seqs=64,
+                max_num_batched_tokens=4096, enable_prefix_caching=False,
+                num_gpu_blocks=64 * (-(-max_len // BLOCK_SIZE)) + 64))
+        sp = SamplingParams(temperature=0.0, max_tokens=args.steps + args.warmup + 1, ignore_eos=True)
+        for p in prompts_for(cfg.vocab_size, B, PROMPT_LEN, seed=100 + B):
+            engine.add_request(p, sp)
+        while engine.scheduler.waiting or any(s.num_generated_tokens == 0 for s in engine.scheduler.running):
+            engine.step()
+        for _ in range(args.warmup):
+            engine.step()
+        torch.cuda.synchronize()
+        with ClockSampler() as clocks:
+            t0 = time.perf_counter()
+            n = 0
+            for _ in range(args.steps):
+                n += sum(1 for o in engine.step() if o.new_token is not None)
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+        value = n / dt
+        return {
+            "metric": "decode tok/s at batch 8 (TinyLlama 1.1B sizes, 512-token prompts, bf16, one B200)",
+            "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(dt * 1000.0 / args.steps, 4), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic: random weights, uniform random token ids",
+            "impl": "reference",
+            "config": {"model": "TinyLlama-1.1B layer sizes" if args.size == "tinyllama-1.1b" else args.size,
+                       "global_batch": B, "seq_len": PROMPT_LEN + DECODE_LEN, "prompt_len": PROMPT_LEN,
+                       "layers": cfg.num_hidden_layers, "layers_full": full_layers, "parallelism": "single GPU",
+                       "attention": engine.attention_backend, "timing": "wall clock around LLMEngine.step()"},
+            "e2e": {"value": round(value, 1), "unit": "tokens/s"},
+            "clocks": clocks.summary(),
+        }
+    except Exception as e:                                            # noqa: BLE001
+        return {"impl": "reference", "unavailable": f"the reference failed to run: {type(e).__name__}: {e}"[:300]}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--size", choices=sorted(SIZES), default="tinyllama-1.1b")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the named size (reported in config)")
+    args = ap.parse_args()
+    if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"unavailable": f"this engine runs on one GPU; --gpus {args.gpus} is not supported",
+                              "n_gpus": args.gpus}))
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    line = run_reference(args) if args.impl == "reference" else run_ours(args)
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

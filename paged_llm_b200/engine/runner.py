@@ -70,6 +70,11 @@ class ModelRunner:
         self.use_graphs = (not config.enforce_eager) and self.device.type == "cuda" and getattr(ops, "supports_graphs", False)
         self.num_graph_steps = 0
         self.num_eager_steps = 0
+        self.graph_launches = 0            # kernels of this package launched by graph replays
+        self.h2d_bytes = 0                 # metadata bytes copied host-to-device so far
+        # A device tensor of token ids that replaces the next step's input ids on the
+        # device (decode loops that never bring sampled tokens to the host).
+        self.next_ids_override: torch.Tensor | None = None
 
     # ------------------------------------------------------------------ metadata
     def _gather(self, items: list[StepItem], pad_to: int | None = None, table_stride: int | None = None):
@@ -171,6 +176,7 @@ class ModelRunner:
                 self._dev_meta = torch.empty(max(pk.size * 2, 1 << 16), dtype=torch.int32, device=self.device)
             dev = self._dev_meta
         dev[:pk.size].copy_(host[:pk.size], non_blocking=True)
+        self.h2d_bytes += pk.size * 4
         if self.device.type == "cuda":
             ev = torch.cuda.Event()
             ev.record()
@@ -216,10 +222,12 @@ class ModelRunner:
         for it in items:
             if it.seq.state_slot is not None and it.seq.num_computed_tokens == 0:
                 self.storage.zero_state(it.seq.state_slot)
+        override, self.next_ids_override = self.next_ids_override, None
         if self._graph_eligible(items):
-            return self._graph_step(items)
+            return self._graph_step(items, override)
         pk, host, info = self._gather(items)
         dev = self._upload(pk)
+        self._override_ids(dev, override)
         ctx = self._context(pk, dev, host, info)
         self.num_eager_steps += 1
         return self.model.forward(ctx)
@@ -235,18 +243,25 @@ class ModelRunner:
     def _table_stride(self) -> int:
         return _align(-(-self.config.max_model_len // self.page_size))
 
-    def _graph_step(self, items: list[StepItem]) -> torch.Tensor:
+    @staticmethod
+    def _override_ids(dev: torch.Tensor, ids: torch.Tensor | None) -> None:
+        if ids is not None:
+            dev[:ids.numel()].copy_(ids.to(torch.int32), non_blocking=True)     # "ids" is the first section
+
+    def _graph_step(self, items: list[StepItem], override: torch.Tensor | None = None) -> torch.Tensor:
         B = next(b for b in self.GRAPH_BUCKETS if b >= len(items))
         pk, host, info = self._gather(items, pad_to=B, table_stride=self._table_stride())
         entry = self._graphs.get(B)
         if entry is None:
             entry = self._capture(B, pk, host, info)
-        dev, graph, logits, size = entry
+        dev, graph, logits, size, launches = entry
         if pk.size != size:
             raise RuntimeError("metadata layout changed between capture and replay")
         self._upload(pk, dev)
+        self._override_ids(dev, override)
         graph.replay()
         self.num_graph_steps += 1
+        self.graph_launches += launches
         return logits[:len(items)]
 
     def _capture(self, B: int, pk: _Packer, host: HostBatch, info: dict):
@@ -261,9 +276,13 @@ class ModelRunner:
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
+        before = getattr(self.ops, "launches", 0)
         with torch.cuda.graph(graph):
             logits = self.model.forward(ctx)
-        entry = (dev, graph, logits, pk.size)
+        launches = getattr(self.ops, "launches", 0) - before
+        if hasattr(self.ops, "launches"):
+            self.ops.launches = before        # capturing launches nothing; replays are counted in graph_launches
+        entry = (dev, graph, logits, pk.size, launches)
         self._graphs[B] = entry
         return entry
 
