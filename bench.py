@@ -314,6 +314,13 @@ def run_ours(args) -> dict:
             max_num_batched_tokens=max(2048, PREFILL_TOKENS), enable_prefix_caching=False,
             num_gpu_blocks=64 * (-(-max_len // BLOCK_SIZE)) + 64))
     B = args.batch
+    if args.only == "decode":            # a short run of one part, for profilers
+        ms, launches, ctx_mid = device_decode_loop(engine, B, args.steps, args.warmup, PROMPT_LEN)
+        return {"only": "decode", "batch": B, "ms_per_step": round(ms, 4), "launches_per_step": launches,
+                "layers": cfg.num_hidden_layers}
+    if args.only == "prefill":
+        pre_ms = prefill_once(engine, PREFILL_TOKENS, iters=max(1, args.steps), warmup=args.warmup)
+        return {"only": "prefill", "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3), "layers": cfg.num_hidden_layers}
     weight_bytes = engine.model.weight_bytes_per_step()
     kv_bytes_per_token = engine.kv_cache.page_bytes() // BLOCK_SIZE
 
@@ -427,6 +434,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--size", choices=sorted(SIZES), default="tinyllama-1.1b")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the named size (reported in config)")
+    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+                    help="run only the decode loop or only the prefill step and print a short line (for profilers)")
     args = ap.parse_args()
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
         if int(os.environ.get("RANK", "0")) == 0:

@@ -67,6 +67,8 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
     constexpr int BM = Shape::BM, BN = Shape::BN, PITCH = Shape::PITCH, THREADS = Shape::THREADS;
     constexpr int CH = DPAD / 8;                          // 16-byte chunks per row
     constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
+    pdl_launch_dependents();
+    pdl_wait();
     const AttnItem it = attn_decode_item(p, blockIdx.x, BM, BN);
     if (!it.valid) return;
 
@@ -92,17 +94,31 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
         *reinterpret_cast<uint4*>(Qs + r * PITCH + c8 * 8) = v;
     }
 
+    // One key tile: every thread first looks up the pages of all its rows (independent loads
+    // that travel together), then issues the copies.
+    constexpr int LOAD_ITERS = (BN * CH + THREADS - 1) / THREADS;
     auto load_tile = [&](int stage, int kt) {
         __nv_bfloat16* kd = Ks + stage * BN * PITCH;
         __nv_bfloat16* vd = Vs + stage * BN * PITCH;
-        for (int e = tid; e < BN * CH; e += THREADS) {
+        int pg[LOAD_ITERS];
+#pragma unroll
+        for (int i = 0; i < LOAD_ITERS; ++i) {
+            const int e = tid + i * THREADS;
             const int j = e / CH, c8 = e - j * CH;
             const int n = kt + j;
-            bool ok = n < it.key_hi && c8 * 8 < d;
-            int page = ok ? bt[n / p.ps] : -1;
-            ok = ok && page >= 0;
-            const __nv_bfloat16* src =
-                ok ? kv + ((((size_t)page * 2) * p.nkv + kvh) * p.ps + n % p.ps) * d + c8 * 8 : kv;
+            const bool ok = e < BN * CH && n < it.key_hi && c8 * 8 < d;
+            const int pi = p.ps_shift >= 0 ? n >> p.ps_shift : n / p.ps;
+            pg[i] = ok ? bt[pi] : -1;
+        }
+#pragma unroll
+        for (int i = 0; i < LOAD_ITERS; ++i) {
+            const int e = tid + i * THREADS;
+            if (e >= BN * CH) break;
+            const int j = e / CH, c8 = e - j * CH;
+            const int n = kt + j;
+            const int po = p.ps_shift >= 0 ? n & (p.ps - 1) : n % p.ps;
+            const bool ok = pg[i] >= 0;
+            const __nv_bfloat16* src = ok ? kv + ((((size_t)pg[i] * 2) * p.nkv + kvh) * p.ps + po) * d + c8 * 8 : kv;
             cp_async16(kd + j * PITCH + c8 * 8, src, ok ? 16 : 0);
             cp_async16(vd + j * PITCH + c8 * 8, ok ? src + v_off : kv, ok ? 16 : 0);
         }
@@ -268,6 +284,68 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
             part[3 + c] = o1;
         }
     }
+    if (it.splits <= 1 || p.counters == nullptr) return;
+
+    // The block of this request and kv head that finishes last merges the splits.
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) is_last = atomicAdd(&p.counters[(size_t)it.seq * p.nkv + kvh], 1u) == (unsigned)it.splits - 1;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    // (m, l) of every row and split go to shared memory in one parallel pass, the factors are
+    // formed there, then every thread adds up one column pair over the splits.
+    float* ml = reinterpret_cast<float*>(smem_raw);                          // [rows][splits][2] -> factors
+    const int n_ml = it.rows_total * it.splits;
+    for (int e = tid; e < n_ml; e += THREADS) {
+        const int R = e / it.splits, j = e - R * it.splits;
+        const float2 v = __ldcg(reinterpret_cast<const float2*>(attn_partial(p, it.scratch_base + R / G, kvh * G + R % G, j)));
+        ml[2 * e] = v.x;
+        ml[2 * e + 1] = v.y;
+    }
+    __syncthreads();
+    for (int R = tid; R < it.rows_total; R += THREADS) {
+        float M = -INFINITY;
+        for (int j = 0; j < it.splits; ++j) M = fmaxf(M, ml[2 * (R * it.splits + j)]);
+        float L = 0.f;
+        for (int j = 0; j < it.splits; ++j) {
+            const float mj = ml[2 * (R * it.splits + j)];
+            const float f = mj == -INFINITY ? 0.f : __expf(mj - M);
+            L += ml[2 * (R * it.splits + j) + 1] * f;
+            ml[2 * (R * it.splits + j)] = f;
+        }
+        const float inv = L > 0.f ? 1.0f / L : 0.f;
+        for (int j = 0; j < it.splits; ++j) ml[2 * (R * it.splits + j)] *= inv;
+    }
+    __syncthreads();
+    for (int e = tid; e < it.rows_total * (d / 2); e += THREADS) {
+        const int R = e / (d / 2), c = (e - R * (d / 2)) * 2;
+        const int tok = R / G, head = kvh * G + R % G;
+        const float* part0 = attn_partial(p, it.scratch_base + tok, head, 0) + 2 + c;
+        const size_t stride = (size_t)(d + 2);
+        float o0 = 0.f, o1 = 0.f;
+        int j = 0;
+        for (; j + 4 <= it.splits; j += 4) {
+            const float2 v0 = __ldcg(reinterpret_cast<const float2*>(part0 + (j + 0) * stride));
+            const float2 v1 = __ldcg(reinterpret_cast<const float2*>(part0 + (j + 1) * stride));
+            const float2 v2 = __ldcg(reinterpret_cast<const float2*>(part0 + (j + 2) * stride));
+            const float2 v3 = __ldcg(reinterpret_cast<const float2*>(part0 + (j + 3) * stride));
+            const float f0 = ml[2 * (R * it.splits + j)], f1 = ml[2 * (R * it.splits + j + 1)];
+            const float f2 = ml[2 * (R * it.splits + j + 2)], f3 = ml[2 * (R * it.splits + j + 3)];
+            o0 += v0.x * f0 + v1.x * f1 + v2.x * f2 + v3.x * f3;
+            o1 += v0.y * f0 + v1.y * f1 + v2.y * f2 + v3.y * f3;
+        }
+        for (; j < it.splits; ++j) {
+            const float2 v = __ldcg(reinterpret_cast<const float2*>(part0 + j * stride));
+            const float f = ml[2 * (R * it.splits + j)];
+            o0 += v.x * f;
+            o1 += v.y * f;
+        }
+        __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)(it.q0 + tok) * p.out_stride + head * d + c;
+        *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(o0, o1);
+    }
+    if (tid == 0) p.counters[(size_t)it.seq * p.nkv + kvh] = 0u;      // ready for the next launch
 }
 
 template <int DPAD, int MW, int NW, int KPW>
@@ -279,8 +357,8 @@ int launch_attn_bf16(const AttnParams& p, cudaStream_t stream) {
                                      Shape::SMEM_BYTES));
         attr_set = true;
     }
-    attn_bf16_kernel<DPAD, MW, NW, KPW><<<dim3(p.n_work, p.nkv), Shape::THREADS, Shape::SMEM_BYTES, stream>>>(p);
-    PL_LAUNCHED("attention_bf16");
+    PL_CUDA(launch_pdl(attn_bf16_kernel<DPAD, MW, NW, KPW>, dim3(p.n_work, p.nkv), dim3(Shape::THREADS),
+                       (size_t)Shape::SMEM_BYTES, stream, p));
     return 0;
 }
 
@@ -300,7 +378,7 @@ PL_EXPORT int PL_CAT(pl_attention_bf16_d, PL_DPAD)(const AttnParams* params, cud
                p.d, PL_DPAD);
     PL_REQUIRE(p.q_stride % 8 == 0 && p.out_stride % 2 == 0, "attention_bf16: row strides must keep 16-byte alignment");
     PL_REQUIRE(((uintptr_t)p.q & 15) == 0 && ((uintptr_t)p.kv & 15) == 0, "attention_bf16: q and kv must be 16-byte aligned");
-    constexpr int KPW_SMALL = PL_DPAD <= 64 ? 64 : (PL_DPAD == 128 ? 32 : 16);
+    constexpr int KPW_SMALL = PL_DPAD <= 128 ? 32 : 16;
     if (p.is_small) return launch_attn_bf16<PL_DPAD, 1, 4, KPW_SMALL>(p, stream);
     return launch_attn_bf16<PL_DPAD, 4, 1, 64>(p, stream);
 }

@@ -106,6 +106,8 @@ PL_EXPORT int pl_attention_decode_static(const void* q, int q_stride, const void
     p.window = window;
     p.is_small = 1;
     p.scale = scale;
+    p.ps_shift = (page_size & (page_size - 1)) == 0 ? __builtin_ctz(page_size) : -1;
+    p.counters = nullptr;                       // the merge runs as its own kernel below
     if (int rc = launch_attn_bf16<PL_DPAD, 1, 4, 32>(p, stream)) return rc;
     if (max_splits > 1) {
         const int threads = head_dim <= 64 ? 64 : 128;

@@ -49,7 +49,7 @@ __global__ void __launch_bounds__(128) attn_f32_kernel(AttnParams p) {
             const int n = kt + j;
             float kk = 0.f, vv = 0.f;
             if (n < it.key_hi) {
-                const int page = bt[n / p.ps];
+                const int page = bt[n / p.ps];      // (ps_shift is for the bfloat16 kernels)
                 if (page >= 0) {
                     const size_t base = ((((size_t)page * 2) * p.nkv + kvh) * p.ps + n % p.ps) * d + c;
                     kk = kv[base];
@@ -123,6 +123,8 @@ __global__ void __launch_bounds__(128) attn_f32_kernel(AttnParams p) {
 // split 0 merges all splits of every token of its request for one head.
 template <typename TO>
 __global__ void attn_combine_kernel(AttnParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
     if ((int)blockIdx.x >= p.n_work) return;
     const int4 w = p.work[blockIdx.x];
     if (w.x < 0 || w.z != 0 || w.w <= 1) return;
@@ -179,11 +181,10 @@ PL_EXPORT int pl_attention_combine(const AttnParams* params, int out_dtype, cuda
     if (int rc = pl_attn_check(p, "attention_combine")) return rc;
     const int threads = p.d <= 64 ? 64 : (p.d <= 128 ? 128 : 256);
     if (out_dtype == PL_F32)
-        attn_combine_kernel<float><<<dim3(p.n_work, p.nh), threads, 0, stream>>>(p);
+        PL_CUDA(launch_pdl(attn_combine_kernel<float>, dim3(p.n_work, p.nh), dim3(threads), 0, stream, p));
     else if (out_dtype == PL_BF16)
-        attn_combine_kernel<__nv_bfloat16><<<dim3(p.n_work, p.nh), threads, 0, stream>>>(p);
+        PL_CUDA(launch_pdl(attn_combine_kernel<__nv_bfloat16>, dim3(p.n_work, p.nh), dim3(threads), 0, stream, p));
     else
         return pl_fail("attention_combine: unknown dtype %d", out_dtype);
-    PL_LAUNCHED("attention_combine");
     return 0;
 }

@@ -7,6 +7,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define PL_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -66,6 +67,32 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
     return t;
 }
 
+// Programmatic dependent launch.  A kernel launched through launch_pdl may start
+// while the kernel in front of it on the stream is still running; it must call
+// pdl_wait() before it reads anything that kernel wrote and before it writes
+// anything at all.  pdl_launch_dependents() lets the kernel behind start early.
+// What a kernel does before pdl_wait() (fetching weights) overlaps the kernel in
+// front.  Launched the ordinary way, both calls do nothing.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    static const bool off = getenv("PAGED_LLM_B200_NO_PDL") != nullptr;     // ordinary launches, for measurements
+    cfg.numAttrs = off ? 0 : 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // Parameters of the paged attention kernels (both precisions).
 struct AttnParams {
     const void* q;          // [T, q_stride] rows; head h of token t at t*q_stride + h*d
@@ -83,4 +110,7 @@ struct AttnParams {
     int window;             // 0: none
     int is_small;           // items are (request, scratch base, split, splits), one tile per request
     float scale;
+    int ps_shift;           // log2(ps) if ps is a power of two, else -1
+    unsigned int* counters; // [requests * kv_heads] zeros, or null: the block of a request's kv head that
+                            // finishes last merges the splits itself (no separate merge kernel)
 };

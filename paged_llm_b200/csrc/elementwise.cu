@@ -13,15 +13,32 @@
 template <typename TW>
 __global__ void embedding_kernel(const TW* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
                                  int H, int V) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * H;
-    if (id < 0 || id >= V) {
-        for (int c = threadIdx.x; c < H; c += blockDim.x) o[c] = 0.f;
+    const bool valid = id >= 0 && id < V;
+    const TW* row = table + (size_t)(valid ? id : 0) * H;
+    if ((H & 3) == 0) {                                   // four elements per step, several steps in flight
+#pragma unroll 4
+        for (int c = threadIdx.x * 4; c < H; c += blockDim.x * 4) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (valid) {
+                if (sizeof(TW) == 4) {
+                    v = *reinterpret_cast<const float4*>(row + c);
+                } else {
+                    const uint2 raw = *reinterpret_cast<const uint2*>(row + c);
+                    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+                    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+                    v = make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+                }
+            }
+            *reinterpret_cast<float4*>(o + c) = v;
+        }
         return;
     }
-    const TW* row = table + (size_t)id * H;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) o[c] = to_float(row[c]);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) o[c] = valid ? to_float(row[c]) : 0.f;
 }
 
 PL_EXPORT int pl_embedding(const void* table, int table_dtype, const int* ids, float* out, int T, int H, int V,
@@ -30,24 +47,81 @@ PL_EXPORT int pl_embedding(const void* table, int table_dtype, const int* ids, f
     PL_REQUIRE(T > 0 && H > 0 && V > 0, "embedding: bad sizes T=%d H=%d V=%d", T, H, V);
     const int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == PL_F32)
-        embedding_kernel<float><<<T, threads, 0, stream>>>((const float*)table, ids, out, H, V);
+        PL_CUDA(launch_pdl(embedding_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)table, ids, out, H, V));
     else if (table_dtype == PL_BF16)
-        embedding_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, H, V);
+        PL_CUDA(launch_pdl(embedding_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream,
+                           (const __nv_bfloat16*)table, ids, out, H, V));
     else
         return pl_fail("embedding: unknown dtype %d", table_dtype);
-    PL_LAUNCHED("embedding");
     return 0;
 }
 
 // ------------------------------------------------------------------ RMSNorm
 // One block per row.  x is the float32 residual stream; with a branch, x += branch
 // is stored back first.  y = x * (1 / sqrt(mean(x^2) + eps)) * w, rounded once.
+template <typename T> struct Vec4 {};
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<__nv_bfloat16> {
+    static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+        return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 raw;
+        raw.x = *reinterpret_cast<uint32_t*>(&a);
+        raw.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = raw;
+    }
+};
+
+constexpr int NORM_VEC_ITERS = 4;     // a thread keeps up to 16 elements of its row in registers
+
 template <typename TB, typename TW, typename TO>
 __global__ void rmsnorm_kernel(float* __restrict__ x, const TB* __restrict__ branch, const TW* __restrict__ w,
-                               TO* __restrict__ y, int H, float eps, int use_smem) {
+                               TO* __restrict__ y, int H, float eps, int mode) {
     extern __shared__ float row_cache[];
     __shared__ float red[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t base = (size_t)blockIdx.x * H;
+    if (mode == 2) {
+        // H % 4 == 0 and H <= 16 * threads: the row lives in registers, all loads go out together
+        float4 v[NORM_VEC_ITERS];
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < NORM_VEC_ITERS; ++i) {
+            const int c = (threadIdx.x + i * blockDim.x) * 4;
+            v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c < H) {
+                v[i] = *reinterpret_cast<const float4*>(x + base + c);
+                if (branch != nullptr) {
+                    const float4 b = Vec4<TB>::load(branch + base + c);
+                    v[i].x += b.x; v[i].y += b.y; v[i].z += b.z; v[i].w += b.w;
+                    *reinterpret_cast<float4*>(x + base + c) = v[i];
+                }
+                ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+            }
+        }
+        ss = block_sum(ss, red);
+        const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+        for (int i = 0; i < NORM_VEC_ITERS; ++i) {
+            const int c = (threadIdx.x + i * blockDim.x) * 4;
+            if (c < H) {
+                const float4 ww = Vec4<TW>::load(w + c);
+                Vec4<TO>::store(y + base + c, make_float4(v[i].x * inv * ww.x, v[i].y * inv * ww.y,
+                                                          v[i].z * inv * ww.z, v[i].w * inv * ww.w));
+            }
+        }
+        return;
+    }
+    const int use_smem = mode == 1;
     float ss = 0.f;
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
         float v = x[base + c];
@@ -69,11 +143,13 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const TB* __restrict__ bra
 template <typename TB, typename TW, typename TO>
 static int launch_rmsnorm(float* x, const void* branch, const void* w, void* y, int rows, int H, float eps,
                           cudaStream_t stream) {
-    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-    const int use_smem = (size_t)H * 4 <= 40 * 1024;
-    rmsnorm_kernel<TB, TW, TO><<<rows, threads, use_smem ? (size_t)H * 4 : 0, stream>>>(
-        x, (const TB*)branch, (const TW*)w, (TO*)y, H, eps, use_smem);
-    PL_LAUNCHED("rmsnorm");
+    const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
+    const bool aligned = (H & 3) == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)y & 7) == 0 &&
+                         ((uintptr_t)w & 7) == 0 && ((uintptr_t)branch & 7) == 0;
+    int mode = (size_t)H * 4 <= 40 * 1024 ? 1 : 0;
+    if (aligned && H <= threads * 4 * NORM_VEC_ITERS) mode = 2;
+    PL_CUDA(launch_pdl(rmsnorm_kernel<TB, TW, TO>, dim3(rows), dim3(threads), mode == 1 ? (size_t)H * 4 : 0, stream, x,
+                       (const TB*)branch, (const TW*)w, (TO*)y, H, eps, mode));
     return 0;
 }
 
@@ -98,31 +174,48 @@ PL_EXPORT int pl_rmsnorm(float* x, const void* branch, int branch_dtype, const v
 
 // ------------------------------------------------------------------ SiLU * mul
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        const size_t r = i / I;
-        const int c = (int)(i - r * I);
-        const float g = to_float(gu[r * 2 * I + c]);
-        const float u = to_float(gu[r * 2 * I + I + c]);
-        const float s = g / (1.0f + expf(-g));
-        out[i] = from_float<T>(s * u);
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, int vec) {
+    const size_t r = blockIdx.y;
+    const T* g = gu + r * 2 * I;
+    const T* u = g + I;
+    T* o = out + r * I;
+    if (vec) {
+#pragma unroll 2
+        for (int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4; c < I; c += gridDim.x * blockDim.x * 4) {
+            const float4 gv = Vec4<T>::load(g + c), uv = Vec4<T>::load(u + c);
+            Vec4<T>::store(o + c, make_float4(gv.x / (1.0f + expf(-gv.x)) * uv.x, gv.y / (1.0f + expf(-gv.y)) * uv.y,
+                                              gv.z / (1.0f + expf(-gv.z)) * uv.z, gv.w / (1.0f + expf(-gv.w)) * uv.w));
+        }
+        return;
+    }
+    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < I; c += gridDim.x * blockDim.x) {
+        const float gg = to_float(g[c]);
+        o[c] = from_float<T>(gg / (1.0f + expf(-gg)) * to_float(u[c]));
     }
 }
 
 PL_EXPORT int pl_silu_mul(const void* gate_up, void* out, int dtype, int rows, int I, cudaStream_t stream) {
     if (rows == 0) return 0;
-    PL_REQUIRE(rows > 0 && I > 0, "silu_mul: bad sizes rows=%d I=%d", rows, I);
-    const size_t total = (size_t)rows * I;
+    PL_REQUIRE(rows > 0 && I > 0 && rows <= 65535 * 16, "silu_mul: bad sizes rows=%d I=%d", rows, I);
+    const int vec = (I & 3) == 0 && ((uintptr_t)gate_up & 15) == 0 && ((uintptr_t)out & 15) == 0;
     const int threads = 256;
-    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
-    if (dtype == PL_F32)
-        silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, I, total);
-    else if (dtype == PL_BF16)
-        silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up,
-                                                                      (__nv_bfloat16*)out, I, total);
-    else
-        return pl_fail("silu_mul: unknown dtype %d", dtype);
-    PL_LAUNCHED("silu_mul");
+    int bx = (I / (vec ? 4 : 1) + threads - 1) / threads;
+    if (bx > 8) bx = 8;
+    if (bx < 1) bx = 1;
+    for (int r0 = 0; r0 < rows; r0 += 65535) {
+        const int nr = rows - r0 < 65535 ? rows - r0 : 65535;
+        const size_t esz = dtype == PL_F32 ? 4 : 2;
+        const char* src = (const char*)gate_up + (size_t)r0 * 2 * I * esz;
+        char* dst = (char*)out + (size_t)r0 * I * esz;
+        if (dtype == PL_F32)
+            silu_mul_kernel<float><<<dim3(bx, nr), threads, 0, stream>>>((const float*)src, (float*)dst, I, vec);
+        else if (dtype == PL_BF16)
+            silu_mul_kernel<__nv_bfloat16><<<dim3(bx, nr), threads, 0, stream>>>((const __nv_bfloat16*)src,
+                                                                                  (__nv_bfloat16*)dst, I, vec);
+        else
+            return pl_fail("silu_mul: unknown dtype %d", dtype);
+        PL_LAUNCHED("silu_mul");
+    }
     return 0;
 }
 
@@ -130,9 +223,23 @@ PL_EXPORT int pl_silu_mul(const void* gate_up, void* out, int dtype, int rows, i
 template <typename T>
 __global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ idx, T* __restrict__ out, int H,
                                    int rows_in) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = idx[blockIdx.x];
+    const bool valid = r >= 0 && r < rows_in;
     T* o = out + (size_t)blockIdx.x * H;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) o[c] = (r >= 0 && r < rows_in) ? x[(size_t)r * H + c] : T(0);
+    const T* src = x + (size_t)(valid ? r : 0) * H;
+    constexpr int PER = 16 / sizeof(T);
+    if (H % PER == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0) {
+#pragma unroll 4
+        for (int c = threadIdx.x * PER; c < H; c += blockDim.x * PER) {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (valid) v = *reinterpret_cast<const uint4*>(src + c);
+            *reinterpret_cast<uint4*>(o + c) = v;
+        }
+        return;
+    }
+    for (int c = threadIdx.x; c < H; c += blockDim.x) o[c] = valid ? src[c] : T(0);
 }
 
 PL_EXPORT int pl_gather_rows(const void* x, const int* idx, void* out, int dtype, int n, int H, int rows_in,
@@ -140,13 +247,13 @@ PL_EXPORT int pl_gather_rows(const void* x, const int* idx, void* out, int dtype
     if (n == 0) return 0;
     PL_REQUIRE(n > 0 && H > 0, "gather_rows: bad sizes n=%d H=%d", n, H);
     if (dtype == PL_F32)
-        gather_rows_kernel<float><<<n, 128, 0, stream>>>((const float*)x, idx, (float*)out, H, rows_in);
+        PL_CUDA(launch_pdl(gather_rows_kernel<float>, dim3(n), dim3(128), 0, stream, (const float*)x, idx, (float*)out, H,
+                           rows_in));
     else if (dtype == PL_BF16)
-        gather_rows_kernel<__nv_bfloat16><<<n, 128, 0, stream>>>((const __nv_bfloat16*)x, idx, (__nv_bfloat16*)out, H,
-                                                                 rows_in);
+        PL_CUDA(launch_pdl(gather_rows_kernel<__nv_bfloat16>, dim3(n), dim3(128), 0, stream, (const __nv_bfloat16*)x,
+                           idx, (__nv_bfloat16*)out, H, rows_in));
     else
         return pl_fail("gather_rows: unknown dtype %d", dtype);
-    PL_LAUNCHED("gather_rows");
     return 0;
 }
 
@@ -177,7 +284,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
                                      int table_len, int rotary_dim, int interleaved, const int* __restrict__ positions,
                                      const int* __restrict__ token_seq, const int* __restrict__ block_table,
                                      int bt_stride, T* __restrict__ kv, int num_pages, int nh, int nkv, int d, int ps,
-                                     int write) {
+                                     int write, int vec) {
     const int t = blockIdx.x;
     const int s = token_seq[t];
     if (s < 0) return;
@@ -186,16 +293,33 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
     const int half = rotary_dim / 2;
     if (half > 0 && pos >= 0 && pos < table_len) {
         const float2* cs = table + (size_t)pos * half;
-        const int pairs = (nh + nkv) * half;
-        for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
-            const int h = i / half, j = i - h * half;
-            T* head = row + h * d;
-            const int ia = interleaved ? 2 * j : j;
-            const int ib = interleaved ? 2 * j + 1 : j + half;
-            const float a = to_float(head[ia]), b = to_float(head[ib]);
-            const float2 c = cs[j];
-            head[ia] = from_float<T>(a * c.x - b * c.y);
-            head[ib] = from_float<T>(b * c.x + a * c.y);
+        if (vec && !interleaved) {
+            // four pairs per step: elements j..j+3 of the first half with their partners
+            const int quads = (nh + nkv) * (half / 4);
+#pragma unroll 2
+            for (int i = threadIdx.x; i < quads; i += blockDim.x) {
+                const int h = i / (half / 4), j = (i - h * (half / 4)) * 4;
+                T* head = row + h * d;
+                const float4 a = Vec4<T>::load(head + j), b = Vec4<T>::load(head + j + half);
+                const float4 c01 = *reinterpret_cast<const float4*>(cs + j);
+                const float4 c23 = *reinterpret_cast<const float4*>(cs + j + 2);
+                Vec4<T>::store(head + j, make_float4(a.x * c01.x - b.x * c01.y, a.y * c01.z - b.y * c01.w,
+                                                     a.z * c23.x - b.z * c23.y, a.w * c23.z - b.w * c23.w));
+                Vec4<T>::store(head + j + half, make_float4(b.x * c01.x + a.x * c01.y, b.y * c01.z + a.y * c01.w,
+                                                            b.z * c23.x + a.z * c23.y, b.w * c23.z + a.w * c23.w));
+            }
+        } else {
+            const int pairs = (nh + nkv) * half;
+            for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+                const int h = i / half, j = i - h * half;
+                T* head = row + h * d;
+                const int ia = interleaved ? 2 * j : j;
+                const int ib = interleaved ? 2 * j + 1 : j + half;
+                const float a = to_float(head[ia]), b = to_float(head[ib]);
+                const float2 c = cs[j];
+                head[ia] = from_float<T>(a * c.x - b * c.y);
+                head[ib] = from_float<T>(b * c.x + a * c.y);
+            }
         }
     }
     if (!write) return;
@@ -205,6 +329,18 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
     const int off = pos % ps;
     const T* k = row + nh * d;
     const T* v = row + (nh + nkv) * d;
+    if (vec) {
+        constexpr int PER = 16 / sizeof(T);
+        const int per_head = d / PER;
+        for (int i = threadIdx.x; i < nkv * per_head; i += blockDim.x) {
+            const int h = i / per_head, c = (i - h * per_head) * PER;
+            const size_t kdst = ((((size_t)page * 2 + 0) * nkv + h) * ps + off) * d + c;
+            const size_t vdst = ((((size_t)page * 2 + 1) * nkv + h) * ps + off) * d + c;
+            *reinterpret_cast<uint4*>(kv + kdst) = *reinterpret_cast<const uint4*>(k + h * d + c);
+            *reinterpret_cast<uint4*>(kv + vdst) = *reinterpret_cast<const uint4*>(v + h * d + c);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < nkv * d; i += blockDim.x) {
         const int h = i / d, c = i - h * d;
         const size_t kdst = ((((size_t)page * 2 + 0) * nkv + h) * ps + off) * d + c;
@@ -224,15 +360,19 @@ PL_EXPORT int pl_rope_kv_write(void* qkv, int dtype, int T, int row_stride, cons
                rotary_dim, d);
     PL_REQUIRE(row_stride >= (nh + 2 * nkv) * d, "rope_kv_write: row stride %d too small", row_stride);
     const int threads = 128;
+    const int per16 = dtype == PL_F32 ? 4 : 8;
+    // 16-byte path: heads, halves and rows start on 16-byte boundaries
+    const int vec = d % per16 == 0 && row_stride % per16 == 0 && (rotary_dim / 2) % per16 == 0 &&
+                    (((uintptr_t)qkv | (uintptr_t)kv | (uintptr_t)table) & 15) == 0;
     if (dtype == PL_F32)
         rope_kv_write_kernel<float><<<T, threads, 0, stream>>>((float*)qkv, row_stride, (const float2*)table, table_len,
                                                                rotary_dim, interleaved, positions, token_seq,
                                                                block_table, bt_stride, (float*)kv, num_pages, nh, nkv,
-                                                               d, ps, write);
+                                                               d, ps, write, vec);
     else if (dtype == PL_BF16)
         rope_kv_write_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(
             (__nv_bfloat16*)qkv, row_stride, (const float2*)table, table_len, rotary_dim, interleaved, positions,
-            token_seq, block_table, bt_stride, (__nv_bfloat16*)kv, num_pages, nh, nkv, d, ps, write);
+            token_seq, block_table, bt_stride, (__nv_bfloat16*)kv, num_pages, nh, nkv, d, ps, write, vec);
     else
         return pl_fail("rope_kv_write: unknown dtype %d", dtype);
     PL_LAUNCHED("rope_kv_write");

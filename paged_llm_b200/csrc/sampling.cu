@@ -65,23 +65,68 @@ __device__ MaxIdx block_argmax(MaxIdx x, MaxIdx* red) {
     return t;
 }
 
-__global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, size_t row_stride) {
+// A row is cut into ARGMAX_PARTS parts, one block each; a block packs its best (value, index)
+// into 64 bits (order-preserving image of the float in the high word, ~index in the low word,
+// so that of equal values the first index wins) and merges it with atomicMax.  The block of a
+// row that finishes last unpacks the winner and leaves the cell and the counter zero.
+constexpr int ARGMAX_PARTS = 16;
+
+__global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, size_t row_stride,
+                              unsigned long long* __restrict__ cells, unsigned int* __restrict__ counters) {
     __shared__ MaxIdx red[32];
-    const float* row = logits + (size_t)blockIdx.x * row_stride;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x, part = blockIdx.y;
+    const float* row = logits + (size_t)r * row_stride;
+    const int per = ((V + ARGMAX_PARTS - 1) / ARGMAX_PARTS + 3) & ~3;
+    const int lo = part * per, hi = min(V, lo + per);
     MaxIdx best{-INFINITY, 0x7fffffff};
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float v = row[i];
-        if (v > best.v || (v == best.v && i < best.i) || best.i == 0x7fffffff) best = MaxIdx{v, i};
+    if ((row_stride & 3) == 0 && ((uintptr_t)logits & 15) == 0) {
+#pragma unroll 2
+        for (int i = lo + threadIdx.x * 4; i < hi; i += blockDim.x * 4) {
+            if (i + 3 < hi) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(row + i));
+                const float vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (vv[e] > best.v || best.i == 0x7fffffff) best = MaxIdx{vv[e], i + e};
+            } else {
+                for (int e = 0; i + e < hi; ++e) {
+                    const float v = __ldcg(row + i + e);
+                    if (v > best.v || best.i == 0x7fffffff) best = MaxIdx{v, i + e};
+                }
+            }
+        }
+    } else {
+        for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+            const float v = __ldcg(row + i);
+            if (v > best.v || best.i == 0x7fffffff) best = MaxIdx{v, i};
+        }
     }
     best = block_argmax(best, red);
-    if (threadIdx.x == 0) out[blockIdx.x] = best.i == 0x7fffffff ? 0 : best.i;
+    if (threadIdx.x == 0) {
+        if (best.i != 0x7fffffff) {
+            const unsigned long long packed =
+                ((unsigned long long)ordered_key(best.v) << 32) | (unsigned long long)(0xffffffffu - (unsigned)best.i);
+            atomicMax(&cells[r], packed);
+        }
+        __threadfence();
+        if (atomicAdd(&counters[r], 1u) == ARGMAX_PARTS - 1) {
+            __threadfence();
+            const unsigned long long w = atomicExch(&cells[r], 0ull);
+            out[r] = w == 0ull ? 0 : (int)(0xffffffffu - (unsigned)(w & 0xffffffffull));
+            counters[r] = 0u;
+        }
+    }
 }
 
-PL_EXPORT int pl_argmax(const float* logits, int* out, int rows, int V, long long row_stride, cudaStream_t stream) {
+// cells, counters: [rows] each, zero before the first call (the kernel leaves them zero).
+PL_EXPORT int pl_argmax(const float* logits, int* out, int rows, int V, long long row_stride,
+                        unsigned long long* cells, unsigned int* counters, cudaStream_t stream) {
     if (rows == 0) return 0;
     PL_REQUIRE(rows > 0 && V > 0 && row_stride >= V, "argmax: bad sizes rows=%d V=%d", rows, V);
-    argmax_kernel<<<rows, 512, 0, stream>>>(logits, out, V, (size_t)row_stride);
-    PL_LAUNCHED("argmax");
+    PL_CUDA(launch_pdl(argmax_kernel, dim3(rows, ARGMAX_PARTS), dim3(256), 0, stream, logits, out, V, (size_t)row_stride,
+                       cells, counters));
     return 0;
 }
 

@@ -28,13 +28,24 @@ class KernelError(RuntimeError):
     pass
 
 
+class LazyNorm:
+    """RMSNorm(x) * weight that no kernel has formed yet: the product that comes next
+    normalises while it loads.  `part` holds the sums of squares of x that the product
+    in front left (per 16 columns and token)."""
+
+    def __init__(self, x: torch.Tensor, part: torch.Tensor, weight: torch.Tensor, eps: float):
+        self.x, self.part, self.weight, self.eps = x, part, weight, eps
+        self.shape = x.shape
+        self.dtype = torch.bfloat16
+
+
 class AttnParams(ctypes.Structure):
     _fields_ = [
         ("q", c_void_p), ("kv", c_void_p), ("out", c_void_p), ("block_table", c_void_p), ("cu_q", c_void_p),
         ("k_lens", c_void_p), ("work", c_void_p), ("scratch", c_void_p), ("scratch_floats", c_longlong),
         ("q_stride", c_int), ("out_stride", c_int), ("bt_stride", c_int), ("n_work", c_int), ("max_splits", c_int),
         ("nh", c_int), ("nkv", c_int), ("d", c_int), ("ps", c_int), ("window", c_int), ("is_small", c_int),
-        ("scale", c_float),
+        ("scale", c_float), ("ps_shift", c_int), ("counters", c_void_p),
     ]
 
 
@@ -86,6 +97,13 @@ class CudaOps:
         self._attn_lib = None
         self._attn_fn = None
         self.launches = 0                 # kernels of this package launched so far
+        self.use_skinny = True            # few-token products on this package's weight-streaming kernel
+        self._argmax_ws = None            # (packed winners, arrival counters) of the multi-block argmax
+        self._argmax_keep: list = []
+        self._attn_counters = None        # arrival counters of the split merge inside the attention kernel
+        self._attn_counters_keep: list = []
+        self._norm_part = None            # sums of squares that an adding product leaves for the next one
+        self._norm_part_keep: list = []
         # the library matrix products must not reduce in bfloat16
         torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 
@@ -154,12 +172,39 @@ class CudaOps:
         return out
 
     # ---- matrix products ---------------------------------------------------------
-    def linear(self, h: torch.Tensor, w: torch.Tensor, out_float32: bool = False) -> torch.Tensor:
-        """h [M, K] @ w[N, K]^T.  float32: this package's CUDA-core kernel;
-        bfloat16: the library product with float32 accumulation."""
+    def materialize(self, h):
+        """A tensor for `h`, which may be a `LazyNorm`."""
+        if isinstance(h, LazyNorm):
+            return self.rms_norm(h.x, h.weight, h.eps)
+        return h
+
+    def _norm_args(self, h):
+        """(X pointer, row stride, partial sums, norm weight, its dtype code, eps) for a product."""
+        if isinstance(h, LazyNorm):
+            return (self._p(h.x), h.x.shape[1], self._p(h.part), self._p(h.weight), self._code(h.weight), c_float(h.eps))
+        return (self._p(h), h.shape[1], c_void_p(0), c_void_p(0), 0, c_float(0.0))
+
+    def _skinny_ok(self, h, N: int) -> bool:
+        """Few tokens: the weight-streaming kernel of this package instead of the library."""
+        M, K = h.shape
+        return self.use_skinny and h.dtype == torch.bfloat16 and 1 <= M <= 16 and K >= 32 and K % 32 == 0
+
+    def linear(self, h, w: torch.Tensor, out_float32: bool = False) -> torch.Tensor:
+        """h [M, K] @ w[N, K]^T.  float32: this package's CUDA-core kernel; bfloat16 with few
+        tokens: this package's weight-streaming kernel; else the library product with
+        float32 accumulation.  `h` may be a `LazyNorm`."""
         M, K = h.shape
         N = w.shape[0]
-        assert w.shape[1] == K and h.is_contiguous() and w.is_contiguous()
+        assert w.shape[1] == K and w.is_contiguous()
+        if self._skinny_ok(h, N) and w.dtype == torch.bfloat16:
+            x, ldx, part, nw, nwc, eps = self._norm_args(h)
+            out = torch.empty((M, N), dtype=torch.float32 if out_float32 else torch.bfloat16, device=self.device)
+            _check(self.core, self.core.pl_gemm_skinny(x, ldx, self._p(w), self._p(out), N, M, N, K,
+                                                       1 if out_float32 else 0, part, nw, nwc, eps, self._stream))
+            self.launches += 1
+            return out
+        h = self.materialize(h)
+        assert h.is_contiguous()
         if h.dtype == torch.float32:
             assert w.dtype == torch.float32
             out = torch.empty((M, N), dtype=torch.float32, device=self.device)
@@ -171,6 +216,60 @@ class CudaOps:
         if out_float32:
             return torch.mm(h, w.t(), out_dtype=torch.float32)
         return torch.nn.functional.linear(h, w)
+
+    def linear_add_rms_norm(self, h, w, x, norm_w, eps):
+        """x += h @ w^T (float32 stream, in place), then RMSNorm(x) * norm_w.  With few tokens
+        the product's epilogue adds and the result is a `LazyNorm` that the next product
+        forms while loading; else the product is followed by the fused sum+norm kernel."""
+        M, K = h.shape
+        N = w.shape[0]
+        if not isinstance(h, LazyNorm) and self._skinny_ok(h, N) and N % 16 == 0 and N % 32 == 0:
+            assert x.dtype == torch.float32 and x.is_contiguous() and x.shape == (M, N) and h.is_contiguous()
+            if self._norm_part is None or self._norm_part.numel() < N:
+                self._norm_part_keep.append(self._norm_part)        # captured graphs hold the old address
+                self._norm_part = torch.zeros(max(N, 1 << 16), dtype=torch.float32, device=self.device)
+            _check(self.core, self.core.pl_gemm_skinny_add(self._p(h), K, self._p(w), self._p(x), M, N, K,
+                                                           self._p(self._norm_part), self._stream))
+            self.launches += 1
+            return LazyNorm(x, self._norm_part, norm_w, eps)
+        return self.add_rms_norm(x, self.linear(h, w), norm_w, eps)
+
+    def gated_silu_linear(self, h, w_gate_up: torch.Tensor) -> torch.Tensor:
+        """silu(h Wg^T) * (h Wu^T) for W = [Wg; Wu]: one kernel for few tokens, else the
+        product followed by the activation kernel."""
+        M, K = h.shape
+        I = w_gate_up.shape[0] // 2
+        if self._skinny_ok(h, 2 * I):
+            x, ldx, part, nw, nwc, eps = self._norm_args(h)
+            out = torch.empty((M, I), dtype=torch.bfloat16, device=self.device)
+            _check(self.core, self.core.pl_gemm_skinny_silu(x, ldx, self._p(w_gate_up), self._p(out), I, M, I, K,
+                                                            part, nw, nwc, eps, self._stream))
+            self.launches += 1
+            return out
+        return self.silu_mul(self.linear(h, w_gate_up))
+
+    def qkv_rope_write(self, h, w_qkv, nh, nkv, d, position, ctx, kv, block_table, write=True) -> torch.Tensor:
+        """The fused q/k/v projection with rotary positions applied to q and k and k, v
+        written to the cache.  Returns the [T, (nh + 2 nkv) d] buffer whose first nh*d
+        columns are the rotated queries."""
+        M, K = h.shape
+        N = (nh + 2 * nkv) * d
+        fusable = (self._skinny_ok(h, N) and position is not None and position.pairing == "half"
+                   and position.rotary_dim == d and M == ctx.num_tokens)
+        if not fusable:
+            qkv = self.linear(h, w_qkv)
+            self.rope_kv_write(qkv, nh, nkv, d, position, ctx, kv, block_table, write=write)
+            return qkv
+        x, ldx, part, nw, nwc, eps = self._norm_args(h)
+        qkv = torch.empty((M, N), dtype=torch.bfloat16, device=self.device)
+        assert kv.dtype == torch.bfloat16 and kv.is_contiguous()
+        _check(self.core, self.core.pl_gemm_skinny_rope(
+            x, ldx, self._p(w_qkv), self._p(qkv), N, M, K, nh, nkv, d, self._p(position.table),
+            position.table.shape[0], self._p(ctx.positions), self._p(ctx.token_seq), self._p(block_table),
+            block_table.shape[1], self._p(kv), kv.shape[0], kv.shape[3], 1 if write else 0, part, nw, nwc, eps,
+            self._stream))
+        self.launches += 1
+        return qkv
 
     # ---- positions ---------------------------------------------------------------
     def rope_table(self, inv_freq: torch.Tensor, max_positions: int) -> torch.Tensor:
@@ -232,6 +331,9 @@ class CudaOps:
         p.q_stride, p.out_stride, p.bt_stride = qkv.shape[1], nh * d, block_table.shape[1]
         p.nh, p.nkv, p.d, p.ps = nh, nkv, d, kv.shape[3]
         p.window, p.scale, p.max_splits = int(window or 0), float(scale), plan.max_splits
+        ps = kv.shape[3]
+        p.ps_shift = ps.bit_length() - 1 if ps & (ps - 1) == 0 else -1
+        p.counters = 0
         bf16 = qkv.dtype == torch.bfloat16
         if bf16:
             lib, fn = self._attention_bf16(d)
@@ -242,9 +344,17 @@ class CudaOps:
             scratch = self._scratch_for(floats)
             p.scratch, p.scratch_floats = scratch.data_ptr(), scratch.numel()
             p.work, p.n_work, p.is_small = plan.small.data_ptr(), plan.n_small, 1
+            fused_merge = bf16 and plan.max_splits > 1
+            if fused_merge:
+                need = ctx.num_seqs * nkv
+                if self._attn_counters is None or self._attn_counters.numel() < need:
+                    self._attn_counters_keep.append(self._attn_counters)    # captured graphs hold the old address
+                    self._attn_counters = torch.zeros(max(need, 4096), dtype=torch.int32, device=self.device)
+                p.counters = self._attn_counters.data_ptr()
             _check(lib, fn(ctypes.byref(p), self._stream))
             self.launches += 1
-            if plan.max_splits > 1:
+            p.counters = 0
+            if plan.max_splits > 1 and not fused_merge:
                 _check(self.core, self.core.pl_attention_combine(ctypes.byref(p), self._code(out), self._stream))
                 self.launches += 1
         if plan.n_large:
@@ -269,8 +379,13 @@ class CudaOps:
         rows, V = logits.shape
         assert logits.dtype == torch.float32 and logits.stride(1) == 1
         out = torch.empty(rows, dtype=torch.int32, device=self.device)
+        if self._argmax_ws is None or self._argmax_ws[0].numel() < rows:
+            self._argmax_keep.append(self._argmax_ws)               # captured graphs hold the old addresses
+            self._argmax_ws = (torch.zeros(max(rows, 1024), dtype=torch.int64, device=self.device),
+                               torch.zeros(max(rows, 1024), dtype=torch.int32, device=self.device))
+        cells, counters = self._argmax_ws
         _check(self.core, self.core.pl_argmax(self._p(logits), self._p(out), rows, V, c_longlong(logits.stride(0)),
-                                              self._stream))
+                                              self._p(cells), self._p(counters), self._stream))
         self.launches += 1
         return out
 

@@ -12,8 +12,8 @@ from dataclasses import dataclass
 
 import torch
 
-from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, FixedState, ModelSpec, PagedKV,
-                          PartSpec, TensorSpec, make_part)
+from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, FixedState, LazyLinear, ModelSpec,
+                          PagedKV, PartSpec, TensorSpec, make_part)
 from ..parts.embedding import LMHead, TokenEmbedding
 
 
@@ -111,8 +111,15 @@ class CausalLM:
             return None
         ops = ctx.ops
         rows = ops.gather_rows(x, ctx.logits_indices)
-        rows_pending = ops.gather_rows(pending, ctx.logits_indices) if pending is not None else None
+        if pending is None:
+            rows_pending = None
+        elif isinstance(pending, LazyLinear):
+            rows_pending = pending.rows(ops, ctx.logits_indices)     # the last projection runs on the wanted rows only
+        else:
+            rows_pending = ops.gather_rows(pending, ctx.logits_indices)
         h = self.final_norm.add_forward(rows, rows_pending, ctx)
+        if not self.head.accepts_lazy_input:
+            h = ops.materialize(h)
         return self.head.forward(h, ctx)
 
 

@@ -2,14 +2,14 @@
 built-in ones."""
 
 from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, Block, FeedForward, FixedState,
-                   LayerSpec, Mixer, ModelSpec, Norm, PagedKV, Part, PartSpec, PositionEncoding, ScheduleEntry,
+                   LayerSpec, LazyLinear, materialize, Mixer, ModelSpec, Norm, PagedKV, Part, PartSpec, PositionEncoding, ScheduleEntry,
                    TensorSpec, make_part, register_block, register_feed_forward, register_mixer, register_norm,
                    register_position_encoding)
 from . import attention, block, embedding, mlp, norm, rope  # noqa: F401  (registration)
 
 __all__ = [
     "BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITION_ENCODINGS", "Block", "FeedForward", "FixedState",
-    "LayerSpec", "Mixer", "ModelSpec", "Norm", "PagedKV", "Part", "PartSpec", "PositionEncoding", "ScheduleEntry",
+    "LayerSpec", "LazyLinear", "materialize", "Mixer", "ModelSpec", "Norm", "PagedKV", "Part", "PartSpec", "PositionEncoding", "ScheduleEntry",
     "TensorSpec", "make_part", "register_block", "register_feed_forward", "register_mixer", "register_norm",
     "register_position_encoding",
 ]

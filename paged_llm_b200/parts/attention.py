@@ -16,11 +16,13 @@ from __future__ import annotations
 
 import torch
 
-from .base import Mixer, PagedKV, TensorSpec, register_mixer
+from .base import LazyLinear, Mixer, PagedKV, TensorSpec, register_mixer
 
 
 @register_mixer("paged_attention")
 class PagedAttention(Mixer):
+    accepts_lazy_input = True
+
     def __init__(self, weights: dict[str, str], hidden_size: int, num_heads: int, num_kv_heads: int,
                  head_dim: int, scale: float | None = None, window: int | None = None, position=None):
         if num_heads % num_kv_heads:
@@ -58,10 +60,9 @@ class PagedAttention(Mixer):
 
     def forward(self, h, ctx, cache):
         ops = ctx.ops
-        qkv = ops.linear(h, self.w_qkv)
         block_table = ctx.block_tables[cache.group]
-        ops.rope_kv_write(qkv, self.num_heads, self.num_kv_heads, self.head_dim, self.position,
-                          ctx, cache.kv, block_table, write=cache.owner)
+        qkv = ops.qkv_rope_write(h, self.w_qkv, self.num_heads, self.num_kv_heads, self.head_dim, self.position,
+                                 ctx, cache.kv, block_table, write=cache.owner)
         o = ops.paged_attention(qkv, self.num_heads, self.num_kv_heads, self.head_dim, cache.kv,
                                 block_table, ctx, self.scale, self.window)
-        return ops.linear(o, self.w_o)
+        return LazyLinear(o, self.w_o)

@@ -107,10 +107,41 @@ class FixedState:
     dtype: torch.dtype = torch.float32
 
 
+# --------------------------------------------------------------------------- lazy branch outputs
+
+@dataclass
+class LazyLinear:
+    """A branch output `input @ weight^T` that has not been computed yet.
+
+    A mixer or feed-forward whose last operation is a projection may return this
+    instead of a tensor.  The norm that consumes the branch can then let one
+    kernel do projection + residual sum + normalisation; anything else calls
+    `materialize`.  A part that returns a plain tensor works everywhere too."""
+
+    input: torch.Tensor
+    weight: torch.Tensor
+
+    def materialize(self, ops) -> torch.Tensor:
+        return ops.linear(self.input, self.weight)
+
+    def rows(self, ops, idx: torch.Tensor) -> "LazyLinear":
+        """The same branch for the rows `idx` only."""
+        return LazyLinear(ops.gather_rows(self.input, idx), self.weight)
+
+
+def materialize(branch, ops):
+    return branch.materialize(ops) if isinstance(branch, LazyLinear) else branch
+
+
 # --------------------------------------------------------------------------- interfaces
 
 class Part:
     """Common to all parts: which tensors it wants and how it takes them."""
+
+    # True if `forward` hands its input straight to the kernel library's products, which
+    # also take a normalisation that has not been carried out yet (ops.materialize turns
+    # one into a tensor).  Parts that look at their input themselves leave this False.
+    accepts_lazy_input = False
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
         """Checkpoint tensor name -> expectation."""
@@ -130,9 +161,9 @@ class Norm(Part):
         """Normalise rows of `x` (residual stream dtype) -> compute dtype."""
         raise NotImplementedError
 
-    def add_forward(self, x: torch.Tensor, branch: torch.Tensor | None, ctx) -> torch.Tensor:
+    def add_forward(self, x: torch.Tensor, branch, ctx) -> torch.Tensor:
         """x += branch (in place, in the residual dtype), then normalise.  With
-        branch None this is `forward`."""
+        branch None this is `forward`.  `branch` is a tensor or a `LazyLinear`."""
         raise NotImplementedError
 
 
@@ -152,7 +183,8 @@ class Mixer(Part):
     def forward(self, h: torch.Tensor, ctx, cache) -> torch.Tensor:
         """h: [T, hidden] in the compute dtype, token-major over all requests of
         the step.  `cache` is a `LayerCache` view (cache/storage.py) for this run
-        of the layer, or None if the mixer keeps nothing.  Returns [T, hidden]."""
+        of the layer, or None if the mixer keeps nothing.  Returns [T, hidden]
+        (a tensor, or a `LazyLinear` if the last operation is a projection)."""
         raise NotImplementedError
 
 

@@ -13,7 +13,11 @@ class PreNormBlock(Block):
 
     def forward(self, x, pending, ctx, cache):
         h = self.norms["input"].add_forward(x, pending, ctx)
+        if not self.mixer.accepts_lazy_input:
+            h = ctx.ops.materialize(h)
         a = self.mixer.forward(h, ctx, cache)
         h = self.norms["post_mixer"].add_forward(x, a, ctx)
+        if not self.feed_forward.accepts_lazy_input:
+            h = ctx.ops.materialize(h)
         f = self.feed_forward.forward(h, ctx)
         return x, f

@@ -28,6 +28,8 @@ class TokenEmbedding(Part):
 
 
 class LMHead(Part):
+    accepts_lazy_input = True
+
     def __init__(self, weights: dict[str, str], vocab_size: int, hidden_size: int, tied_to: str | None = None):
         self.vocab_size, self.hidden_size = vocab_size, hidden_size
         self.name = weights["weight"]

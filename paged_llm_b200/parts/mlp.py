@@ -6,11 +6,13 @@ from __future__ import annotations
 
 import torch
 
-from .base import FeedForward, TensorSpec, register_feed_forward
+from .base import FeedForward, LazyLinear, TensorSpec, register_feed_forward
 
 
 @register_feed_forward("gated_mlp")
 class GatedMLP(FeedForward):
+    accepts_lazy_input = True
+
     def __init__(self, weights: dict[str, str], hidden_size: int, intermediate_size: int, activation: str = "silu"):
         if activation != "silu":
             raise ValueError(f"activation {activation!r} is not implemented (silu only)")
@@ -36,5 +38,4 @@ class GatedMLP(FeedForward):
 
     def forward(self, h, ctx):
         ops = ctx.ops
-        gate_up = ops.linear(h, self.w_gate_up)
-        return ops.linear(ops.silu_mul(gate_up), self.w_down)
+        return LazyLinear(ops.gated_silu_linear(h, self.w_gate_up), self.w_down)

@@ -4,7 +4,7 @@ pagedllm/model/llama.py:74-83)."""
 
 from __future__ import annotations
 
-from .base import Norm, TensorSpec, register_norm
+from .base import LazyLinear, Norm, TensorSpec, register_norm
 
 
 @register_norm("rms_norm")
@@ -29,4 +29,6 @@ class RMSNorm(Norm):
     def add_forward(self, x, branch, ctx):
         if branch is None:
             return ctx.ops.rms_norm(x, self.weight, self.eps)
+        if isinstance(branch, LazyLinear):
+            return ctx.ops.linear_add_rms_norm(branch.input, branch.weight, x, self.weight, self.eps)
         return ctx.ops.add_rms_norm(x, branch, self.weight, self.eps)

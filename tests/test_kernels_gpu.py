@@ -326,3 +326,88 @@ def test_sampling_distribution(ops):
         want = plain_llama.sampling_distribution(row[0].cpu(), temp, k if k else -1, p).numpy()
         assert (freq[want == 0] == 0).all(), "a filtered token was drawn"
         assert np.abs(freq - want).max() < 0.015
+
+
+# ---------------------------------------------------------------------------- few-token products
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(2560, 2048), (509, 96), (100, 64), (2048, 5632), (37, 160), (130, 8192), (64, 14336)])
+def test_skinny_linear(ops, M, N, K):
+    a, b = randn(M, K, seed=20, dtype=torch.bfloat16), randn(N, K, seed=21, dtype=torch.bfloat16, std=0.1)
+    want = a.float() @ b.float().T
+    got = ops.linear(a, b)
+    assert got.dtype == torch.bfloat16
+    torch.testing.assert_close(got.float(), want, atol=2e-2 * math.sqrt(K) * 0.1, rtol=1e-2)
+    full = ops.linear(a, b, out_float32=True)
+    torch.testing.assert_close(full, want, atol=1e-4 * math.sqrt(K), rtol=1e-4)
+    one = ops.linear(a[M // 2:M // 2 + 1].contiguous(), b, out_float32=True)
+    assert torch.equal(one[0], full[M // 2]), "a token's product must not depend on the tokens beside it"
+    assert ops.core.pl_gemm_skinny_timeouts() == 0, "a bounded wait inside the kernel gave up"
+
+
+@pytest.mark.parametrize("M", [1, 8, 13])
+@pytest.mark.parametrize("I,K", [(5632, 2048), (172, 64), (100, 96), (7, 32)])
+def test_skinny_gated_silu(ops, M, I, K):
+    h, w = randn(M, K, seed=22, dtype=torch.bfloat16), randn(2 * I, K, seed=23, dtype=torch.bfloat16, std=0.1)
+    got = ops.gated_silu_linear(h, w)
+    ops.use_skinny = False
+    try:
+        want = ops.gated_silu_linear(h, w)
+    finally:
+        ops.use_skinny = True
+    g, u = (h.float() @ w[:I].float().T), (h.float() @ w[I:].float().T)
+    torch.testing.assert_close(got.float(), g * torch.sigmoid(g) * u, atol=3e-2, rtol=3e-2)
+    torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("nh,nkv,d", [(32, 4, 64), (4, 2, 16), (3, 3, 32), (6, 2, 48)])
+@pytest.mark.parametrize("q_lens,k_lens", [([1, 1, 1], [5, 300, 31]), ([5, 1, 7], [5, 300, 31]), ([1], [1])])
+def test_skinny_qkv_rope_write_equals_the_separate_kernels(ops, nh, nkv, d, q_lens, k_lens):
+    from paged_llm_b200.parts.rope import RotaryEncoding
+    ops.set_compute_dtype(torch.bfloat16)
+    rope = RotaryEncoding({}, head_dim=d, theta=10000.0)
+    rope.prepare(512, "cuda", ops)
+    H, ps, pages = 96, 8, 64
+    ctx = make_ctx(ops, q_lens, k_lens, nh, nkv, None)
+    T = sum(q_lens)
+    h = randn(T, H, seed=24, dtype=torch.bfloat16)
+    w = randn((nh + 2 * nkv) * d, H, seed=25, dtype=torch.bfloat16, std=0.2)
+    bt = torch.stack([torch.randperm(pages, generator=torch.Generator().manual_seed(s))[:40] for s in range(len(q_lens))]).int().cuda()
+    kv_a = torch.full((pages, 2, nkv, ps, d), 7.0, dtype=torch.bfloat16, device="cuda")
+    kv_b = kv_a.clone()
+    fused = ops.qkv_rope_write(h, w, nh, nkv, d, rope, ctx, kv_a, bt, write=True)
+    ops.use_skinny = False
+    try:
+        plain = ops.qkv_rope_write(h, w, nh, nkv, d, rope, ctx, kv_b, bt, write=True)
+    finally:
+        ops.use_skinny = True
+    torch.testing.assert_close(fused[:, :nh * d].float(), plain[:, :nh * d].float(), atol=3e-2, rtol=3e-2)
+    torch.testing.assert_close(kv_a.float(), kv_b.float(), atol=3e-2, rtol=3e-2)
+    assert ((kv_a == 7.0) == (kv_b == 7.0)).all(), "the fused kernel must write exactly the same slots"
+
+
+@pytest.mark.parametrize("M", [1, 8, 11])
+@pytest.mark.parametrize("N,K,wdtype", [(2048, 2048, torch.bfloat16), (2048, 5632, torch.bfloat16), (96, 256, torch.float32),
+                                        (128, 64, torch.float32)])
+def test_skinny_add_then_normalising_products(ops, M, N, K, wdtype):
+    """Projection + residual sum in one kernel, the norm carried out by the products that
+    follow while they load; three rounds in a row on the same workspace."""
+    from paged_llm_b200.kernels.ops import LazyNorm
+    ops.set_compute_dtype(torch.bfloat16)
+    for rep in range(3):
+        h, w = randn(M, K, seed=30 + rep, dtype=torch.bfloat16), randn(N, K, seed=31, dtype=torch.bfloat16, std=0.05)
+        x = randn(M, N, seed=32 + rep, std=2.0)
+        nw = (1 + 0.1 * randn(N, seed=33)).to(wdtype)
+        x_fused = x.clone()
+        lazy = ops.linear_add_rms_norm(h, w, x_fused, nw, 1e-5)
+        assert isinstance(lazy, LazyNorm)
+        branch = (h.float() @ w.float().T).to(torch.bfloat16).float()
+        torch.testing.assert_close(x_fused, x + branch, atol=2e-2, rtol=1e-2)
+        normed = plain_llama.rms_norm(x_fused.cpu(), nw.float().cpu(), 1e-5)
+        torch.testing.assert_close(ops.materialize(lazy).float().cpu(), normed, atol=4e-2, rtol=1.6e-2)
+        w2 = randn(176, N, seed=34, dtype=torch.bfloat16, std=0.05)
+        want = normed.to(torch.bfloat16).float() @ w2.float().cpu().T
+        torch.testing.assert_close(ops.linear(lazy, w2, out_float32=True).cpu(), want, atol=3e-2, rtol=2e-2)
+        g, u = want[:, :88], want[:, 88:]
+        torch.testing.assert_close(ops.gated_silu_linear(lazy, w2).float().cpu(), g * torch.sigmoid(g) * u, atol=4e-2, rtol=4e-2)
+    assert ops.core.pl_gemm_skinny_timeouts() == 0

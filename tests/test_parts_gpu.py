@@ -55,7 +55,8 @@ def test_feed_forward_part(ops, dtype):
     assert {k: v.shape for k, v in ffn.tensor_specs().items()} == {k: tuple(v.shape) for k, v in ws.items()}
     ffn.load(ws)
     h = randn(13, 72, seed=7).to(dtype)
-    got = ffn.forward(h, type("C", (), {"ops": ops})()).float().cpu()
+    from paged_llm_b200.parts import materialize
+    got = materialize(ffn.forward(h, type("C", (), {"ops": ops})()), ops).float().cpu()
     want = plain_llama.gated_mlp(h.float().cpu(), *(ws[k].float().cpu() for k in ("p.gate_proj", "p.up_proj", "p.down_proj")))
     torch.testing.assert_close(got, want, atol=3e-2 if dtype == torch.bfloat16 else 1e-5, rtol=3e-2 if dtype == torch.bfloat16 else 1e-5)
     with pytest.raises(ValueError, match="silu"):
@@ -98,7 +99,8 @@ def test_attention_part(ops, dtype, window):
         ctx.ops = ops
         ctx.block_tables = [bt[active].contiguous()]
         h = torch.cat([hs[s][starts[s]:ends[s]] for s in active]).contiguous()
-        out = mixer.forward(h, ctx, cache).float().cpu()
+        from paged_llm_b200.parts import materialize
+        out = materialize(mixer.forward(h, ctx, cache), ops).float().cpu()
         o = 0
         for s, n in zip(active, q_lens):
             outs[s].append(out[o:o + n])

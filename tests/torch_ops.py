@@ -54,6 +54,20 @@ class TorchOps:
         g, u = gate_up[:, :i].float(), gate_up[:, i:].float()
         return (g * torch.sigmoid(g) * u).to(self.compute_dtype)
 
+    def materialize(self, h):
+        return h
+
+    def linear_add_rms_norm(self, h, w, x, norm_w, eps):
+        return self.add_rms_norm(x, self.linear(h, w), norm_w, eps)
+
+    def gated_silu_linear(self, h, w_gate_up):
+        return self.silu_mul(self.linear(h, w_gate_up))
+
+    def qkv_rope_write(self, h, w_qkv, nh, nkv, d, position, ctx, kv, block_table, write=True):
+        qkv = self.linear(h, w_qkv)
+        self.rope_kv_write(qkv, nh, nkv, d, position, ctx, kv, block_table, write=write)
+        return qkv
+
     def gather_rows(self, x, idx):
         return x[idx.long()].clone()
 
