@@ -171,19 +171,33 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
                     mma_bf16(sacc[2 * n2 + 1], a, b[2], b[3]);
                 }
             }
-            // scale, mask, running maximum
+            // scale, mask, running maximum.  A tile whose keys all lie at or before the first
+            // row's position (and inside the window and the range) needs no mask.
+            const int pos_min_warp = __reduce_min_sync(0xffffffffu, min(pos[0], pos[1]));    // -1 if a row is padding
+            const bool full_tile = p.window <= 0 && kbase + KPW <= it.key_hi && kbase + KPW - 1 <= pos_min_warp;
             float mx[2] = {-INFINITY, -INFINITY};
+            if (full_tile) {
 #pragma unroll
-            for (int j = 0; j < KPW / 8; ++j)
+                for (int j = 0; j < KPW / 8; ++j)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int n = kbase + 8 * j + 2 * t4 + (e & 1);
-                    const int pr = pos[e >> 1];
-                    const bool vis = n < it.key_hi && n <= pr && (p.window <= 0 || n > pr - p.window);
-                    const float s = vis ? sacc[j][e] * scale_log2 : -INFINITY;
-                    sacc[j][e] = s;
-                    mx[e >> 1] = fmaxf(mx[e >> 1], s);
-                }
+                    for (int e = 0; e < 4; ++e) {
+                        const float s = sacc[j][e] * scale_log2;
+                        sacc[j][e] = s;
+                        mx[e >> 1] = fmaxf(mx[e >> 1], s);
+                    }
+            } else {
+#pragma unroll
+                for (int j = 0; j < KPW / 8; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int n = kbase + 8 * j + 2 * t4 + (e & 1);
+                        const int pr = pos[e >> 1];
+                        const bool vis = n < it.key_hi && n <= pr && (p.window <= 0 || n > pr - p.window);
+                        const float s = vis ? sacc[j][e] * scale_log2 : -INFINITY;
+                        sacc[j][e] = s;
+                        mx[e >> 1] = fmaxf(mx[e >> 1], s);
+                    }
+            }
             float alpha[2];
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -364,11 +378,22 @@ int launch_attn_bf16(const AttnParams& p, cudaStream_t stream) {
 
 }  // namespace
 
+#if PL_DPAD == 64
+#include "attention_tc.cuh"
+// Waits inside the tcgen05 kernel that gave up since the library was loaded (0 unless something is broken).
+PL_EXPORT int pl_attention_tc_timeouts() {
+    int n = 0;
+    if (cudaMemcpyFromSymbol(&n, tc::g_timeouts, sizeof(int)) != cudaSuccess) return -1;
+    return n;
+}
+#endif
+
 #define PL_CAT_(a, b) a##b
 #define PL_CAT(a, b) PL_CAT_(a, b)
 
 // Tile rows of the two shapes, so that the host plans with the same numbers.
-PL_EXPORT int PL_CAT(pl_attention_bf16_rows_d, PL_DPAD)(int small) { return small ? 16 : 64; }
+#define PL_LARGE_MW (PL_DPAD <= 128 ? 8 : 4)
+PL_EXPORT int PL_CAT(pl_attention_bf16_rows_d, PL_DPAD)(int small) { return small ? 16 : 16 * PL_LARGE_MW; }
 
 PL_EXPORT int PL_CAT(pl_attention_bf16_d, PL_DPAD)(const AttnParams* params, cudaStream_t stream) {
     AttnParams p = *params;
@@ -380,5 +405,10 @@ PL_EXPORT int PL_CAT(pl_attention_bf16_d, PL_DPAD)(const AttnParams* params, cud
     PL_REQUIRE(((uintptr_t)p.q & 15) == 0 && ((uintptr_t)p.kv & 15) == 0, "attention_bf16: q and kv must be 16-byte aligned");
     constexpr int KPW_SMALL = PL_DPAD <= 128 ? 32 : 16;
     if (p.is_small) return launch_attn_bf16<PL_DPAD, 1, 4, KPW_SMALL>(p, stream);
-    return launch_attn_bf16<PL_DPAD, 4, 1, 64>(p, stream);
+#if PL_DPAD == 64
+    // prefill tiles of head size 64 run on tcgen05 with tensor-memory accumulators
+    static const bool no_tc = getenv("PAGED_LLM_B200_NO_TCGEN05") != nullptr;
+    if (p.d == 64 && !no_tc) return tc::launch(p, stream);
+#endif
+    return launch_attn_bf16<PL_DPAD, PL_LARGE_MW, 1, 64>(p, stream);
 }

@@ -1,0 +1,394 @@
+// Paged prefill attention on the 5th-generation tensor cores (tcgen05) with the
+// accumulators in tensor memory, for head size 64 in bfloat16.
+//
+// One thread block takes a tile of 128 query rows of one kv head (row = token * G
+// + head within the group, as in attention_bf16.cuh) and walks its keys 128 at a
+// time:
+//   S = Q K^T     tcgen05.mma 128x128x64, Q and the key tile in shared memory
+//                 (K-major, 128-byte swizzle), S in tensor memory (128 columns);
+//   softmax       two threads per row, each with half of the columns: they read S
+//                 from tensor memory (tcgen05.ld), mask by absolute position,
+//                 exchange their maxima through shared memory, keep the running
+//                 maximum and sum in float32, rescale O in tensor memory where a
+//                 maximum moved, and write P in bfloat16 to shared memory;
+//   O += P V      tcgen05.mma 128x64x128, P from shared memory, the value tile as
+//                 the MN-major operand, O in tensor memory (64 columns).
+// Keys and values come through the block table with cp.async into two swizzled
+// stages, zero-filled outside the key range.  A block allocates 256 columns of
+// tensor memory and 97 KiB of shared memory, so two blocks share an SM and one
+// block's softmax overlaps the other's products.  Completion of the products is
+// signalled by tcgen05.commit on mbarriers; every wait is bounded and counts a
+// timeout instead of hanging (pl_attention_tc_timeouts).
+//
+// Semantics are those of attention_bf16.cuh (xiyiji/paged-llm
+// pagedllm/attention/triton_kernel.py:22-93): float32 scores, maximum, sum and
+// accumulator; P rounded to bfloat16 for the second product.
+#pragma once
+
+#include "attention_common.cuh"
+
+namespace tc {
+
+constexpr int BM = 128, BN = 128, D = 64;
+constexpr int THREADS = 256;          // two threads per query row: each takes half of the columns
+constexpr int TMEM_COLS = 256;           // S: columns 0..127, O: 128..191
+constexpr int Q_BYTES = BM * 128, KV_STAGE_BYTES = BN * 128, P_BYTES = BM * BN * 2;
+constexpr int SMEM_BYTES = Q_BYTES + 3 * KV_STAGE_BYTES + P_BYTES + 1024;     // + alignment slack
+constexpr unsigned SPIN_LIMIT = 1u << 20;
+
+__device__ int g_timeouts = 0;
+
+__device__ __forceinline__ uint32_t saddr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp16(void* dst, const void* src, int bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(saddr(dst)), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(saddr(bar)), "r"(count));
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    for (unsigned i = 0; i < SPIN_LIMIT; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done)
+            : "r"(saddr(bar)), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    atomicAdd(&g_timeouts, 1);
+    return false;
+}
+
+// 64-bit shared-memory matrix descriptor: start address, leading and stride byte offsets
+// (all in units of 16 bytes), descriptor version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)(lbo_bytes >> 4) << 16;
+    d |= (uint64_t)(sbo_bytes >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;                     // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor of kind::f16: float32 accumulator, bfloat16 operands.
+__host__ __device__ constexpr uint32_t instr_desc(int m, int n, bool b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.u32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(saddr(bar)) : "memory");
+}
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n" ::"r"(taddr),
+        "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+        "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+        "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm volatile("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Byte offset of 16-byte chunk c (0..7) of row r in a [rows][128 B] tile with 128-byte swizzle.
+__device__ __forceinline__ int swz(int r, int c) { return r * 128 + ((c ^ (r & 7)) << 4); }
+
+__global__ void __launch_bounds__(THREADS, 2) attn_tc_kernel(AttnParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const AttnItem it = attn_decode_item(p, blockIdx.x, BM, BN);
+    if (!it.valid) return;
+
+    extern __shared__ unsigned char smem_unaligned[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_unaligned + 1023) & ~(uintptr_t)1023);
+    unsigned char* Qs = smem;                                  // [128][128 B]
+    unsigned char* Ks = Qs + Q_BYTES;                          // [128][128 B]: free again once S is done
+    unsigned char* Vs = Ks + KV_STAGE_BYTES;                   // [2][128][128 B]
+    unsigned char* Ps = Vs + 2 * KV_STAGE_BYTES;               // [2 column blocks][128][128 B]
+    __shared__ uint64_t bar_s, bar_o;
+    __shared__ uint32_t tmem_base_slot;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int kvh = blockIdx.y, G = p.nh / p.nkv;
+    const __nv_bfloat16* q = (const __nv_bfloat16*)p.q;
+    const __nv_bfloat16* kv = (const __nv_bfloat16*)p.kv;
+    const int* bt = p.block_table + (size_t)it.seq * p.bt_stride;
+    const size_t v_off = (size_t)p.nkv * p.ps * D;
+
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(saddr(&tmem_base_slot)),
+                     "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    }
+    if (tid == 0) {
+        mbar_init(&bar_s, 1);
+        mbar_init(&bar_o, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+
+    // Q tile: row R = token * G + head; eight 16-byte chunks per row
+    for (int e = tid; e < BM * 8; e += THREADS) {
+        const int r = e >> 3, c = e & 7;
+        const int R = it.row_base + r;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (R < it.rows_total)
+            v = *reinterpret_cast<const uint4*>(q + (size_t)(it.q0 + R / G) * p.q_stride + (kvh * G + R % G) * D + c * 8);
+        *reinterpret_cast<uint4*>(Qs + swz(r, c)) = v;
+    }
+
+    // One tile of keys (sel 0) or values (sel 1): every thread looks up the pages of its rows
+    // first, then issues the copies.
+    auto load_tile = [&](unsigned char* dst, int kt, int sel) {
+        constexpr int ITERS = BN * 8 / THREADS;
+        int pg[ITERS];
+#pragma unroll
+        for (int i = 0; i < ITERS; ++i) {
+            const int n = kt + ((tid + i * THREADS) >> 3);
+            const int pi = p.ps_shift >= 0 ? n >> p.ps_shift : n / p.ps;
+            pg[i] = n < it.key_hi ? bt[pi] : -1;
+        }
+#pragma unroll
+        for (int i = 0; i < ITERS; ++i) {
+            const int e = tid + i * THREADS;
+            const int j = e >> 3, c = e & 7;
+            const int n = kt + j;
+            const int po = p.ps_shift >= 0 ? n & (p.ps - 1) : n % p.ps;
+            const bool ok = pg[i] >= 0;
+            const __nv_bfloat16* src =
+                ok ? kv + ((((size_t)pg[i] * 2 + sel) * p.nkv + kvh) * p.ps + po) * D + c * 8 : kv;
+            cp16(dst + swz(j, c), src, ok ? 16 : 0);
+        }
+        cp_commit();
+    };
+
+    const int n_tiles = (it.key_hi - it.key_lo + BN - 1) / BN;
+    if (n_tiles > 0) {
+        load_tile(Ks, it.key_lo, 0);
+        load_tile(Vs, it.key_lo, 1);
+    }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem_base = tmem_base_slot;
+    const int half = warp >> 2;                                 // which half of the columns this thread takes
+    const uint32_t tmem_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);   // this warp's 32 lanes
+    const uint32_t tmem_s = tmem_row + half * 64, tmem_o = tmem_row + 128 + half * 32;
+    __shared__ float xmax[2][BM];                               // the halves' maxima of the current tile
+
+    const int r = (warp & 3) * 32 + lane;                       // this thread's row of the tile
+    const int R = it.row_base + r;
+    const int pos = R < it.rows_total ? it.lk - it.nq + R / G : -1;
+    float m_run = -INFINITY, l_run = 0.f;
+    const float scale_log2 = p.scale * 1.4426950408889634f;
+    constexpr uint32_t IDESC_S = instr_desc(BM, BN, false), IDESC_O = instr_desc(BM, D, true);
+    uint32_t phase_s = 0, phase_o = 0;
+
+    // cp.async groups: at the top of iteration t the copies of K(t) and V(t) are in flight or done;
+    // V(t+1) is requested there, K(t+1) as soon as S(t) is done with the key stage.
+    for (int t = 0; t < n_tiles; ++t) {
+        const int stage = t & 1;
+        const bool more = t + 1 < n_tiles;
+        if (t > 0) {
+            // P V of the tile before must be done before its P, its value stage and O are touched
+            mbar_wait(&bar_o, phase_o);
+            phase_o ^= 1;
+            __syncwarp();
+            fence_after_sync();
+        }
+        if (more) load_tile(Vs + (stage ^ 1) * KV_STAGE_BYTES, it.key_lo + (t + 1) * BN, 1);
+        if (more) cp_wait<1>(); else cp_wait<0>();             // all but V(t+1): K(t) and V(t) have landed
+        fence_async_smem();                                     // cp.async and Q stores -> tensor-core reads
+        __syncthreads();
+        if (tid == 0) {
+            fence_after_sync();
+            const uint32_t qa = saddr(Qs), ka = saddr(Ks);
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk)
+                mma_f16(tmem_base, smem_desc(qa + kk * 32, 16, 1024), smem_desc(ka + kk * 32, 16, 1024), IDESC_S, kk > 0);
+            mma_commit(&bar_s);
+        }
+        mbar_wait(&bar_s, phase_s);
+        phase_s ^= 1;
+        __syncwarp();
+        fence_after_sync();
+        if (more) load_tile(Ks, it.key_lo + (t + 1) * BN, 0);   // the key stage is free again
+
+        // softmax of this thread's half row, in two passes over S in tensor memory
+        const int kbase = it.key_lo + t * BN;
+        const int kcol = kbase + half * 64;
+        const bool row_full = p.window <= 0 && kbase + BN <= it.key_hi && kbase + BN - 1 <= pos;
+        const bool warp_full = __all_sync(0xffffffffu, row_full);
+        float m_tile = -INFINITY;
+        float sv[32];
+        if (warp_full) {
+#pragma unroll 1
+            for (int cb = 0; cb < 2; ++cb) {
+                tmem_ld32(tmem_s + cb * 32, sv);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) m_tile = fmaxf(m_tile, sv[i]);
+            }
+            m_tile *= scale_log2;
+        } else {
+#pragma unroll 1
+            for (int cb = 0; cb < 2; ++cb) {
+                tmem_ld32(tmem_s + cb * 32, sv);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int n = kcol + cb * 32 + i;
+                    const bool vis = n < it.key_hi && n <= pos && (p.window <= 0 || n > pos - p.window);
+                    m_tile = fmaxf(m_tile, vis ? sv[i] * scale_log2 : -INFINITY);
+                }
+            }
+        }
+        xmax[half][r] = m_tile;
+        __syncthreads();
+        m_tile = fmaxf(m_tile, xmax[half ^ 1][r]);
+        const float m_new = fmaxf(m_run, m_tile);
+        const float alpha = m_run == -INFINITY ? 0.f : ex2(m_run - m_new);
+        const bool changed = m_new != m_run;
+        m_run = m_new;
+        l_run *= alpha;
+        const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
+        float l_add = 0.f;
+#pragma unroll 1
+        for (int cb = 0; cb < 2; ++cb) {
+            tmem_ld32(tmem_s + cb * 32, sv);
+            uint32_t packed[16];
+            if (warp_full) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float p0 = ex2(fmaf(sv[2 * i], scale_log2, neg_m));
+                    const float p1 = ex2(fmaf(sv[2 * i + 1], scale_log2, neg_m));
+                    l_add += p0 + p1;
+                    __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
+                    packed[i] = *reinterpret_cast<uint32_t*>(&b);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    float pv[2];
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int n = kcol + cb * 32 + 2 * i + e;
+                        const bool vis = n < it.key_hi && n <= pos && (p.window <= 0 || n > pos - p.window);
+                        pv[e] = vis ? ex2(fmaf(sv[2 * i + e], scale_log2, neg_m)) : 0.f;
+                    }
+                    l_add += pv[0] + pv[1];
+                    __nv_bfloat162 b = __floats2bfloat162_rn(pv[0], pv[1]);
+                    packed[i] = *reinterpret_cast<uint32_t*>(&b);
+                }
+            }
+            unsigned char* blk = Ps + half * (BM * 128);            // this half's 64-key column block
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4)
+                *reinterpret_cast<uint4*>(blk + swz(r, cb * 4 + c4)) =
+                    make_uint4(packed[4 * c4], packed[4 * c4 + 1], packed[4 * c4 + 2], packed[4 * c4 + 3]);
+        }
+        l_run += l_add;
+        // rescale O where a row's maximum moved (skipped when it moved in no row of the warp)
+        if (t > 0 && __any_sync(0xffffffffu, changed)) {
+            tmem_ld32(tmem_o, sv);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) sv[i] *= alpha;
+            tmem_st32(tmem_o, sv);
+            tmem_st_wait();
+        }
+        fence_async_smem();                                     // P (generic stores) -> tensor-core reads
+        fence_before_sync();
+        __syncthreads();
+        if (tid == 0) {
+            fence_after_sync();
+            const uint32_t pa = saddr(Ps), va = saddr(Vs + stage * KV_STAGE_BYTES);
+#pragma unroll
+            for (int kk = 0; kk < BN / 16; ++kk)
+                mma_f16(tmem_base + 128, smem_desc(pa + (kk >> 2) * (BM * 128) + (kk & 3) * 32, 16, 1024),
+                        smem_desc(va + kk * 2048, 16, 1024), IDESC_O, t > 0 || kk > 0);
+            mma_commit(&bar_o);
+        }
+    }
+    if (n_tiles > 0) {
+        mbar_wait(&bar_o, phase_o);
+        __syncwarp();
+        fence_after_sync();
+        // the row sum is the sum of the halves' sums
+        xmax[half][r] = l_run;
+        __syncthreads();
+        const float l_row = l_run + xmax[half ^ 1][r];
+        // every lane takes part in the aligned load; only valid rows store their 32 columns
+        const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
+        const int Rc = pos >= 0 ? R : it.row_base;
+        const int tok = Rc / G, head = kvh * G + Rc % G;
+        __nv_bfloat16* o_row = (__nv_bfloat16*)p.out + (size_t)(it.q0 + tok) * p.out_stride + head * D + half * 32;
+        float o[32];
+        tmem_ld32(tmem_o, o);
+        if (pos >= 0) {
+#pragma unroll
+            for (int c8 = 0; c8 < 4; ++c8) {
+                __nv_bfloat162 b[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) b[i] = __floats2bfloat162_rn(o[c8 * 8 + 2 * i] * inv, o[c8 * 8 + 2 * i + 1] * inv);
+                *reinterpret_cast<uint4*>(o_row + c8 * 8) = *reinterpret_cast<uint4*>(b);
+            }
+        }
+        __syncwarp();
+    }
+    fence_before_sync();
+    __syncthreads();
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS));
+}
+
+inline int launch(const AttnParams& p, cudaStream_t stream) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        PL_CUDA(cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        PL_CUDA(cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                     (int)cudaSharedmemCarveoutMaxShared));
+        attr_set = true;
+    }
+    PL_CUDA(launch_pdl(attn_tc_kernel, dim3(p.n_work, p.nkv), dim3(THREADS), (size_t)SMEM_BYTES, stream, p));
+    return 0;
+}
+
+}  // namespace tc

@@ -70,7 +70,7 @@ constexpr int SK_ROW_PAD = 64;           // bytes between rows of a stage beyond
 constexpr int SK_STAGE_PITCH = SK_KC * 2 + SK_ROW_PAD;
 constexpr int SK_STAGE_BYTES = 16 * SK_STAGE_PITCH;
 constexpr int SK_STAGES = 6;
-constexpr unsigned SK_SPIN_LIMIT = 1u << 24;
+constexpr unsigned SK_SPIN_LIMIT = 1u << 21;
 
 __device__ int g_skinny_timeouts = 0;    // waits that gave up (never expected; read by pl_gemm_skinny_timeouts)
 

@@ -297,14 +297,19 @@ class CudaOps:
         self.launches += 1
 
     # ---- attention ---------------------------------------------------------------
-    def _large_rows(self) -> int:
-        return 64 if self.compute_dtype == torch.bfloat16 else 16
+    def _large_rows(self, head_dim: int) -> int:
+        """Query rows of a prefill tile: what the kernel that will run was built with."""
+        if self.compute_dtype != torch.bfloat16:
+            return 16
+        b = head_dim_build(head_dim)
+        lib = load_module(f"attn_bf16_d{b}")
+        return int(getattr(lib, f"pl_attention_bf16_rows_d{b}")(0))
 
-    def plan_attention(self, q_lens, k_lens, group_size, num_kv_heads, window, pad_requests=None,
+    def plan_attention(self, q_lens, k_lens, group_size, num_kv_heads, window, head_dim, pad_requests=None,
                        fixed_capacity=False) -> dict:
         return planning.plan_attention(
             q_lens, k_lens, group_size, num_kv_heads, window, small_rows=self.SMALL_ROWS,
-            large_rows=self._large_rows(), min_split_keys=self.MIN_SPLIT_KEYS, num_sms=self.num_sms,
+            large_rows=self._large_rows(head_dim), min_split_keys=self.MIN_SPLIT_KEYS, num_sms=self.num_sms,
             max_splits=self.MAX_SPLITS, pad_requests=pad_requests, fixed_capacity=fixed_capacity)
 
     def _scratch_for(self, floats: int) -> torch.Tensor:
@@ -321,7 +326,7 @@ class CudaOps:
 
     def paged_attention(self, qkv, nh, nkv, d, kv, block_table, ctx, scale, window):
         T = ctx.num_tokens
-        plan = ctx.attention_plans[(nh // nkv, nkv, window)]
+        plan = ctx.attention_plans[(nh // nkv, nkv, window, d)]
         out = torch.empty((T, nh * d), dtype=qkv.dtype, device=self.device)
         if T > sum(ctx.host.q_lens):
             out.zero_()                                   # padded rows of a graph bucket

@@ -39,8 +39,8 @@ class PagedAttention(Mixer):
         return PagedKV(self.num_kv_heads, self.head_dim, self.window)
 
     def attention_plan_key(self):
-        """(query heads per kv head, kv heads, window): what the step's work lists depend on."""
-        return (self.num_heads // self.num_kv_heads, self.num_kv_heads, self.window)
+        """(query heads per kv head, kv heads, window, head size): what the step's work lists depend on."""
+        return (self.num_heads // self.num_kv_heads, self.num_kv_heads, self.window, self.head_dim)
 
     def tensor_specs(self):
         h, d = self.hidden_size, self.head_dim

@@ -132,11 +132,11 @@ def paged_case(q_lens, k_lens, nh, nkv, d, ps, dtype, seed=0, spare=3):
     return q, kv.to(dtype), bt, keys, vals
 
 
-def make_ctx(ops, q_lens, k_lens, nh, nkv, window):
+def make_ctx(ops, q_lens, k_lens, nh, nkv, window, d=64):
     from paged_llm_b200.engine.context import AttentionPlan, HostBatch
     S = len(q_lens)
     host = HostBatch(list(q_lens), [k - q for q, k in zip(q_lens, k_lens)], [-1] * S)
-    plan = ops.plan_attention(q_lens, k_lens, nh // nkv, nkv, window)
+    plan = ops.plan_attention(q_lens, k_lens, nh // nkv, nkv, window, d)
     dev = lambda a: torch.from_numpy(np.ascontiguousarray(a, np.int32)).cuda()
     small, large = plan["small"].reshape(-1, 4), plan["large"].reshape(-1, 4)
     ap = AttentionPlan(dev(small) if len(small) else None, dev(large) if len(large) else None, dev(plan["splits"]),
@@ -146,7 +146,7 @@ def make_ctx(ops, q_lens, k_lens, nh, nkv, window):
     tseq = np.concatenate([np.full(q, s) for s, q in enumerate(q_lens)])
     return types.SimpleNamespace(num_tokens=T, num_seqs=S, host=host, cu_seqlens_q=dev(host.cu),
                                  seq_lens_k=dev(k_lens), positions=dev(pos), token_seq=dev(tseq),
-                                 attention_plans={(nh // nkv, nkv, window): ap})
+                                 attention_plans={(nh // nkv, nkv, window, d): ap})
 
 
 ATTN_SHAPES = [(8, 8, 64), (32, 8, 128), (32, 4, 64), (6, 2, 48), (3, 3, 32), (4, 2, 16), (5, 1, 80), (2, 1, 256)]
@@ -169,7 +169,7 @@ def test_paged_attention(ops, dtype, ps, nh, nkv, d, case):
         pytest.skip("full cross product only for the benchmark head shape")
     ops.set_compute_dtype(dtype)
     q, kv, bt, keys, vals = paged_case(q_lens, k_lens, nh, nkv, d, ps, dtype, seed=case)
-    ctx = make_ctx(ops, q_lens, k_lens, nh, nkv, None)
+    ctx = make_ctx(ops, q_lens, k_lens, nh, nkv, None, d)
     qkv = torch.cat([q.reshape(-1, nh * d), torch.zeros(q.shape[0], 2 * nkv * d, dtype=dtype)], dim=1).cuda().contiguous()
     out = ops.paged_attention(qkv, nh, nkv, d, kv.cuda(), bt.cuda(), ctx, d ** -0.5, None).float().cpu()
     cu = ctx.host.cu
@@ -193,7 +193,7 @@ def test_paged_attention_window(ops, dtype, window):
         for j in range(bt.shape[1]):
             if (j + 1) * ps <= first_needed:
                 bt[s, j] = -1
-    ctx = make_ctx(ops, q_lens, k_lens, nh, nkv, window)
+    ctx = make_ctx(ops, q_lens, k_lens, nh, nkv, window, d)
     qkv = torch.cat([q.reshape(-1, nh * d), torch.zeros(q.shape[0], 2 * nkv * d, dtype=dtype)], dim=1).cuda().contiguous()
     out = ops.paged_attention(qkv, nh, nkv, d, kv.cuda(), bt.cuda(), ctx, 0.3, window).float().cpu()
     cu = ctx.host.cu
@@ -219,7 +219,7 @@ def test_one_far_key_among_hundreds(ops, dtype):
         for h in range(nkv):
             keys[0][target, h] = (direction * 40).to(dtype).float()
             kv[bt[0, target // ps], 0, h, target % ps] = keys[0][target, h].to(dtype)
-        ctx = make_ctx(ops, [1], [L], nh, nkv, None)
+        ctx = make_ctx(ops, [1], [L], nh, nkv, None, d)
         qkv = torch.cat([q.reshape(-1, nh * d), torch.zeros(1, 2 * nkv * d, dtype=dtype)], dim=1).cuda().contiguous()
         out = ops.paged_attention(qkv, nh, nkv, d, kv.cuda(), bt.cuda(), ctx, d ** -0.5, None).float().cpu()
         want = vals[0][target].repeat_interleave(nh // nkv, dim=0).reshape(1, nh * d)
@@ -235,7 +235,7 @@ def test_rope_and_kv_write(ops, dtype, pairing, nh, nkv, d, rd):
     rope = RotaryEncoding({}, head_dim=d, theta=10000.0, rotary_dim=rd, pairing=pairing)
     rope.prepare(512, "cuda", ops)
     ps, q_lens, k_lens = 8, [5, 1, 20], [5, 300, 31]
-    ctx = make_ctx(ops, q_lens, k_lens, nh, nkv, None)
+    ctx = make_ctx(ops, q_lens, k_lens, nh, nkv, None, d)
     T = sum(q_lens)
     qkv = randn(T, (nh + 2 * nkv) * d, seed=11).to(dtype)
     before = qkv.clone()
@@ -368,7 +368,7 @@ def test_skinny_qkv_rope_write_equals_the_separate_kernels(ops, nh, nkv, d, q_le
     rope = RotaryEncoding({}, head_dim=d, theta=10000.0)
     rope.prepare(512, "cuda", ops)
     H, ps, pages = 96, 8, 64
-    ctx = make_ctx(ops, q_lens, k_lens, nh, nkv, None)
+    ctx = make_ctx(ops, q_lens, k_lens, nh, nkv, None, d)
     T = sum(q_lens)
     h = randn(T, H, seed=24, dtype=torch.bfloat16)
     w = randn((nh + 2 * nkv) * d, H, seed=25, dtype=torch.bfloat16, std=0.2)

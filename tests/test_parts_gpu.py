@@ -95,7 +95,7 @@ def test_attention_part(ops, dtype, window):
     for starts, ends in cuts:
         active = [s for s in range(2) if ends[s] > starts[s]]
         q_lens = [ends[s] - starts[s] for s in active]
-        ctx = make_ctx(ops, q_lens, [ends[s] for s in active], nh, nkv, window)
+        ctx = make_ctx(ops, q_lens, [ends[s] for s in active], nh, nkv, window, d)
         ctx.ops = ops
         ctx.block_tables = [bt[active].contiguous()]
         h = torch.cat([hs[s][starts[s]:ends[s]] for s in active]).contiguous()

@@ -50,8 +50,8 @@ def test_static_scratch_entry_point_matches_the_regular_one(nh, nkv, d, ps):
         if nh // nkv * max(q_lens) > 16:
             q_lens = [1] * len(q_lens)
         q, kv, bt, _, _ = paged_case(q_lens, k_lens, nh, nkv, d, ps, torch.bfloat16, seed=40 + call)
-        ctx = make_ctx(ops, q_lens, k_lens, nh, nkv, None)
-        plan = ctx.attention_plans[(nh // nkv, nkv, None)]
+        ctx = make_ctx(ops, q_lens, k_lens, nh, nkv, None, d)
+        plan = ctx.attention_plans[(nh // nkv, nkv, None, d)]
         assert plan.n_small and not plan.n_large and plan.max_splits > 1
         qkv = torch.cat([q.reshape(-1, nh * d), torch.zeros(q.shape[0], 2 * nkv * d, dtype=torch.bfloat16)], 1).cuda().contiguous()
         kv, bt = kv.cuda(), bt.cuda()

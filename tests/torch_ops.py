@@ -109,7 +109,7 @@ class TorchOps:
                 kv[page, 1, :, p % ps, :] = v[t].to(kv.dtype)
 
     # ---- attention -------------------------------------------------------------
-    def plan_attention(self, q_lens, k_lens, group_size, num_kv_heads, window, pad_requests=None,
+    def plan_attention(self, q_lens, k_lens, group_size, num_kv_heads, window, head_dim, pad_requests=None,
                        fixed_capacity=False):
         return plan_attention(q_lens, k_lens, group_size, num_kv_heads, window, small_rows=16, large_rows=64,
                               min_split_keys=128, num_sms=4, pad_requests=pad_requests, fixed_capacity=fixed_capacity)
