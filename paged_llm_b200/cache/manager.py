@@ -257,15 +257,37 @@ class CacheManager:
             return None
         return idx if self.pools[g].pages[table[idx]].ref_count > 1 else None
 
+    def _covered(self, seq: Sequence, num_new_tokens: int) -> bool:
+        """True if every group's table already covers the new tokens and the page that takes
+        the first of them is this request's alone (no page to take, no copy to make)."""
+        bs = self.block_size
+        first = seq.num_computed_tokens
+        need = -(-(first + num_new_tokens) // bs)
+        tables = seq.block_tables
+        if len(tables) < len(self.pools):
+            return False
+        for g, pool in enumerate(self.pools):
+            table = tables[g]
+            if len(table) < need:
+                return False
+            if first % bs:
+                page = table[first // bs]
+                if page == NO_PAGE or pool.pages[page].ref_count != 1:
+                    return False
+        return True
+
     def allocate_slots(self, seq: Sequence, num_new_tokens: int, computed_blocks=None) -> list[int] | None:
         """Make every group's table cover computed + cached + new tokens.  Returns
         the new page ids of the first group, or None, having changed nothing, if
         any group cannot cover it (block_manager.py:171-217)."""
+        if not computed_blocks and self._covered(seq, num_new_tokens):
+            return []                                  # the usual decode step: the last page has room
         if not self.can_allocate(seq, num_new_tokens, computed_blocks):
             return None
         hits = self._normalise_hits(computed_blocks)
         num_cached = len(hits[0]) * self.block_size
         tables = self._tables(seq)
+        seq.table_version += 1
         first_group_new: list[int] = []
         for g, pool in enumerate(self.pools):
             cow_idx = self._cow_target(g, seq, num_cached, hits[g]) if num_new_tokens > 0 else None
@@ -306,6 +328,7 @@ class CacheManager:
                     self.pools[g].release(table[j])
                     table[j] = NO_PAGE
                     released += 1
+                    seq.table_version += 1
                 j += 1
         return released
 
@@ -319,6 +342,7 @@ class CacheManager:
                     self.pools[g].release(b)
         seq.block_tables = [[] for _ in self.pools]
         seq.page_hashes = []
+        seq.table_version += 1
         self.release_state_slot(seq)
 
     def fork(self, parent: Sequence, child: Sequence) -> None:
@@ -331,6 +355,7 @@ class CacheManager:
                 if b != NO_PAGE:
                     self.pools[g].touch(b)
         child.block_tables = [list(t) for t in parent.block_tables]
+        child.table_version += 1
         child.page_hashes = list(parent.page_hashes)
         child.num_computed_tokens = parent.num_computed_tokens
 

@@ -51,6 +51,16 @@ class _Packer:
         self.size += _align(cap)
 
 
+class _Staging:
+    """One pinned host buffer of the metadata ring, with the event of its last copy."""
+
+    def __init__(self):
+        self.tensor = None
+        self.array = None
+        self.event = None
+        self.busy = False
+
+
 class ModelRunner:
     GRAPH_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 
@@ -84,27 +94,37 @@ class ModelRunner:
         q_lens = [it.num_new_tokens for it in items]
         starts = [it.seq.num_computed_tokens for it in items]
         T = sum(q_lens)
-        ids = np.empty(T, np.int32)
-        pos = np.empty(T, np.int32)
-        tseq = np.empty(T, np.int32)
-        want = []
-        o = 0
-        for s, it in enumerate(items):
-            n, st = q_lens[s], starts[s]
-            if n < 1:
-                raise ValueError("a step item needs at least one new token")
-            toks = it.seq.token_ids[st:st + n]
-            if len(toks) != n:
-                raise ValueError(f"request {it.seq.seq_id} has {len(it.seq.token_ids)} tokens, step asks for "
-                                 f"{st}..{st + n}")
-            ids[o:o + n] = toks
-            pos[o:o + n] = np.arange(st, st + n, dtype=np.int32)
-            tseq[o:o + n] = s
-            for w in it.want:
-                if not 0 <= w < n:
-                    raise ValueError(f"wanted place {w} is outside the {n} tokens of this step")
-                want.append(o + w)
-            o += n
+        if T == S and all(it.want == (0,) for it in items):
+            # every request brings one token and wants its logits: no per-token loops
+            for it, st in zip(items, starts):
+                if st >= len(it.seq.token_ids):
+                    raise ValueError(f"request {it.seq.seq_id} has {len(it.seq.token_ids)} tokens, step asks for {st}")
+            ids = np.fromiter((it.seq.token_ids[st] for it, st in zip(items, starts)), np.int32, S)
+            pos = np.array(starts, np.int32)
+            tseq = np.arange(S, dtype=np.int32)
+            want = list(range(S))
+        else:
+            ids = np.empty(T, np.int32)
+            pos = np.empty(T, np.int32)
+            tseq = np.empty(T, np.int32)
+            want = []
+            o = 0
+            for s, it in enumerate(items):
+                n, st = q_lens[s], starts[s]
+                if n < 1:
+                    raise ValueError("a step item needs at least one new token")
+                toks = it.seq.token_ids[st:st + n]
+                if len(toks) != n:
+                    raise ValueError(f"request {it.seq.seq_id} has {len(it.seq.token_ids)} tokens, step asks for "
+                                     f"{st}..{st + n}")
+                ids[o:o + n] = toks
+                pos[o:o + n] = np.arange(st, st + n, dtype=np.int32)
+                tseq[o:o + n] = s
+                for w in it.want:
+                    if not 0 <= w < n:
+                        raise ValueError(f"wanted place {w} is outside the {n} tokens of this step")
+                    want.append(o + w)
+                o += n
         S_pad = pad_to or S
         T_pad = pad_to or T
         host = HostBatch(q_lens, starts, [(-1 if it.seq.state_slot is None else it.seq.state_slot) for it in items],
@@ -133,10 +153,10 @@ class ModelRunner:
         pk.add("lidx", lidx)
         strides = []
         for g in range(self.storage.num_groups):
-            tables = [it.seq.block_tables[g] if g < len(it.seq.block_tables) else [] for it in items]
-            stride = table_stride or _align(max([len(t) for t in tables] + [1]))
+            rows = [self._table_row(it.seq, g) for it in items]
+            stride = table_stride or _align(max([len(t) for t in rows] + [1]))
             bt = np.zeros((S_pad, stride), np.int32)
-            for s, t in enumerate(tables):
+            for s, t in enumerate(rows):
                 if len(t) > stride:
                     raise ValueError("block table longer than the captured stride")
                 bt[s, :len(t)] = t
@@ -153,34 +173,46 @@ class ModelRunner:
         return pk, host, dict(T=T_pad, S=S_pad, L=len(want), L_pad=L_pad, strides=strides, plans=plans,
                               max_q=max(q_lens))
 
-    def _host_buffer(self, n: int):
+    def _table_row(self, seq: Sequence, g: int) -> np.ndarray:
+        """The request's block table of group g as an array, rebuilt only when the cache
+        manager changed it."""
+        cache = seq.__dict__.get("_table_rows")
+        if cache is None or cache[0] != seq.table_version:
+            cache = (seq.table_version, [np.asarray(t, np.int32) for t in seq.block_tables])
+            seq.__dict__["_table_rows"] = cache
+        rows = cache[1]
+        return rows[g] if g < len(rows) else np.zeros(0, np.int32)
+
+    def _host_buffer(self, n: int) -> "_Staging":
         """A pinned staging buffer that no copy in flight still reads."""
         if not self._host_ring:
-            self._host_ring = [[None, None] for _ in range(4)]
+            self._host_ring = [_Staging() for _ in range(4)]
         slot = self._host_ring[self._ring_pos % len(self._host_ring)]
         self._ring_pos += 1
-        if slot[1] is not None:
-            slot[1].synchronize()
-            slot[1] = None
-        if slot[0] is None or slot[0].numel() < n:
-            slot[0] = torch.empty(max(2 * n, 1 << 14), dtype=torch.int32, pin_memory=self.device.type == "cuda")
-        return slot[0], slot
+        if slot.busy:
+            slot.event.synchronize()
+            slot.busy = False
+        if slot.tensor is None or slot.tensor.numel() < n:
+            slot.tensor = torch.empty(max(2 * n, 1 << 14), dtype=torch.int32, pin_memory=self.device.type == "cuda")
+            slot.array = slot.tensor.numpy()
+        return slot
 
     def _upload(self, pk: _Packer, dev: torch.Tensor | None = None) -> torch.Tensor:
-        host, slot = self._host_buffer(pk.size)
-        hv = host.numpy()
+        slot = self._host_buffer(pk.size)
+        hv = slot.array
         for _, off, data in pk.sections:
             hv[off:off + data.size] = data
         if dev is None:
             if self._dev_meta is None or self._dev_meta.numel() < pk.size:
                 self._dev_meta = torch.empty(max(pk.size * 2, 1 << 16), dtype=torch.int32, device=self.device)
             dev = self._dev_meta
-        dev[:pk.size].copy_(host[:pk.size], non_blocking=True)
+        dev[:pk.size].copy_(slot.tensor[:pk.size], non_blocking=True)
         self.h2d_bytes += pk.size * 4
         if self.device.type == "cuda":
-            ev = torch.cuda.Event()
-            ev.record()
-            slot[1] = ev
+            if slot.event is None:
+                slot.event = torch.cuda.Event()
+            slot.event.record()
+            slot.busy = True
         return dev
 
     def _context(self, pk: _Packer, dev: torch.Tensor, host: HostBatch, info: dict) -> StepContext:

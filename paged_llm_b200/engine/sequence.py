@@ -51,6 +51,7 @@ class Sequence:
         self.token_ids: list[int] = list(self.prompt_token_ids)
         self.block_tables: list[list[int]] = [[]]
         self.page_hashes: list[int] = []      # chained content hash of each full page so far
+        self.table_version: int = 0           # bumped by the cache manager whenever a block table changes
         self.state_slot: int | None = None    # slot of fixed-size per-request state
         self.max_tokens: int = self.sampling_params.max_tokens   # may be clamped at admission
 
@@ -101,5 +102,6 @@ class Sequence:
         self.num_computed_tokens = 0
         self.block_tables = [[] for _ in self.block_tables]
         self.page_hashes = []
+        self.table_version += 1
         self.status = SequenceStatus.WAITING
         self.num_preemptions += 1

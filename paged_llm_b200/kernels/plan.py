@@ -28,11 +28,38 @@ def wanted_splits(num_small: int, num_kv_heads: int, num_sms: int, max_splits: i
     return int(min(max_splits, max(1, -(-target_items // num_small))))
 
 
+def _plan_decode(S, S_pad, k_lens, num_kv_heads, min_split_keys, num_sms, max_splits, fixed_capacity) -> dict:
+    """The same plan for the common step in which every request brings one token, in array form."""
+    want = wanted_splits(S_pad if fixed_capacity else S, num_kv_heads, num_sms, max_splits)
+    lk = np.asarray(k_lens, np.int64)
+    ns = np.maximum(1, np.minimum(want, -(-lk // min_split_keys))).astype(np.int32)
+    splits = np.ones((S_pad, 2), np.int32)
+    splits[:, 1] = 0
+    splits[:S, 0] = ns
+    splits[:S, 1] = np.arange(S, dtype=np.int32)
+    total = int(ns.sum())
+    seq = np.repeat(np.arange(S, dtype=np.int32), ns)
+    first = np.cumsum(ns) - ns
+    small = np.empty((total, 4), np.int32)
+    small[:, 0] = seq
+    small[:, 1] = seq                                   # scratch base: one token per request
+    small[:, 2] = np.arange(total, dtype=np.int32) - np.repeat(first, ns).astype(np.int32)
+    small[:, 3] = np.repeat(ns, ns)
+    if fixed_capacity:
+        cap = S_pad * want
+        if cap > total:
+            small = np.concatenate([small, np.full((cap - total, 4), -1, np.int32)])
+    return {"small": small.reshape(-1), "large": np.zeros(0, np.int32), "splits": splits.reshape(-1),
+            "max_splits": int(want), "num_small_tokens": int(S_pad if fixed_capacity else S)}
+
+
 def plan_attention(q_lens, k_lens, group_size: int, num_kv_heads: int, window: int | None, *, small_rows: int,
                    large_rows: int, min_split_keys: int, num_sms: int, max_splits: int = 32,
                    pad_requests: int | None = None, fixed_capacity: bool = False) -> dict:
     S = len(q_lens)
     S_pad = pad_requests or S
+    if S and max(q_lens) == 1 and group_size <= small_rows and not window:
+        return _plan_decode(S, S_pad, k_lens, num_kv_heads, min_split_keys, num_sms, max_splits, fixed_capacity)
     small_ids = [s for s in range(S) if q_lens[s] * group_size <= small_rows]
     n_small = S_pad if fixed_capacity else len(small_ids)
     want = wanted_splits(n_small, num_kv_heads, num_sms, max_splits)
