@@ -85,14 +85,6 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
     const int* bt = p.block_table + (size_t)it.seq * p.bt_stride;
     const size_t v_off = (size_t)p.nkv * p.ps * d;
 
-    for (int e = tid; e < BM * CH; e += THREADS) {
-        const int r = e / CH, c8 = e - r * CH;
-        const int R = it.row_base + r;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (R < it.rows_total && c8 * 8 < d)
-            v = *reinterpret_cast<const uint4*>(q + (size_t)(it.q0 + R / G) * p.q_stride + (kvh * G + R % G) * d + c8 * 8);
-        *reinterpret_cast<uint4*>(Qs + r * PITCH + c8 * 8) = v;
-    }
 
     // One key tile: every thread first looks up the pages of all its rows (independent loads
     // that travel together), then issues the copies.
@@ -141,7 +133,15 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
     const float scale_log2 = p.scale * LOG2E;
 
     const int n_tiles = (it.key_hi - it.key_lo + BN - 1) / BN;
-    if (n_tiles > 0) load_tile(0, it.key_lo);
+    if (n_tiles > 0) load_tile(0, it.key_lo);        // the first keys are on their way while Q is fetched
+    for (int e = tid; e < BM * CH; e += THREADS) {
+        const int r = e / CH, c8 = e - r * CH;
+        const int R = it.row_base + r;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (R < it.rows_total && c8 * 8 < d)
+            v = *reinterpret_cast<const uint4*>(q + (size_t)(it.q0 + R / G) * p.q_stride + (kvh * G + R % G) * d + c8 * 8);
+        *reinterpret_cast<uint4*>(Qs + r * PITCH + c8 * 8) = v;
+    }
     for (int t = 0; t < n_tiles; ++t) {
         if (t + 1 < n_tiles) {
             load_tile((t + 1) & 1, it.key_lo + (t + 1) * BN);

@@ -231,6 +231,14 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(SkinnyParams
         const int tid = threadIdx.x, tok = tid & 15, slice = tid >> 4, nb = p.K / 16;
         float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
         int b = slice;
+        for (; b + 112 < nb; b += 128) {                 // eight loads in flight per thread
+            const float v0 = __ldcg(p.part_in + (size_t)b * 16 + tok), v1 = __ldcg(p.part_in + (size_t)(b + 16) * 16 + tok);
+            const float v2 = __ldcg(p.part_in + (size_t)(b + 32) * 16 + tok), v3 = __ldcg(p.part_in + (size_t)(b + 48) * 16 + tok);
+            const float v4 = __ldcg(p.part_in + (size_t)(b + 64) * 16 + tok), v5 = __ldcg(p.part_in + (size_t)(b + 80) * 16 + tok);
+            const float v6 = __ldcg(p.part_in + (size_t)(b + 96) * 16 + tok), v7 = __ldcg(p.part_in + (size_t)(b + 112) * 16 + tok);
+            s0 += v0; s1 += v1; s2 += v2; s3 += v3;
+            s0 += v4; s1 += v5; s2 += v6; s3 += v7;
+        }
         for (; b + 48 < nb; b += 64) {
             s0 += __ldcg(p.part_in + (size_t)b * 16 + tok);
             s1 += __ldcg(p.part_in + (size_t)(b + 16) * 16 + tok);
@@ -260,14 +268,57 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(SkinnyParams
     // X does not depend on the row block, only on the chunk: the fragments of the next chunk
     // are fetched while the current one is multiplied, so their latency hides behind the
     // wait for the weights.
+    // All loads of a stage go out before the first value is used: with the normalising prologue
+    // the raw float32 values and the norm weights are fetched first, then scaled and packed.
     auto fetch_x = [&](uint4 (&dst)[NT][SLABS_PER_WARP], int chunk) {
         const int k_base = chunk * SK_KC + warp * SLABS_PER_WARP * 32 + 8 * t;
+        if (!NORM) {
+#pragma unroll
+            for (int u = 0; u < SLABS_PER_WARP; ++u)
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+                    dst[nt][u] = (k_base + u * 32 < p.K) ? load_x<false>(p, x_row[nt], k_base + u * 32, 1.f)
+                                                         : make_uint4(0, 0, 0, 0);
+            return;
+        }
+        float4 xa[NT][SLABS_PER_WARP], xb[NT][SLABS_PER_WARP];
+        float w[SLABS_PER_WARP][8];
+#pragma unroll
+        for (int u = 0; u < SLABS_PER_WARP; ++u) {
+            const int k = min(k_base + u * 32, p.K - 8);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                xa[nt][u] = __ldcg(reinterpret_cast<const float4*>((const float*)x_row[nt] + k));
+                xb[nt][u] = __ldcg(reinterpret_cast<const float4*>((const float*)x_row[nt] + k + 4));
+            }
+            if (p.norm_w_bf16) {
+                const uint4 wv = __ldg(reinterpret_cast<const uint4*>((const __nv_bfloat16*)p.norm_w + k));
+                const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    w[u][2 * i] = __low2float(w2[i]);
+                    w[u][2 * i + 1] = __high2float(w2[i]);
+                }
+            } else {
+                const float4 w0 = __ldg(reinterpret_cast<const float4*>((const float*)p.norm_w + k));
+                const float4 w1 = __ldg(reinterpret_cast<const float4*>((const float*)p.norm_w + k + 4));
+                w[u][0] = w0.x; w[u][1] = w0.y; w[u][2] = w0.z; w[u][3] = w0.w;
+                w[u][4] = w1.x; w[u][5] = w1.y; w[u][6] = w1.z; w[u][7] = w1.w;
+            }
+        }
 #pragma unroll
         for (int u = 0; u < SLABS_PER_WARP; ++u)
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
-                dst[nt][u] = (k_base + u * 32 < p.K) ? load_x<NORM>(p, x_row[nt], k_base + u * 32, scale[nt])
-                                                     : make_uint4(0, 0, 0, 0);
+            for (int nt = 0; nt < NT; ++nt) {
+                const float sc = scale[nt];
+                const float4 a = xa[nt][u], b = xb[nt][u];
+                __nv_bfloat162 o[4];
+                o[0] = __floats2bfloat162_rn(a.x * sc * w[u][0], a.y * sc * w[u][1]);
+                o[1] = __floats2bfloat162_rn(a.z * sc * w[u][2], a.w * sc * w[u][3]);
+                o[2] = __floats2bfloat162_rn(b.x * sc * w[u][4], b.y * sc * w[u][5]);
+                o[3] = __floats2bfloat162_rn(b.z * sc * w[u][6], b.w * sc * w[u][7]);
+                dst[nt][u] = (k_base + u * 32 < p.K) ? *reinterpret_cast<uint4*>(o) : make_uint4(0, 0, 0, 0);
+            }
     };
     auto multiply = [&](float (&acc)[NT][4], const uint4 (&x)[NT][SLABS_PER_WARP], int chunk, int it) {
         const int s = it % SK_STAGES;
@@ -303,6 +354,19 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(SkinnyParams
     int it = 0, blk_i = 0;
     for (int c = blockIdx.x; c < p.num_blocks; c += gridDim.x, ++blk_i) {
         const int row_lo = map_row<EPI>(p, c, g), row_hi = map_row<EPI>(p, c, g + 8);
+        // What the epilogue will read is requested now, so that its latency hides behind the
+        // product: the residual values of the two tokens this thread finishes (warps < NT only).
+        float x_lo[2] = {0.f, 0.f}, x_hi[2] = {0.f, 0.f};
+        if (EPI == EPI_ADD && warp < NT) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int tok = warp * 8 + 2 * t + e;
+                if (tok < p.M) {
+                    if (row_lo >= 0) x_lo[e] = __ldcg(p.resid + (size_t)tok * p.N + row_lo);
+                    if (row_hi >= 0) x_hi[e] = __ldcg(p.resid + (size_t)tok * p.N + row_hi);
+                }
+            }
+        }
         float acc[NT][4];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
@@ -361,12 +425,12 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(SkinnyParams
                 // the branch is rounded to bfloat16 first, as a separate product would store it
                 float* x = p.resid + (size_t)tok * p.N;
                 if (row_lo >= 0) {
-                    const float nx = x[row_lo] + __bfloat162float(__float2bfloat16_rn(lo));
+                    const float nx = x_lo[e] + __bfloat162float(__float2bfloat16_rn(lo));
                     x[row_lo] = nx;
                     ss[e] += nx * nx;
                 }
                 if (row_hi >= 0) {
-                    const float nx = x[row_hi] + __bfloat162float(__float2bfloat16_rn(hi));
+                    const float nx = x_hi[e] + __bfloat162float(__float2bfloat16_rn(hi));
                     x[row_hi] = nx;
                     ss[e] += nx * nx;
                 }
