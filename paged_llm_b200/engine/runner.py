@@ -76,7 +76,8 @@ class ModelRunner:
         self._host_ring: list = []
         self._ring_pos = 0
         self._dev_meta = None
-        self._graphs: dict[int, object] = {}
+        self._graphs: dict[tuple, object] = {}
+        self._portion_seen: dict[tuple, int] = {}
         self.use_graphs = (not config.enforce_eager) and self.device.type == "cuda" and getattr(ops, "supports_graphs", False)
         self.num_graph_steps = 0
         self.num_eager_steps = 0
@@ -255,8 +256,9 @@ class ModelRunner:
             if it.seq.state_slot is not None and it.seq.num_computed_tokens == 0:
                 self.storage.zero_state(it.seq.state_slot)
         override, self.next_ids_override = self.next_ids_override, None
-        if self._graph_eligible(items):
-            return self._graph_step(items, override)
+        key = self._graph_key(items)
+        if key is not None:
+            return self._graph_step(items, key, override)
         pk, host, info = self._gather(items)
         dev = self._upload(pk)
         self._override_ids(dev, override)
@@ -265,12 +267,32 @@ class ModelRunner:
         return self.model.forward(ctx)
 
     # ------------------------------------------------------------------ CUDA graphs for decode
-    def _graph_eligible(self, items: list[StepItem]) -> bool:
-        if not self.use_graphs or len(items) > self.GRAPH_BUCKETS[-1]:
-            return False
-        if self.cm.num_state_slots:
-            return False
-        return all(it.num_new_tokens == 1 and it.want == (0,) for it in items)
+    MAX_PORTION_GRAPHS = 4
+
+    def _graph_key(self, items: list[StepItem]):
+        """The captured graph this step can replay, or None.  Decode-only steps (every request
+        brings one token) replay a graph per batch-size bucket.  A step that is one portion of
+        one request replays a graph per portion length, captured when that length is the token
+        budget or comes a second time (a prompt cut by the budget brings the same length again
+        and again)."""
+        if not self.use_graphs or self.cm.num_state_slots:
+            return None
+        if all(it.num_new_tokens == 1 and it.want == (0,) for it in items):
+            if len(items) > self.GRAPH_BUCKETS[-1]:
+                return None
+            return ("decode", next(b for b in self.GRAPH_BUCKETS if b >= len(items)))
+        if len(items) == 1:
+            n, want = items[0].num_new_tokens, items[0].want
+            if n >= 64 and want in ((), (n - 1,)) and items[0].seq.num_computed_tokens + n <= self.config.max_model_len:
+                key = ("portion", n, len(want))
+                if key in self._graphs:
+                    return key
+                seen = self._portion_seen.get(key, 0) + 1
+                self._portion_seen[key] = seen
+                captured = sum(1 for k in self._graphs if k[0] == "portion")
+                if captured < self.MAX_PORTION_GRAPHS and (n == self.config.max_num_batched_tokens or seen >= 2):
+                    return key
+        return None
 
     def _table_stride(self) -> int:
         return _align(-(-self.config.max_model_len // self.page_size))
@@ -280,12 +302,12 @@ class ModelRunner:
         if ids is not None:
             dev[:ids.numel()].copy_(ids.to(torch.int32), non_blocking=True)     # "ids" is the first section
 
-    def _graph_step(self, items: list[StepItem], override: torch.Tensor | None = None) -> torch.Tensor:
-        B = next(b for b in self.GRAPH_BUCKETS if b >= len(items))
-        pk, host, info = self._gather(items, pad_to=B, table_stride=self._table_stride())
-        entry = self._graphs.get(B)
+    def _graph_step(self, items: list[StepItem], key, override: torch.Tensor | None = None):
+        pad = key[1] if key[0] == "decode" else None
+        pk, host, info = self._gather(items, pad_to=pad, table_stride=self._table_stride())
+        entry = self._graphs.get(key)
         if entry is None:
-            entry = self._capture(B, pk, host, info)
+            entry = self._capture(key, pk, host, info)
         dev, graph, logits, size, launches = entry
         if pk.size != size:
             raise RuntimeError("metadata layout changed between capture and replay")
@@ -294,9 +316,11 @@ class ModelRunner:
         graph.replay()
         self.num_graph_steps += 1
         self.graph_launches += launches
-        return logits[:len(items)]
+        if logits is None:
+            return None
+        return logits[:len(items)] if key[0] == "decode" else logits
 
-    def _capture(self, B: int, pk: _Packer, host: HostBatch, info: dict):
+    def _capture(self, key, pk: _Packer, host: HostBatch, info: dict):
         dev = torch.empty(pk.size, dtype=torch.int32, device=self.device)
         self._upload(pk, dev)
         ctx = self._context(pk, dev, host, info)
@@ -315,7 +339,7 @@ class ModelRunner:
         if hasattr(self.ops, "launches"):
             self.ops.launches = before        # capturing launches nothing; replays are counted in graph_launches
         entry = (dev, graph, logits, pk.size, launches)
-        self._graphs[B] = entry
+        self._graphs[key] = entry
         return entry
 
     # ------------------------------------------------------------------ scheduler-facing

@@ -88,3 +88,21 @@ def test_trace_run_program(folders, tmp_path):
     got = schedules.collect(steps, outputs)
     for rid, toks in reqs.items():
         assert_logits_close(got[rid], plain_logits(folders["A"], toks), "float32", f"trace_run/{rid}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_repeated_portions_replay_a_graph(folders, dtype):
+    """A prompt cut into equal portions: from the second portion on the step replays a captured
+    graph (other context lengths, same shapes) and still matches the plain logits."""
+    hf, _ = TINIES["C"]
+    toks = requests_for(hf["vocab_size"], (64 * 5 + 7,), seed=9)["r0"]
+    steps = []
+    for i in range(5):
+        steps.append({"step": i, "entries": [{"id": "a", "tokens": toks[64 * i:64 * (i + 1)], "want": [63]}], "end": []})
+    steps.append({"step": 5, "entries": [{"id": "a", "tokens": toks[320:], "want": list(range(7))}], "end": ["a"]})
+    outputs, rp = replay(folders["C"], dtype, steps, 384)
+    assert rp.runner.num_graph_steps == 4 and ("portion", 64, 1) in rp.runner._graphs
+    want = plain_logits(folders["C"], toks)
+    got = np.concatenate([outputs[i] for i in range(6)])
+    rows = [64 * i + 63 for i in range(5)] + list(range(320, 327))
+    assert_logits_close(got, want[rows], dtype, "portion graph")
