@@ -20,11 +20,11 @@ import numpy as np
 
 
 def wanted_splits(num_small: int, num_kv_heads: int, num_sms: int, max_splits: int) -> int:
-    """Splits per request so that requests x kv heads x splits is about two
-    thread blocks per SM."""
+    """Splits per request so that requests x kv heads x splits is about one
+    thread block per SM (measured: more splits cost more in merging than they win)."""
     if num_small <= 0:
         return 1
-    target_items = -(-2 * num_sms // max(num_kv_heads, 1))
+    target_items = -(-num_sms // max(num_kv_heads, 1))
     return int(min(max_splits, max(1, -(-target_items // num_small))))
 
 
