@@ -182,9 +182,10 @@ def test_paged_attention(ops, dtype, ps, nh, nkv, d, case):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("window", [1, 7, 16, 100])
-def test_paged_attention_window(ops, dtype, window):
+@pytest.mark.parametrize("nh,nkv,d", [(4, 2, 32), (8, 2, 64)])
+def test_paged_attention_window(ops, dtype, window, nh, nkv, d):
     ops.set_compute_dtype(dtype)
-    nh, nkv, d, ps = 4, 2, 32, 16
+    ps = 16
     q_lens, k_lens = [40, 1, 3, 90], [40, 300, 19, 200]
     q, kv, bt, keys, vals = paged_case(q_lens, k_lens, nh, nkv, d, ps, dtype, seed=window)
     # pages wholly behind the window are given back by the cache manager: poison their table entries
