@@ -72,3 +72,4 @@ class StepContext:
     max_q_len: int
     host: HostBatch
     attention_plans: dict = field(default_factory=dict)    # (group size, window) -> AttentionPlan
+    logits_all: bool = False        # logits are wanted at every token, in order (decode steps): no row gather

@@ -172,7 +172,7 @@ class ModelRunner:
             pk.add(f"large{key}", plan["large"])
             pk.add(f"splits{key}", plan["splits"])
         return pk, host, dict(T=T_pad, S=S_pad, L=len(want), L_pad=L_pad, strides=strides, plans=plans,
-                              max_q=max(q_lens))
+                              max_q=max(q_lens), logits_all=(L_pad == T_pad and want == list(range(len(want)))))
 
     def _table_row(self, seq: Sequence, g: int) -> np.ndarray:
         """The request's block table of group g as an array, rebuilt only when the cache
@@ -239,7 +239,7 @@ class ModelRunner:
             input_ids=view("ids"), positions=view("pos"), token_seq=view("tseq"), cu_seqlens_q=view("cu"),
             seq_lens_k=view("klen"), state_slots=view("slots"), logits_indices=view("lidx", max(info["L_pad"], 1)),
             block_tables=tables, layer_caches=self.storage.layer_caches, page_size=self.page_size,
-            max_q_len=info["max_q"], host=host, attention_plans=plans)
+            max_q_len=info["max_q"], host=host, attention_plans=plans, logits_all=info["logits_all"])
 
     # ------------------------------------------------------------------ the step
     @torch.no_grad()

@@ -110,6 +110,12 @@ class CausalLM:
         if ctx.num_logits == 0:
             return None
         ops = ctx.ops
+        if getattr(ctx, "logits_all", False):
+            # every row is wanted, in order: x may be finished in place, nothing to gather
+            h = self.final_norm.add_forward(x, pending, ctx)
+            if not self.head.accepts_lazy_input:
+                h = ops.materialize(h)
+            return self.head.forward(h, ctx)
         rows = ops.gather_rows(x, ctx.logits_indices)
         if pending is None:
             rows_pending = None
