@@ -43,7 +43,7 @@ if ROOT not in sys.path:
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 SIZES = {
-    # BASELINE.json configs[2]: TinyLlama 1.1B layer sizes
+    # TinyLlama 1.1B layer sizes (22 layers, 32 query / 4 kv heads of 64, hidden 2048, context 2048)
     "tinyllama-1.1b": dict(vocab_size=32000, hidden_size=2048, intermediate_size=5632, num_hidden_layers=22,
                            num_attention_heads=32, num_key_value_heads=4, head_dim=64, rope_theta=10000.0,
                            rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=2048),

@@ -412,3 +412,33 @@ def test_skinny_add_then_normalising_products(ops, M, N, K, wdtype):
         g, u = want[:, :88], want[:, 88:]
         torch.testing.assert_close(ops.gated_silu_linear(lazy, w2).float().cpu(), g * torch.sigmoid(g) * u, atol=4e-2, rtol=4e-2)
     assert ops.core.pl_gemm_skinny_timeouts() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d", [32, 64])
+def test_window_edge_is_exact(ops, dtype, d):
+    """Random scores would hide an off-by-one at the window's edge: put a key with an
+    overwhelming score just outside the window (it must change nothing) and one just inside
+    (it must take all the weight), for a decoded token and for rows of a prompt portion."""
+    ops.set_compute_dtype(dtype)
+    nh, nkv, ps, L, window = 4, 2, 16, 300, 37
+    for nq in (1, 40):
+        q, kv, bt, keys, vals = paged_case([nq], [L], nh, nkv, d, ps, dtype, seed=nq)
+        direction = torch.randn(d, generator=torch.Generator().manual_seed(2))
+        direction = (direction / direction.norm() * 40).to(dtype)
+        q[:] = direction
+        last = L - 1                               # position of the last query row
+        outside, inside = last - window, last - window + 1
+        for n, kdir in ((outside, direction * 2), (inside, direction)):
+            for h in range(nkv):
+                keys[0][n, h] = kdir.float()
+                kv[bt[0, n // ps], 0, h, n % ps] = kdir
+        ctx = make_ctx(ops, [nq], [L], nh, nkv, window, d)
+        qkv = torch.cat([q.reshape(-1, nh * d), torch.zeros(nq, 2 * nkv * d, dtype=dtype)], dim=1).cuda().contiguous()
+        out = ops.paged_attention(qkv, nh, nkv, d, kv.cuda(), bt.cuda(), ctx, d ** -0.5, window).float().cpu()
+        want_last = vals[0][inside].repeat_interleave(nh // nkv, dim=0).reshape(nh * d)
+        torch.testing.assert_close(out[-1], want_last, atol=2e-2, rtol=2e-2, msg=f"nq={nq}: the key at the edge")
+        qs = torch.zeros(L, nh, d)
+        qs[L - nq:] = q.float()
+        full = plain_llama.causal_attention(qs, keys[0], vals[0], d ** -0.5, window=window)[L - nq:].reshape(nq, nh * d)
+        torch.testing.assert_close(out, full, atol=2e-2, rtol=2e-2, msg=f"nq={nq}")
