@@ -51,6 +51,20 @@ class _Packer:
         self.size += _align(cap)
 
 
+class _Graph:
+    """A captured step: its metadata buffer on the device, the graph, its output, and the
+    packed metadata of the last replay (patched in place while the batch stays the same)."""
+
+    def __init__(self, dev, graph, logits, size, launches, bucket):
+        self.dev, self.graph, self.logits, self.size, self.launches, self.bucket = dev, graph, logits, size, launches, bucket
+        self.packed = None
+        self.offsets = None
+        self.seq_ids = None
+        self.versions = None
+        self.strides = None
+        self.plan_tag = None
+
+
 class _Staging:
     """One pinned host buffer of the metadata ring, with the event of its last copy."""
 
@@ -207,13 +221,7 @@ class ModelRunner:
             if self._dev_meta is None or self._dev_meta.numel() < pk.size:
                 self._dev_meta = torch.empty(max(pk.size * 2, 1 << 16), dtype=torch.int32, device=self.device)
             dev = self._dev_meta
-        dev[:pk.size].copy_(slot.tensor[:pk.size], non_blocking=True)
-        self.h2d_bytes += pk.size * 4
-        if self.device.type == "cuda":
-            if slot.event is None:
-                slot.event = torch.cuda.Event()
-            slot.event.record()
-            slot.busy = True
+        self._copy_up(slot, dev, pk.size)
         return dev
 
     def _context(self, pk: _Packer, dev: torch.Tensor, host: HostBatch, info: dict) -> StepContext:
@@ -303,24 +311,92 @@ class ModelRunner:
             dev[:ids.numel()].copy_(ids.to(torch.int32), non_blocking=True)     # "ids" is the first section
 
     def _graph_step(self, items: list[StepItem], key, override: torch.Tensor | None = None):
-        pad = key[1] if key[0] == "decode" else None
-        pk, host, info = self._gather(items, pad_to=pad, table_stride=self._table_stride())
         entry = self._graphs.get(key)
-        if entry is None:
-            entry = self._capture(key, pk, host, info)
-        dev, graph, logits, size, launches = entry
-        if pk.size != size:
-            raise RuntimeError("metadata layout changed between capture and replay")
-        self._upload(pk, dev)
-        self._override_ids(dev, override)
-        graph.replay()
+        if entry is not None and key[0] == "decode" and self._patch_decode(items, entry):
+            pass                                        # the packed metadata of the last step was patched in place
+        else:
+            pad = key[1] if key[0] == "decode" else None
+            pk, host, info = self._gather(items, pad_to=pad, table_stride=self._table_stride())
+            if entry is None:
+                entry = self._capture(key, pk, host, info)
+            if pk.size != entry.size:
+                raise RuntimeError("metadata layout changed between capture and replay")
+            packed = np.zeros(pk.size, np.int32)
+            for _, off, data in pk.sections:
+                packed[off:off + data.size] = data
+            entry.packed = packed
+            entry.offsets = {name: off for name, off, _ in pk.sections}
+            entry.seq_ids = tuple(it.seq.seq_id for it in items)
+            entry.versions = [it.seq.table_version for it in items]
+            entry.strides = info["strides"]
+            entry.plan_tag = None
+        slot = self._host_buffer(entry.size)
+        slot.array[:entry.size] = entry.packed
+        self._copy_up(slot, entry.dev, entry.size)
+        self._override_ids(entry.dev, override)
+        entry.graph.replay()
         self.num_graph_steps += 1
-        self.graph_launches += launches
-        if logits is None:
+        self.graph_launches += entry.launches
+        if entry.logits is None:
             return None
-        return logits[:len(items)] if key[0] == "decode" else logits
+        return entry.logits[:len(items)] if key[0] == "decode" else entry.logits
 
-    def _capture(self, key, pk: _Packer, host: HostBatch, info: dict):
+    def _patch_decode(self, items: list[StepItem], entry) -> bool:
+        """Steady decoding: the same requests as in the last replay of this graph, one token
+        further.  Only what moved is rewritten in the packed metadata: token ids, positions,
+        context lengths, block-table rows that the cache manager changed, and the attention
+        work lists.  Returns False if the batch is another one (the caller gathers anew)."""
+        if entry.packed is None or entry.seq_ids != tuple(it.seq.seq_id for it in items):
+            return False
+        S = len(items)
+        starts = [it.seq.num_computed_tokens for it in items]
+        try:
+            ids = [it.seq.token_ids[st] for it, st in zip(items, starts)]
+        except IndexError:
+            raise ValueError("a request has no token at the position this step asks for") from None
+        buf, off = entry.packed, entry.offsets
+        buf[off["ids"]:off["ids"] + S] = ids
+        buf[off["pos"]:off["pos"] + S] = starts
+        klen = [st + 1 for st in starts]
+        buf[off["klen"]:off["klen"] + S] = klen
+        for s, it in enumerate(items):
+            if it.seq.table_version != entry.versions[s]:
+                entry.versions[s] = it.seq.table_version
+                for g, stride in enumerate(entry.strides):
+                    row = self._table_row(it.seq, g)
+                    if len(row) > stride:
+                        raise ValueError("block table longer than the captured stride")
+                    o = off[f"bt{g}"] + s * stride
+                    buf[o:o + len(row)] = row
+                    buf[o + len(row):o + stride] = 0
+        # the work lists change only when a context grows past another multiple of the split size
+        step_keys = getattr(self.ops, "MIN_SPLIT_KEYS", 128)
+        windowed = any(key[2] for key in self.plan_keys)
+        tag = None if windowed else tuple(-(-k // step_keys) for k in klen)
+        if tag is None or tag != entry.plan_tag:
+            entry.plan_tag = tag
+            ones = [1] * S
+            for key in self.plan_keys:
+                plan = self.ops.plan_attention(ones, klen, *key, pad_requests=entry.bucket, fixed_capacity=True)
+                for name in ("small", "large", "splits"):
+                    data = plan[name]
+                    o = off[f"{name}{key}"]
+                    buf[o:o + data.size] = data
+        return True
+
+    def _copy_up(self, slot: "_Staging", dev: torch.Tensor, n: int) -> None:
+        if hasattr(self.ops, "copy_h2d"):
+            self.ops.copy_h2d(dev, slot.tensor, n * 4)
+        else:
+            dev[:n].copy_(slot.tensor[:n], non_blocking=True)
+        self.h2d_bytes += n * 4
+        if self.device.type == "cuda":
+            if slot.event is None:
+                slot.event = torch.cuda.Event()
+            slot.event.record()
+            slot.busy = True
+
+    def _capture(self, key, pk: _Packer, host: HostBatch, info: dict) -> "_Graph":
         dev = torch.empty(pk.size, dtype=torch.int32, device=self.device)
         self._upload(pk, dev)
         ctx = self._context(pk, dev, host, info)
@@ -338,7 +414,7 @@ class ModelRunner:
         launches = getattr(self.ops, "launches", 0) - before
         if hasattr(self.ops, "launches"):
             self.ops.launches = before        # capturing launches nothing; replays are counted in graph_launches
-        entry = (dev, graph, logits, pk.size, launches)
+        entry = _Graph(dev, graph, logits, pk.size, launches, key[1] if key[0] == "decode" else None)
         self._graphs[key] = entry
         return entry
 

@@ -126,6 +126,10 @@ class CudaOps:
         except KeyError:
             raise KernelError(f"tensor of dtype {t.dtype} where float32 or bfloat16 is expected") from None
 
+    def copy_h2d(self, dst: torch.Tensor, src: torch.Tensor, nbytes: int) -> None:
+        """Asynchronous copy of `nbytes` from pinned host memory to the device on the current stream."""
+        _check(self.core, self.core.pl_copy_h2d(self._p(dst), self._p(src), c_longlong(nbytes), self._stream))
+
     # ---- embedding, norms, activation ------------------------------------------
     def embedding(self, table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
         T, (V, H) = ids.numel(), table.shape
