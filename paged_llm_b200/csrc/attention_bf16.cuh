@@ -69,7 +69,8 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
     constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
     pdl_launch_dependents();
     pdl_wait();
-    const AttnItem it = attn_decode_item(p, blockIdx.x, BM, BN);
+    const AttnItem it = attn_decode_item(p, blockIdx.x / p.nkv, BM, BN);     // kv heads of an item side by side:
+                                                                                // the list's longest-first order holds over heads
     if (!it.valid) return;
 
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -79,7 +80,7 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wm = warp % MW, wn = warp / MW;
-    const int d = p.d, kvh = blockIdx.y, G = p.nh / p.nkv;
+    const int d = p.d, kvh = blockIdx.x % p.nkv, G = p.nh / p.nkv;
     const __nv_bfloat16* q = (const __nv_bfloat16*)p.q;
     const __nv_bfloat16* kv = (const __nv_bfloat16*)p.kv;
     const int* bt = p.block_table + (size_t)it.seq * p.bt_stride;
@@ -371,7 +372,7 @@ int launch_attn_bf16(const AttnParams& p, cudaStream_t stream) {
                                      Shape::SMEM_BYTES));
         attr_set = true;
     }
-    PL_CUDA(launch_pdl(attn_bf16_kernel<DPAD, MW, NW, KPW>, dim3(p.n_work, p.nkv), dim3(Shape::THREADS),
+    PL_CUDA(launch_pdl(attn_bf16_kernel<DPAD, MW, NW, KPW>, dim3(p.n_work * p.nkv), dim3(Shape::THREADS),
                        (size_t)Shape::SMEM_BYTES, stream, p));
     return 0;
 }
@@ -386,6 +387,9 @@ PL_EXPORT int pl_attention_tc_timeouts() {
     if (cudaMemcpyFromSymbol(&n, tc::g_timeouts, sizeof(int)) != cudaSuccess) return -1;
     return n;
 }
+#ifdef PL_TC2_PROF
+PL_EXPORT int pl_attention_tc_prof(unsigned long long* out) { return tc2::read_prof(out); }
+#endif
 #endif
 
 #define PL_CAT_(a, b) a##b
@@ -408,7 +412,8 @@ PL_EXPORT int PL_CAT(pl_attention_bf16_d, PL_DPAD)(const AttnParams* params, cud
 #if PL_DPAD == 64
     // prefill tiles of head size 64 run on tcgen05 with tensor-memory accumulators
     static const bool no_tc = getenv("PAGED_LLM_B200_NO_TCGEN05") != nullptr;
-    if (p.d == 64 && !no_tc) return tc::launch(p, stream);
+    static const bool serial_tc = getenv("PAGED_LLM_B200_TC_SERIAL") != nullptr;     // the block-synchronous variant
+    if (p.d == 64 && !no_tc) return serial_tc || !tc2::takes(p) ? tc::launch(p, stream) : tc2::launch(p, stream);
 #endif
     return launch_attn_bf16<PL_DPAD, PL_LARGE_MW, 1, 64>(p, stream);
 }

@@ -9,10 +9,10 @@ constexpr int F32_MAXD = 256;
 
 // grid: (items, kv heads); 128 threads = 4 warps, each owning 4 of the 16 rows.
 __global__ void __launch_bounds__(128) attn_f32_kernel(AttnParams p) {
-    const AttnItem it = attn_decode_item(p, blockIdx.x, F32_ROWS, F32_KEYS);
+    const AttnItem it = attn_decode_item(p, blockIdx.x / p.nkv, F32_ROWS, F32_KEYS);
     if (!it.valid) return;
     extern __shared__ float smem[];
-    const int d = p.d, kvh = blockIdx.y, G = p.nh / p.nkv;
+    const int d = p.d, kvh = blockIdx.x % p.nkv, G = p.nh / p.nkv;
     float* Qs = smem;                          // [16][d]
     float* Ks = Qs + F32_ROWS * d;             // [32][d + 1]
     float* Vs = Ks + F32_KEYS * (d + 1);       // [32][d]
@@ -170,7 +170,7 @@ PL_EXPORT int pl_attention_f32(const AttnParams* params, cudaStream_t stream) {
         PL_CUDA(cudaFuncSetAttribute(attn_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
         attr_set = true;
     }
-    attn_f32_kernel<<<dim3(p.n_work, p.nkv), 128, smem, stream>>>(p);
+    attn_f32_kernel<<<dim3(p.n_work * p.nkv), 128, smem, stream>>>(p);
     PL_LAUNCHED("attention_f32");
     return 0;
 }

@@ -25,6 +25,12 @@
 // accumulator; P rounded to bfloat16 for the second product.
 #pragma once
 
+#include <cuda.h>
+
+#include <mutex>
+#include <utility>
+#include <vector>
+
 #include "attention_common.cuh"
 
 namespace tc {
@@ -137,7 +143,7 @@ __device__ __forceinline__ int swz(int r, int c) { return r * 128 + ((c ^ (r & 7
 __global__ void __launch_bounds__(THREADS, 2) attn_tc_kernel(AttnParams p) {
     pdl_launch_dependents();
     pdl_wait();
-    const AttnItem it = attn_decode_item(p, blockIdx.x, BM, BN);
+    const AttnItem it = attn_decode_item(p, blockIdx.x / p.nkv, BM, BN);
     if (!it.valid) return;
 
     extern __shared__ unsigned char smem_unaligned[];
@@ -150,7 +156,7 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_kernel(AttnParams p) {
     __shared__ uint32_t tmem_base_slot;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int kvh = blockIdx.y, G = p.nh / p.nkv;
+    const int kvh = blockIdx.x % p.nkv, G = p.nh / p.nkv;
     const __nv_bfloat16* q = (const __nv_bfloat16*)p.q;
     const __nv_bfloat16* kv = (const __nv_bfloat16*)p.kv;
     const int* bt = p.block_table + (size_t)it.seq * p.bt_stride;
@@ -387,8 +393,445 @@ inline int launch(const AttnParams& p, cudaStream_t stream) {
                                      (int)cudaSharedmemCarveoutMaxShared));
         attr_set = true;
     }
-    PL_CUDA(launch_pdl(attn_tc_kernel, dim3(p.n_work, p.nkv), dim3(THREADS), (size_t)SMEM_BYTES, stream, p));
+    PL_CUDA(launch_pdl(attn_tc_kernel, dim3(p.n_work * p.nkv), dim3(THREADS), (size_t)SMEM_BYTES, stream, p));
     return 0;
 }
 
 }  // namespace tc
+
+// ---------------------------------------------------------------------------------------------
+// The same attention with the phases of a block running side by side instead of one after the
+// other.  Warps have roles: four softmax warps (one thread per query row, the whole row of 64
+// scores in registers), one warp that issues the tensor-core products, two warps that bring keys
+// and values in with TMA: the pool of one layer is a 2-D tensor [pages * 2 * kv_heads *
+// page_size, 64] whose rows are 128 bytes, a box is the rows of one page (at most 64) and lands in
+// shared memory in the 128-byte swizzle the products read.  Scores are double-buffered in tensor
+// memory (two tiles of 64 keys), P in shared memory, keys and values in rings of three stages each;
+// everything is handed over through mbarriers:
+//   k_full[s], v_full[s]    the boxes of a stage of keys / values have landed (TMA complete_tx)
+//   k_empty[s], v_empty[s]  the product reading the stage is done              (tcgen05.commit)
+//   s_full[b]    S[b] = Q K^T is in tensor memory        (tcgen05.commit)
+//   s_free[b]    the softmax has read S[b]               (softmax threads)
+//   p_full[b]    P[b] is in shared memory, O is rescaled, stray value rows are zeroed (softmax threads)
+//   pv_done[b]   O += P[b] V is done                     (tcgen05.commit)
+// The product warp issues S(t+2) before P(t) V(t), so the tensor cores work on the scores to come
+// while the softmax warps work on the current ones.  Key tiles start at multiples of 64 so that a
+// box never straddles a page; keys outside the block's range are masked by position, and their
+// value rows are zeroed in shared memory (a page may hold anything behind the last token).
+// Needs a page size that is a power of two >= 8; other page sizes run the kernel above.
+namespace tc2 {
+
+using tc::saddr;
+using tc::mbar_init;
+using tc::mbar_wait;
+using tc::smem_desc;
+using tc::instr_desc;
+using tc::mma_f16;
+using tc::mma_commit;
+using tc::fence_before_sync;
+using tc::fence_after_sync;
+using tc::fence_async_smem;
+using tc::tmem_st32;
+using tc::tmem_st_wait;
+using tc::ex2;
+using tc::swz;
+
+// #define PL_TC2_PROF 1   // TEMPORARY
+#ifdef PL_TC2_PROF
+__device__ unsigned long long g_prof[32];
+#define PROF_DECL long long pt_ = clock64(); const bool prof_ = blockIdx.x == 0 && (threadIdx.x & 31) == 0; unsigned long long pacc_[10] = {0,0,0,0,0,0,0,0,0,0};
+#define PROF(i) { long long n_ = clock64(); pacc_[i] += n_ - pt_; pt_ = n_; }
+#define PROF_SET(i, v) pacc_[i] = (v);
+#define PROF_FLUSH(base, n) if (prof_) for (int i_ = 0; i_ < n; ++i_) atomicAdd(&g_prof[base + i_], pacc_[i_]);
+#else
+#define PROF_DECL
+#define PROF(i)
+#define PROF_SET(i, v)
+#define PROF_FLUSH(base, n)
+#endif
+
+constexpr int BM = 128, BN = 64, D = 64, STAGES = 3;
+constexpr int SOFTMAX_WARPS = 4, MMA_WARP = 4, K_WARP = 5, V_WARP = 6;
+constexpr int THREADS = (SOFTMAX_WARPS + 3) * 32;                   // 224
+constexpr int TMEM_COLS = 256;               // S0: 0..63, S1: 64..127, O: 128..191
+constexpr float LAZY_LOG2 = 8.f;
+constexpr int Q_BYTES = BM * 128, K_BYTES = BN * 128, P_BYTES = BM * 128;
+constexpr int SMEM_BYTES = Q_BYTES + 2 * STAGES * K_BYTES + 2 * P_BYTES + 1024;
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(saddr(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(saddr(bar)), "r"(bytes) : "memory");
+}
+// One box of the tensor map at rows [row, row + box rows), all 64 columns, to shared memory;
+// the bytes are counted on `bar`.
+__device__ __forceinline__ void tma_box(void* dst, const CUtensorMap* map, int row, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::
+            "r"(saddr(dst)), "l"(map), "r"(0), "r"(row), "r"(saddr(bar))
+        : "memory");
+}
+// 64 columns of this thread's lane of tensor memory, one wait for both halves.
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&v)[64]) {
+    uint32_t r[64];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        uint32_t* q = r + 32 * h;
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+            : "=r"(q[0]), "=r"(q[1]), "=r"(q[2]), "=r"(q[3]), "=r"(q[4]), "=r"(q[5]), "=r"(q[6]), "=r"(q[7]), "=r"(q[8]),
+              "=r"(q[9]), "=r"(q[10]), "=r"(q[11]), "=r"(q[12]), "=r"(q[13]), "=r"(q[14]), "=r"(q[15]), "=r"(q[16]),
+              "=r"(q[17]), "=r"(q[18]), "=r"(q[19]), "=r"(q[20]), "=r"(q[21]), "=r"(q[22]), "=r"(q[23]), "=r"(q[24]),
+              "=r"(q[25]), "=r"(q[26]), "=r"(q[27]), "=r"(q[28]), "=r"(q[29]), "=r"(q[30]), "=r"(q[31])
+            : "r"(taddr + 32 * h));
+    }
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, const __grid_constant__ CUtensorMap kv_map) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const AttnItem it = attn_decode_item(p, blockIdx.x / p.nkv, BM, BN);
+    if (!it.valid) return;
+
+    extern __shared__ unsigned char smem_unaligned[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_unaligned + 1023) & ~(uintptr_t)1023);
+    unsigned char* Qs = smem;                                  // [128][128 B]
+    unsigned char* Ks = Qs + Q_BYTES;                          // [STAGES][64 keys][128 B]
+    unsigned char* Vs = Ks + STAGES * K_BYTES;                 // [STAGES][64 keys][128 B]
+    unsigned char* Ps = Vs + STAGES * K_BYTES;                 // [2][128][128 B]
+    __shared__ uint64_t k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
+    __shared__ uint64_t s_full[2], s_free[2], p_full[2], pv_done[2];
+    __shared__ uint32_t tmem_base_slot;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int kvh = blockIdx.x % p.nkv, G = p.nh / p.nkv;
+    const __nv_bfloat16* q = (const __nv_bfloat16*)p.q;
+    const int key0 = it.key_lo & ~(BN - 1);                    // tiles start at multiples of 64
+    const int n_tiles = (it.key_hi - key0 + BN - 1) / BN;
+
+    if (warp == MMA_WARP) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(saddr(&tmem_base_slot)),
+                     "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    }
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&k_full[s], 1);
+            mbar_init(&k_empty[s], 1);
+            mbar_init(&v_full[s], 1);
+            mbar_init(&v_empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&s_full[b], 1);
+            mbar_init(&s_free[b], SOFTMAX_WARPS * 32);
+            mbar_init(&p_full[b], SOFTMAX_WARPS * 32);
+            mbar_init(&pv_done[b], 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    // Q tile: row R = token * G + head; eight 16-byte chunks per row
+    for (int e = tid; e < BM * 8; e += THREADS) {
+        const int r = e >> 3, c = e & 7;
+        const int R = it.row_base + r;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (R < it.rows_total)
+            v = *reinterpret_cast<const uint4*>(q + (size_t)(it.q0 + R / G) * p.q_stride + (kvh * G + R % G) * D + c * 8);
+        *reinterpret_cast<uint4*>(Qs + swz(r, c)) = v;
+    }
+    fence_async_smem();
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp >= K_WARP) {
+        // ---------------------------------------------------------------- copy warps (keys, values): lane i brings box i
+        const bool values = warp == V_WARP;
+        const int* bt = p.block_table + (size_t)it.seq * p.bt_stride;
+        const int box_rows = min(p.ps, BN), boxes = BN / box_rows;
+        const uint32_t box_bytes = box_rows * 128;
+        const int row_add = values ? p.nkv * p.ps : 0;         // rows from a page's keys to its values
+        unsigned char* ring = values ? Vs : Ks;
+        uint64_t* full = values ? v_full : k_full;
+        uint64_t* empty = values ? v_empty : k_empty;
+        auto page_of = [&](int t) {                             // page of this lane's box of tile t, or -1
+            const int n0 = key0 + t * BN + lane * box_rows;
+            if (t >= n_tiles || lane >= boxes || n0 >= it.key_hi || n0 + box_rows <= it.key_lo) return -1;
+            return bt[n0 >> p.ps_shift];
+        };
+        PROF_DECL
+        int pg_next = page_of(0);
+        for (int t = 0; t < n_tiles; ++t) {
+            const int s = t % STAGES;
+            const int pg = pg_next;
+            pg_next = page_of(t + 1);
+            PROF(0)
+            if (t >= STAGES) mbar_wait(&empty[s], ((t / STAGES) - 1) & 1);
+            PROF(1)
+            const bool ok = pg >= 0;
+            const int n_ok = __popc(__ballot_sync(0xffffffffu, ok));
+            if (lane == 0) mbar_arrive_expect(&full[s], n_ok * box_bytes);
+            __syncwarp();
+            if (ok) {
+                const int n0 = key0 + t * BN + lane * box_rows;
+                const int row = (pg * 2 * p.nkv + kvh) * p.ps + (n0 & (p.ps - 1)) + row_add;
+                tma_box(ring + s * K_BYTES + lane * box_bytes, &kv_map, row, &full[s]);
+            }
+            PROF(2)
+        }
+        if (!values) { PROF_FLUSH(16, 3) }
+    } else if (warp == MMA_WARP) {
+        // ---------------------------------------------------------------- product warp: one thread issues
+        if (lane == 0) {
+            constexpr uint32_t IDESC_S = instr_desc(BM, BN, false), IDESC_O = instr_desc(BM, D, true);
+            const uint32_t qa = saddr(Qs);
+            PROF_DECL
+            auto issue_s = [&](int t) {                     // S[t & 1] = Q K(t)^T
+                const int b = t & 1, s = t % STAGES;
+                mbar_wait(&k_full[s], (t / STAGES) & 1);
+                PROF(0)
+                if (t >= 2) mbar_wait(&s_free[b], ((t - 2) >> 1) & 1);
+                PROF(1)
+                fence_after_sync();
+                const uint32_t ka = saddr(Ks + s * K_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk)
+                    mma_f16(tmem_base + b * 64, smem_desc(qa + kk * 32, 16, 1024), smem_desc(ka + kk * 32, 16, 1024),
+                            IDESC_S, kk > 0);
+                mma_commit(&s_full[b]);
+                mma_commit(&k_empty[s]);
+                PROF(2)
+            };
+            // Scores run two tiles ahead of the second product: S(u + 2) is issued as soon as the
+            // softmax has taken S(u) into registers, long before it hands P(u) over.
+            if (n_tiles > 0) issue_s(0);
+            if (n_tiles > 1) issue_s(1);
+            for (int u = 0; u < n_tiles; ++u) {
+                const int bu = u & 1, su = u % STAGES;
+                if (u + 2 < n_tiles) issue_s(u + 2);
+                mbar_wait(&v_full[su], (u / STAGES) & 1);
+                mbar_wait(&p_full[bu], (u >> 1) & 1);
+                PROF(3)
+                fence_after_sync();
+                const uint32_t pa = saddr(Ps + bu * P_BYTES), va = saddr(Vs + su * K_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; ++kk)
+                    mma_f16(tmem_base + 128, smem_desc(pa + kk * 32, 16, 1024), smem_desc(va + kk * 2048, 16, 1024),
+                            IDESC_O, u > 0 || kk > 0);
+                mma_commit(&pv_done[bu]);
+                mma_commit(&v_empty[su]);
+                PROF(4)
+            }
+            PROF_FLUSH(10, 5)
+        }
+        __syncwarp();
+    } else {
+        // ---------------------------------------------------------------- softmax warps: one thread per row
+        const int r = tid;
+        const int R = it.row_base + r;
+        const int pos = R < it.rows_total ? it.lk - it.nq + R / G : -1;
+        const uint32_t tmem_row = tmem_base + ((uint32_t)(warp * 32) << 16);
+        const uint32_t tmem_o = tmem_row + 128;
+        const float scale_log2 = p.scale * 1.4426950408889634f;
+        float m_run = -INFINITY, l_run = 0.f;
+        float sv[64];
+        PROF_DECL
+        for (int t = 0; t < n_tiles; ++t) {
+            const int b = t & 1;
+            mbar_wait(&s_full[b], (t >> 1) & 1);
+            __syncwarp();
+            fence_after_sync();
+            PROF(0)
+            tmem_ld64(tmem_row + b * 64, sv);
+            // S[b] is in registers: the product warp may overwrite it
+            fence_before_sync();
+            mbar_arrive(&s_free[b]);
+            const int kbase = key0 + t * BN;
+            const bool row_full = p.window <= 0 && kbase >= it.key_lo && kbase + BN <= it.key_hi && kbase + BN - 1 <= pos;
+            const bool warp_full = __all_sync(0xffffffffu, row_full);
+            if (!warp_full) {
+#pragma unroll
+                for (int i = 0; i < 64; ++i) {
+                    const int n = kbase + i;
+                    const bool vis = n >= it.key_lo && n < it.key_hi && n <= pos && (p.window <= 0 || n > pos - p.window);
+                    sv[i] = vis ? sv[i] : -INFINITY;
+                }
+            }
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int i = 0; i < 64; ++i) mx[i & 3] = fmaxf(mx[i & 3], sv[i]);
+            const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;
+            // The reference maximum moves only when the tile's maximum exceeds it by more than 2^8:
+            // P stays below 256, exact enough in bfloat16 and float32, and O is seldom rescaled.
+            const bool changed = m_tile > m_run + LAZY_LOG2;
+            const float alpha = !changed ? 1.f : m_run == -INFINITY ? 0.f : ex2(m_run - m_tile);
+            if (changed) m_run = m_tile;
+            const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
+            PROF(1)
+            // P(t-2) must have been consumed before its buffer is written again
+            if (t >= 2) {
+                mbar_wait(&pv_done[b], ((t - 2) >> 1) & 1);
+                __syncwarp();
+            }
+            PROF(2)
+            unsigned char* prow = Ps + b * P_BYTES;
+            float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                uint32_t packed[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    // a masked score is -inf: fma gives -inf and the exponential 0
+                    const float p0 = ex2(fmaf(sv[c * 8 + 2 * i], scale_log2, neg_m));
+                    const float p1 = ex2(fmaf(sv[c * 8 + 2 * i + 1], scale_log2, neg_m));
+                    ls[i] += p0 + p1;
+                    __nv_bfloat162 bb = __floats2bfloat162_rn(p0, p1);
+                    packed[i] = *reinterpret_cast<uint32_t*>(&bb);
+                }
+                *reinterpret_cast<uint4*>(prow + swz(r, c)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            }
+            l_run = l_run * alpha + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
+            PROF(3)
+            // O is rescaled once the product of the tile before is done
+            if (t >= 1 && __any_sync(0xffffffffu, changed)) {
+                mbar_wait(&pv_done[b ^ 1], ((t - 1) >> 1) & 1);
+                __syncwarp();
+                fence_after_sync();
+                PROF(4)
+                {
+                    tmem_ld64(tmem_o, sv);
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) sv[i] *= alpha;
+                    tmem_st32(tmem_o, reinterpret_cast<const float(&)[32]>(sv[0]));
+                    tmem_st32(tmem_o + 32, reinterpret_cast<const float(&)[32]>(sv[32]));
+                    tmem_st_wait();
+                }
+                PROF(5)
+            }
+            if (kbase < it.key_lo || kbase + BN > it.key_hi) {
+                // Value rows of keys outside the range are zeroed, so that 0 * anything stays 0 (a
+                // page may hold anything behind the last token).
+                mbar_wait(&v_full[t % STAGES], (t / STAGES) & 1);
+                unsigned char* vd = Vs + (t % STAGES) * K_BYTES;
+                for (int e = tid; e < BN * 8; e += SOFTMAX_WARPS * 32) {
+                    const int n = kbase + (e >> 3);
+                    if (n < it.key_lo || n >= it.key_hi) *reinterpret_cast<uint4*>(vd + e * 16) = make_uint4(0, 0, 0, 0);
+                }
+            }
+            fence_async_smem();                                      // generic stores -> tensor-core reads
+            fence_before_sync();
+            mbar_arrive(&p_full[b]);
+            PROF(6)
+        }
+        PROF_SET(9, n_tiles)
+        if (tid == 0) { PROF_FLUSH(0, 10) }
+        if (n_tiles > 0) {
+            const int last = n_tiles - 1;
+            mbar_wait(&pv_done[last & 1], (last >> 1) & 1);
+            __syncwarp();
+            fence_after_sync();
+            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+            tmem_ld64(tmem_o, sv);
+            if (pos >= 0) {
+                const int tok = R / G, head = kvh * G + R % G;
+                __nv_bfloat16* o_row = (__nv_bfloat16*)p.out + (size_t)(it.q0 + tok) * p.out_stride + head * D;
+#pragma unroll
+                for (int c8 = 0; c8 < 8; ++c8) {
+                    __nv_bfloat162 bb[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        bb[i] = __floats2bfloat162_rn(sv[c8 * 8 + 2 * i] * inv, sv[c8 * 8 + 2 * i + 1] * inv);
+                    *reinterpret_cast<uint4*>(o_row + c8 * 8) = *reinterpret_cast<uint4*>(bb);
+                }
+            }
+        }
+    }
+    fence_before_sync();
+    __syncthreads();
+    if (warp == MMA_WARP)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS));
+}
+
+// The tensor map of one layer of a pool: rows of 64 bfloat16, boxes of min(page size, 64) rows,
+// 128-byte swizzle.  Made once per (address, shape) and kept.
+struct MapKey {
+    const void* kv;
+    int pages, nkv, ps;
+    bool operator==(const MapKey& o) const { return kv == o.kv && pages == o.pages && nkv == o.nkv && ps == o.ps; }
+};
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline const CUtensorMap* kv_tensor_map(const AttnParams& p) {
+    static std::mutex mu;
+    static std::vector<std::pair<MapKey, CUtensorMap*>> maps;
+    static EncodeTiledFn encode = nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    const MapKey key{p.kv, p.num_pages, p.nkv, p.ps};
+    for (auto& m : maps)
+        if (m.first == key) return m.second;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &res) != cudaSuccess ||
+            res != cudaDriverEntryPointSuccess || !fn) {
+            pl_fail("tcgen05 attention: the driver has no cuTensorMapEncodeTiled");
+            return nullptr;
+        }
+        encode = (EncodeTiledFn)fn;
+    }
+    void* mem = nullptr;
+    if (posix_memalign(&mem, 64, sizeof(CUtensorMap)) != 0) {
+        pl_fail("tcgen05 attention: out of host memory");
+        return nullptr;
+    }
+    CUtensorMap* map = (CUtensorMap*)mem;
+    const cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)p.num_pages * 2 * p.nkv * p.ps};
+    const cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)D, (cuuint32_t)(p.ps < BN ? p.ps : BN)};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult rc = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(p.kv), dims, strides, box, estr,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) {
+        free(mem);
+        pl_fail("tcgen05 attention: cuTensorMapEncodeTiled failed (%d)", (int)rc);
+        return nullptr;
+    }
+    maps.emplace_back(key, map);
+    return map;
+}
+
+// Whether this kernel takes the call: a page is a power of two of at least 8 tokens and the
+// pool's row numbers fit the 32-bit coordinates of a box.
+inline bool takes(const AttnParams& p) {
+    return p.ps_shift >= 3 && p.num_pages > 0 && (long long)p.num_pages * 2 * p.nkv * p.ps < (1ll << 31) &&
+           ((uintptr_t)p.kv & 15) == 0;
+}
+
+inline int launch(const AttnParams& p, cudaStream_t stream) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        PL_CUDA(cudaFuncSetAttribute(attn_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        PL_CUDA(cudaFuncSetAttribute(attn_tc2_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                     (int)cudaSharedmemCarveoutMaxShared));
+        attr_set = true;
+    }
+    const CUtensorMap* map = kv_tensor_map(p);
+    if (!map) return 1;
+    PL_CUDA(launch_pdl(attn_tc2_kernel, dim3(p.n_work * p.nkv), dim3(THREADS), (size_t)SMEM_BYTES, stream, p, *map));
+    return 0;
+}
+
+#ifdef PL_TC2_PROF
+inline int read_prof(unsigned long long* out) {
+    return cudaMemcpyFromSymbol(out, g_prof, sizeof(g_prof)) == cudaSuccess ? 0 : -1;
+}
+#endif
+}  // namespace tc2

@@ -113,4 +113,5 @@ struct AttnParams {
     int ps_shift;           // log2(ps) if ps is a power of two, else -1
     unsigned int* counters; // [requests * kv_heads] zeros, or null: the block of a request's kv head that
                             // finishes last merges the splits itself (no separate merge kernel)
+    int num_pages;          // pages in `kv` (0: unknown; kernels that need it step aside)
 };

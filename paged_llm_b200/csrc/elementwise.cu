@@ -173,6 +173,37 @@ PL_EXPORT int pl_rmsnorm(float* x, const void* branch, int branch_dtype, const v
 }
 
 // ------------------------------------------------------------------ SiLU * mul
+// 16-byte vectors of T as floats.
+template <typename T> struct Vec16 {};
+template <> struct Vec16<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
+        const float4 a = *reinterpret_cast<const float4*>(p);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[8]) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+template <> struct Vec16<__nv_bfloat16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[2 * i] = __low2float(h[i]);
+            v[2 * i + 1] = __high2float(h[i]);
+        }
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+        __nv_bfloat162 h[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        *reinterpret_cast<uint4*>(p) = *reinterpret_cast<uint4*>(h);
+    }
+};
+
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, int vec) {
     const size_t r = blockIdx.y;
@@ -180,11 +211,15 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
     const T* u = g + I;
     T* o = out + r * I;
     if (vec) {
+        constexpr int N = Vec16<T>::N;
 #pragma unroll 2
-        for (int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4; c < I; c += gridDim.x * blockDim.x * 4) {
-            const float4 gv = Vec4<T>::load(g + c), uv = Vec4<T>::load(u + c);
-            Vec4<T>::store(o + c, make_float4(gv.x / (1.0f + expf(-gv.x)) * uv.x, gv.y / (1.0f + expf(-gv.y)) * uv.y,
-                                              gv.z / (1.0f + expf(-gv.z)) * uv.z, gv.w / (1.0f + expf(-gv.w)) * uv.w));
+        for (int c = (blockIdx.x * blockDim.x + threadIdx.x) * N; c < I; c += gridDim.x * blockDim.x * N) {
+            float gv[8], uv[8], ov[8];
+            Vec16<T>::load(g + c, gv);
+            Vec16<T>::load(u + c, uv);
+#pragma unroll
+            for (int i = 0; i < N; ++i) ov[i] = gv[i] / (1.0f + expf(-gv[i])) * uv[i];
+            Vec16<T>::store(o + c, ov);
         }
         return;
     }
@@ -197,9 +232,10 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
 PL_EXPORT int pl_silu_mul(const void* gate_up, void* out, int dtype, int rows, int I, cudaStream_t stream) {
     if (rows == 0) return 0;
     PL_REQUIRE(rows > 0 && I > 0 && rows <= 65535 * 16, "silu_mul: bad sizes rows=%d I=%d", rows, I);
-    const int vec = (I & 3) == 0 && ((uintptr_t)gate_up & 15) == 0 && ((uintptr_t)out & 15) == 0;
+    const int per = dtype == PL_F32 ? 4 : 8;
+    const int vec = I % per == 0 && ((uintptr_t)gate_up & 15) == 0 && ((uintptr_t)out & 15) == 0;
     const int threads = 256;
-    int bx = (I / (vec ? 4 : 1) + threads - 1) / threads;
+    int bx = (I / (vec ? per : 1) + threads - 1) / threads;
     if (bx > 8) bx = 8;
     if (bx < 1) bx = 1;
     for (int r0 = 0; r0 < rows; r0 += 65535) {

@@ -45,7 +45,7 @@ class AttnParams(ctypes.Structure):
         ("k_lens", c_void_p), ("work", c_void_p), ("scratch", c_void_p), ("scratch_floats", c_longlong),
         ("q_stride", c_int), ("out_stride", c_int), ("bt_stride", c_int), ("n_work", c_int), ("max_splits", c_int),
         ("nh", c_int), ("nkv", c_int), ("d", c_int), ("ps", c_int), ("window", c_int), ("is_small", c_int),
-        ("scale", c_float), ("ps_shift", c_int), ("counters", c_void_p),
+        ("scale", c_float), ("ps_shift", c_int), ("counters", c_void_p), ("num_pages", c_int),
     ]
 
 
@@ -338,7 +338,7 @@ class CudaOps:
         p.q, p.kv, p.out = qkv.data_ptr(), kv.data_ptr(), out.data_ptr()
         p.block_table, p.cu_q, p.k_lens = block_table.data_ptr(), ctx.cu_seqlens_q.data_ptr(), ctx.seq_lens_k.data_ptr()
         p.q_stride, p.out_stride, p.bt_stride = qkv.shape[1], nh * d, block_table.shape[1]
-        p.nh, p.nkv, p.d, p.ps = nh, nkv, d, kv.shape[3]
+        p.nh, p.nkv, p.d, p.ps, p.num_pages = nh, nkv, d, kv.shape[3], kv.shape[0]
         p.window, p.scale, p.max_splits = int(window or 0), float(scale), plan.max_splits
         ps = kv.shape[3]
         p.ps_shift = ps.bit_length() - 1 if ps & (ps - 1) == 0 else -1
