@@ -140,6 +140,14 @@ def build_module(name: str, verbose: bool = True) -> str:
         tmp_out = os.path.join(work, "lib.so")
         _run([nvcc, "--shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", tmp_out, *objs])
         os.replace(tmp_out, out)
+        # libraries of this module from older sources are of no use any more
+        prefix = f"libpl_{name}-"
+        for old in os.listdir(folder):
+            if old.startswith(prefix) and old.endswith(".so") and os.path.join(folder, old) != out:
+                try:
+                    os.remove(os.path.join(folder, old))
+                except OSError:
+                    pass
     finally:
         stop.set()
         shutil.rmtree(work, ignore_errors=True)
