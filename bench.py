@@ -255,7 +255,9 @@ def e2e_decode(engine, batch: int, steps: int, warmup: int, prompt_len: int):
     from paged_llm_b200.config import SamplingParams
 
     vocab = engine.model_config.vocab_size
-    sp = SamplingParams(temperature=0.0, max_tokens=steps + warmup + 1, ignore_eos=True)
+    # no request ends inside the timed steps (the requests of the second prefill step are a token
+    # behind the others): all of them are steady decoding of the whole batch
+    sp = SamplingParams(temperature=0.0, max_tokens=steps + warmup + 8, ignore_eos=True)
     for p in prompts_for(vocab, batch, prompt_len, seed=100 + batch):
         engine.add_request(p, sp)
     while any(not s.is_prefill_done or s.num_generated_tokens == 0 for s in engine.scheduler.running) \

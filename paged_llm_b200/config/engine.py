@@ -7,7 +7,9 @@ so that a call written for it reads the same here.  What differs:
   compatibility and must be "auto" or "cuda";
 * `dtype` is "auto", "bfloat16" or "float32" ("auto" reads the checkpoint's
   `torch_dtype`/`dtype` key; float16 checkpoints run in bfloat16);
-* `enforce_eager` switches CUDA-graph replay of decode steps off.
+* `enforce_eager` switches CUDA-graph replay of decode steps off;
+* `overlap_decode` (not in the reference): while requests only decode, the engine launches
+  the next step before it has read the tokens of the last one (see `LLMEngine.step`).
 """
 
 from __future__ import annotations
@@ -32,6 +34,7 @@ class EngineConfig:
     device: str = "cuda"
     seed: int = 0
     enforce_eager: bool = False
+    overlap_decode: bool = True
 
     def __post_init__(self) -> None:
         if self.block_size <= 0 or self.block_size & (self.block_size - 1):

@@ -54,6 +54,18 @@ class EngineStats:
     num_decode_tokens: int = 0
     num_preemptions: int = 0
     step_times: list[float] = field(default_factory=list)
+    num_steps_ahead: int = 0           # steps launched before the tokens of the step in front were read
+
+
+@dataclass
+class _InFlight:
+    """A step that is launched but whose tokens have not been read yet."""
+    out: object                     # its SchedulerOutput
+    sampled: list                   # the requests that sample in it, in the order of `ids`
+    ids: torch.Tensor | None        # their token ids on the device
+    host: torch.Tensor | None       # the same on their way to pinned host memory
+    event: object                   # recorded behind that copy
+    t0: float
 
 
 _FINISH = {"FINISHED_STOPPED": "stop", "FINISHED_LENGTH": "length", "FINISHED_ABORTED": "abort"}
@@ -106,6 +118,10 @@ class LLMEngine:
         self.runner = ModelRunner(self.model, self.kv_cache, self.block_manager, cfg, ops, self.sampler)
         self.stats = EngineStats()
         self._seqs: dict[int, Sequence] = {}
+        self._in_flight: _InFlight | None = None
+        self._unreported: list[StepOutput] = []
+        self._pinned: list[torch.Tensor] = []
+        self._pinned_pos = 0
         log.info("KV cache: %d blocks x %d tokens = %d tokens (%.2f GiB)", num_blocks, cfg.block_size,
                  num_blocks * cfg.block_size, num_blocks * self.kv_cache.page_bytes() / 2 ** 30)
 
@@ -153,29 +169,105 @@ class LLMEngine:
         return seq.seq_id
 
     def abort_request(self, seq_id: int) -> None:
+        if self._in_flight is not None:              # its tokens first, then the request may go
+            flight, self._in_flight = self._in_flight, None
+            self._unreported += self._resolve(flight)
         self.scheduler.abort(seq_id)
 
     @property
     def has_unfinished_requests(self) -> bool:
-        return self.scheduler.has_unfinished
+        return self.scheduler.has_unfinished or self._in_flight is not None or bool(self._unreported)
 
+    # ---- stepping -----------------------------------------------------------------
     def step(self) -> list[StepOutput]:
+        """One step of the engine: returns, for each request of the step whose tokens are read,
+        its new token (None for a portion of a prompt that samples nothing) and whether it
+        finished (reference: pagedllm/engine.py:186-211).
+
+        While requests only decode, the steps overlap: the step after is launched from what is
+        known on the host (positions, pages) with its input tokens taken from the device, and
+        only then are the tokens of the step in front read, appended and checked.  The device
+        never waits for the host that way.  A request that turns out to have stopped (EOS, a
+        stop token) has then run one step in vain; its token of that step is dropped.  A step
+        is never launched ahead when a request is about to reach its length limit, when
+        requests wait for admission, or when pages could run out."""
         t0 = time.perf_counter()
+        outputs, self._unreported = self._unreported, []
+        flight = self._in_flight
+        if flight is None:
+            flight = self._launch(None, t0)
+            if flight is None:
+                return outputs
+        self._in_flight = self._launch(flight, t0) if self._may_run_ahead(flight) else None
+        outputs += self._resolve(flight)
+        self.stats.step_times.append(time.perf_counter() - t0)
+        return outputs
+
+    def _launch(self, ahead_of: _InFlight | None, t0: float) -> _InFlight | None:
+        """Schedules and launches a step.  `ahead_of`: the step whose tokens, still on the
+        device, are this step's input."""
         out = self.scheduler.schedule()
         if out.is_empty:
-            if self.scheduler.has_unfinished:
+            if self.scheduler.has_unfinished and ahead_of is None:
                 raise RuntimeError("no request can be scheduled although some are unfinished: the cache pool is "
                                    "too small for the oldest waiting request")
-            return []
-        sampled = self.runner.run(out)
-        finished = {s.seq_id for s in self.scheduler.update(out, sampled)}
+            return None
+        if ahead_of is not None:
+            assert [i.seq.seq_id for i in out.scheduled] == [s.seq_id for s in ahead_of.sampled]
+            self.runner.next_ids_override = ahead_of.ids
+            self.stats.num_steps_ahead += 1
+        sampled, ids = self.runner.launch(out)
+        self.scheduler.advance(out)
+        host = event = None
+        if ids is not None and ids.is_cuda:
+            if len(self._pinned) < 2 or self._pinned[0].numel() < ids.numel():
+                self._pinned = [torch.empty(max(ids.numel(), 256), dtype=ids.dtype, pin_memory=True) for _ in range(2)]
+            self._pinned_pos ^= 1
+            host = self._pinned[self._pinned_pos][:ids.numel()]
+            host.copy_(ids, non_blocking=True)
+            event = torch.cuda.Event()
+            event.record()
         st = self.stats
         st.num_steps += 1
         st.num_prefill_tokens += out.num_prefill_tokens
         st.num_decode_tokens += out.num_decode_tokens
         st.num_preemptions += len(out.preempted)
-        st.step_times.append(time.perf_counter() - t0)
-        return [StepOutput(i.seq.seq_id, sampled.get(i.seq.seq_id), i.seq.seq_id in finished) for i in out.scheduled]
+        return _InFlight(out, sampled, ids, host, event, t0)
+
+    def _may_run_ahead(self, flight: _InFlight) -> bool:
+        """Whether the step after `flight` can be launched before its tokens are read: it is
+        the same requests decoding one token further, whatever those tokens are."""
+        sch, cfg = self.scheduler, self.config
+        if not cfg.overlap_decode or flight.ids is None or sch.waiting:
+            return False
+        out = flight.out
+        if out.num_prefill_tokens or out.preempted or len(out.scheduled) != len(sch.running) \
+                or self.block_manager.num_state_slots:
+            return False
+        for item, seq in zip(out.scheduled, sch.running):
+            if item.seq is not seq or not item.needs_sampling or seq.num_unresolved != 1:
+                return False
+            # its length limit would end it with the token on its way: nothing to run ahead for
+            if seq.num_generated_tokens >= seq.max_tokens or seq.num_tokens >= cfg.max_model_len:
+                return False
+        # a page each at most, and none must be taken from a running request
+        bm = self.block_manager
+        return min(bm.num_free_in_group(g) for g in range(len(bm.pools))) >= len(sch.running)
+
+    def _resolve(self, flight: _InFlight) -> list[StepOutput]:
+        """Reads the tokens of a launched step and lets the scheduler take them in."""
+        sampled: dict[int, int] = {}
+        if flight.ids is not None:
+            if flight.event is not None:
+                flight.event.synchronize()
+                tokens = flight.host.tolist()
+            else:
+                tokens = flight.ids.tolist()
+            sampled = {seq.seq_id: int(tok) for seq, tok in zip(flight.sampled, tokens)}
+        live = [i for i in flight.out.scheduled if not i.seq.is_finished]
+        finished = {s.seq_id for s in self.scheduler.resolve(flight.out, sampled)}
+        return [StepOutput(i.seq.seq_id, sampled.get(i.seq.seq_id) if i.needs_sampling else None,
+                           i.seq.seq_id in finished) for i in live]
 
     def _to_output(self, seq: Sequence) -> RequestOutput:
         text = ""

@@ -423,11 +423,19 @@ class ModelRunner:
     def run(self, out) -> dict[int, int]:
         """One scheduled step: runs it and samples where a request reached its
         last known token (reference: pagedllm/engine.py:93-102)."""
+        sampled, ids = self.launch(out)
+        if ids is None:
+            return {}
+        return {seq.seq_id: int(tok) for seq, tok in zip(sampled, ids.tolist())}
+
+    @torch.no_grad()
+    def launch(self, out):
+        """The same without waiting for the result: returns the requests that sample in this
+        step and their token ids as a device tensor (None if no request samples)."""
         items = [StepItem(s.seq, s.num_new_tokens, (s.num_new_tokens - 1,) if s.needs_sampling else ())
                  for s in out.scheduled]
         logits = self.step(items)
         if logits is None:
-            return {}
+            return [], None
         sampled = [s.seq for s in out.scheduled if s.needs_sampling]
-        tokens = self.sampler.sample(logits, sampled)
-        return {seq.seq_id: int(tok) for seq, tok in zip(sampled, tokens)}
+        return sampled, self.sampler.sample_on_device(logits, sampled)

@@ -178,26 +178,54 @@ class Scheduler:
         return out
 
     # ---- after the step ----------------------------------------------------------
+    PLACEHOLDER = 0      # stands in `token_ids` for a token that is sampled but not yet read back
+
     def update(self, out: SchedulerOutput, sampled: dict[int, int]) -> list[Sequence]:
         """Advance watermarks, register full pages, append sampled tokens, retire
-        what finished (scheduler.py:161-187).  Returns the requests that finished."""
+        what finished (scheduler.py:161-187).  Returns the requests that finished.
+        It is `advance` followed by `resolve`; an engine that launches the next step
+        before it has read this step's tokens calls the two apart."""
+        self.advance(out)
+        return self.resolve(out, sampled)
+
+    def advance(self, out: SchedulerOutput) -> None:
+        """The step is launched: its tokens count as computed, and a request that
+        samples in it gets a place for the token to come."""
+        for item in out.scheduled:
+            seq = item.seq
+            seq.num_computed_tokens += item.num_new_tokens
+            self.bm.release_behind_window(seq)
+            if item.needs_sampling:
+                seq.append_token(self.PLACEHOLDER)
+                seq.num_unresolved += 1
+
+    def resolve(self, out: SchedulerOutput, sampled: dict[int, int]) -> list[Sequence]:
+        """The step's tokens are known: they take their places, pages that are full of
+        known tokens get their hashes, finished requests are retired.  A request that
+        finished in an earlier step (while this one was already running) is skipped."""
         done: list[Sequence] = []
         for item in out.scheduled:
             seq = item.seq
-            before = seq.num_computed_tokens
-            seq.num_computed_tokens = before + item.num_new_tokens
-            self.bm.cache_full_blocks(seq, before, seq.num_computed_tokens)
-            self.bm.release_behind_window(seq)
+            if seq.is_finished:
+                continue
+            if item.needs_sampling:
+                token = int(sampled[seq.seq_id])
+                seq.token_ids[seq.num_tokens - seq.num_unresolved] = token
+                seq.num_unresolved -= 1
+            known = seq.num_tokens - seq.num_unresolved
+            self.bm.cache_full_blocks(seq, 0, min(seq.num_computed_tokens, known))
             if not item.needs_sampling:
                 continue
-            token = sampled[seq.seq_id]
-            seq.append_token(token)
             sp = seq.sampling_params
+            generated = known - seq.num_prompt_tokens
             if (not sp.ignore_eos and token == self.eos_token_id) or token in sp.stop_token_ids:
                 seq.status = SequenceStatus.FINISHED_STOPPED
-            elif seq.num_generated_tokens >= seq.max_tokens or seq.num_tokens >= self.config.max_model_len:
+            elif generated >= seq.max_tokens or known >= self.config.max_model_len:
                 seq.status = SequenceStatus.FINISHED_LENGTH
             if seq.is_finished:
+                if seq.num_unresolved:                     # places of a step that ran ahead in vain
+                    del seq.token_ids[known:]
+                    seq.num_unresolved = 0
                 self.running.remove(seq)
                 self.bm.free(seq)
                 done.append(seq)

@@ -54,6 +54,7 @@ class Sequence:
         self.table_version: int = 0           # bumped by the cache manager whenever a block table changes
         self.state_slot: int | None = None    # slot of fixed-size per-request state
         self.max_tokens: int = self.sampling_params.max_tokens   # may be clamped at admission
+        self.num_unresolved: int = 0          # trailing tokens that are sampled on the device but not yet known here
 
     # the first cache group's table, which is what a single-group model has
     @property

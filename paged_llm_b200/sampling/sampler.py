@@ -38,14 +38,18 @@ class Sampler:
     def sample(self, logits: torch.Tensor, seqs: list) -> list[int]:
         """logits: [n, vocab] float32 on the device; seqs: the n requests, whose
         `sampling_params` decide how each row is drawn.  Returns n token ids."""
+        return self.sample_on_device(logits, seqs).tolist()
+
+    def sample_on_device(self, logits: torch.Tensor, seqs: list) -> torch.Tensor:
+        """The same, but the n token ids stay on the device (int32) and nothing waits."""
         n = logits.shape[0]
         assert n == len(seqs)
         params = [s.sampling_params for s in seqs]
         if all(p.greedy for p in params):
-            return self.ops.argmax(logits).tolist()
+            return self.ops.argmax(logits)
         temps = np.array([p.temperature for p in params], np.float32)
         top_k = np.array([p.top_k if p.top_k > 0 else 0 for p in params], np.int32)
         top_p = np.array([p.top_p for p in params], np.float32)
         seeds = np.array([request_seed(self.seed, s) for s in seqs], np.uint64)
         counters = np.array([s.num_tokens for s in seqs], np.uint64)
-        return self.ops.sample(logits, temps, top_k, top_p, seeds, counters).tolist()
+        return self.ops.sample(logits, temps, top_k, top_p, seeds, counters)

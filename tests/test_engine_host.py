@@ -48,6 +48,66 @@ def test_chunked_and_mixed_generation_equals_plain(folders):
     assert eng.stats.num_prefill_tokens == sum(map(len, prompts)) and eng.stats.num_decode_tokens == 4 * 9
 
 
+def plain_greedy_with_stop(folder, prompt, n, stop):
+    toks = plain_greedy(folder, prompt, n)
+    for i, t in enumerate(toks):
+        if t in stop:
+            return toks[:i + 1]
+    return toks
+
+
+@pytest.mark.parametrize("tiny", ["A", "B"])
+def test_steps_that_run_ahead_change_no_token(folders, tiny):
+    """Decoding overlapped (the next step launched before the last one's tokens are read)
+    and not: the same tokens, the same reasons to stop, every page back.  Requests end at
+    different lengths and on stop tokens that only show once the step after is on its way."""
+    vocab = TINIES[tiny][0]["vocab_size"]
+    prompts = [random_tokens(vocab, n, 10 + n) for n in (7, 19, 3, 26)]
+    lengths = (14, 5, 22, 9)
+    free_run = [plain_greedy(folders[tiny], p, n) for p, n in zip(prompts, lengths)]
+    stops = [[], [free_run[1][2]], [free_run[2][9]], []]            # requests 1 and 2 stop early on a token
+    sps = [SamplingParams(temperature=0.0, max_tokens=n, stop_token_ids=st) for n, st in zip(lengths, stops)]
+    results = {}
+    for overlap in (True, False):
+        eng = engine(folders[tiny], overlap_decode=overlap, max_num_batched_tokens=64)
+        outs = eng.generate(prompts, sps)
+        results[overlap] = [(o.token_ids, o.finish_reason) for o in outs]
+        assert eng.block_manager.num_free_blocks == 64 and not eng.has_unfinished_requests
+        assert (eng.stats.num_steps_ahead > 0) == overlap
+    assert results[True] == results[False]
+    for (toks, reason), p, n, st in zip(results[True], prompts, lengths, stops):
+        want = plain_greedy_with_stop(folders[tiny], p, n, st)
+        assert toks == want and reason == ("stop" if st and want[-1] in st else "length")
+
+
+def test_running_ahead_with_sampling_arrivals_and_abort(folders):
+    """Seeded sampling gives the same tokens overlapped or not; a request that arrives or is
+    aborted while a step is on its way is handled between steps."""
+    prompts = [random_tokens(256, n, 70 + n) for n in (9, 15, 4)]
+    sps = [SamplingParams(temperature=0.8, top_k=20, max_tokens=12, seed=5 + i) for i in range(3)]
+    tokens = {}
+    for overlap in (True, False):
+        eng = engine(folders["A"], overlap_decode=overlap)
+        ids = [eng.add_request(p, sp) for p, sp in zip(prompts[:2], sps[:2])]
+        got: dict[int, list[int]] = {}
+        steps = 0
+        while eng.has_unfinished_requests:
+            for o in eng.step():
+                if o.new_token is not None:
+                    got.setdefault(o.seq_id, []).append(o.new_token)
+            steps += 1
+            if steps == 4:
+                ids.append(eng.add_request(prompts[2], sps[2]))      # arrives while the others decode
+            if steps == 7:
+                eng.abort_request(ids[1])
+        tokens[overlap] = [got[i] for i in ids]
+        assert eng.block_manager.num_free_blocks == 64
+        assert len(got[ids[0]]) == 12 and len(got[ids[2]]) == 12 and len(got[ids[1]]) < 12
+    assert tokens[True][0] == tokens[False][0] and tokens[True][2] == tokens[False][2]
+    n = min(len(tokens[True][1]), len(tokens[False][1]))
+    assert tokens[True][1][:n] == tokens[False][1][:n]
+
+
 def test_prefix_hit(folders):
     eng = engine(folders["B"], max_num_batched_tokens=128)
     shared = random_tokens(509, 24, 7)

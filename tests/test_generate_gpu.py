@@ -44,6 +44,30 @@ def test_greedy_generation_float32(folders, name, block, blocks):
     assert eng.runner.num_graph_steps > 0 and eng.ops.launches > 0
 
 
+def test_steps_that_run_ahead_change_no_token_on_the_device(folders):
+    """The next decode step launched before the last one's tokens are read (its input ids taken
+    from the device) against the step-by-step engine: the same tokens, greedy and sampled, with
+    requests that end at different lengths and on a stop token."""
+    from paged_llm_b200 import LLMEngine, SamplingParams
+    hf, _ = TINIES["A"]
+    prompts = [random_tokens(hf["vocab_size"], n, 30 + n) for n in (6, 21, 2, 12)]
+    free_run = plain_greedy(folders["A"], prompts[1], 12)
+    sps = [SamplingParams(temperature=0.0, max_tokens=15),
+           SamplingParams(temperature=0.0, max_tokens=12, stop_token_ids=[free_run[6]]),
+           SamplingParams(temperature=0.9, top_p=0.9, max_tokens=20, seed=11),
+           SamplingParams(temperature=0.0, max_tokens=4)]
+    got = {}
+    for overlap in (True, False):
+        eng = LLMEngine(folders["A"], dtype="float32", block_size=16, num_gpu_blocks=32, max_model_len=128,
+                        overlap_decode=overlap)
+        got[overlap] = [(o.token_ids, o.finish_reason) for o in eng.generate(prompts, sps)]
+        assert (eng.stats.num_steps_ahead > 0) == overlap
+        assert eng.block_manager.num_free_blocks == 32 and not eng.has_unfinished_requests
+    assert got[True] == got[False]
+    assert got[True][0][0] == plain_greedy(folders["A"], prompts[0], 15)
+    assert got[True][1] == (free_run[:free_run.index(free_run[6]) + 1], "stop")
+
+
 def test_greedy_generation_bfloat16_follows_the_plain_model(folders):
     """bfloat16 may flip a near-tie; every generated token must be the argmax or
     within rounding of it in the plain model's logits for the same prefix."""
