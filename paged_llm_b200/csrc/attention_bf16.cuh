@@ -17,9 +17,13 @@
 // machine busy on few requests.
 #pragma once
 
+#include <cooperative_groups.h>
+
 #include "attention_common.cuh"
 
 namespace {
+
+namespace cg = cooperative_groups;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -61,7 +65,10 @@ struct AttnShape {
     static constexpr int SMEM_BYTES = (BM + 4 * BN) * PITCH * 2;
 };
 
-template <int DPAD, int MW, int NW, int KPW>
+// CLUSTER: the blocks of a thread-block cluster take the splits of one (request, kv head) and
+// merge their partial results through distributed shared memory: no partials in global memory,
+// no counter, no work list.
+template <int DPAD, int MW, int NW, int KPW, bool CLUSTER = false>
 __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
     using Shape = AttnShape<DPAD, MW, NW, KPW>;
     constexpr int BM = Shape::BM, BN = Shape::BN, PITCH = Shape::PITCH, THREADS = Shape::THREADS;
@@ -69,9 +76,10 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
     constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
     pdl_launch_dependents();
     pdl_wait();
-    const AttnItem it = attn_decode_item(p, blockIdx.x / p.nkv, BM, BN);     // kv heads of an item side by side:
-                                                                                // the list's longest-first order holds over heads
-    if (!it.valid) return;
+    // kv heads of an item side by side: the list's longest-first order holds over heads
+    const AttnItem it = CLUSTER ? attn_cluster_item(p, blockIdx.x / (p.cluster * p.nkv), blockIdx.x % p.cluster, p.cluster)
+                                : attn_decode_item(p, blockIdx.x / p.nkv, BM, BN);
+    if (!it.valid) return;           // the same for all blocks of a cluster
 
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
@@ -80,7 +88,7 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wm = warp % MW, wn = warp / MW;
-    const int d = p.d, kvh = blockIdx.x % p.nkv, G = p.nh / p.nkv;
+    const int d = p.d, kvh = CLUSTER ? (blockIdx.x / p.cluster) % p.nkv : blockIdx.x % p.nkv, G = p.nh / p.nkv;
     const __nv_bfloat16* q = (const __nv_bfloat16*)p.q;
     const __nv_bfloat16* kv = (const __nv_bfloat16*)p.kv;
     const int* bt = p.block_table + (size_t)it.seq * p.bt_stride;
@@ -252,6 +260,7 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
     }
     float* red_ml = reinterpret_cast<float*>(smem_raw);                     // [NW][BM][2] in the Q region
     float* red_o = reinterpret_cast<float*>(smem_raw + BM * PITCH * 2);     // [NW][BM][DPAD] in the K/V region
+    float* cpart = red_o + (size_t)NW * BM * DPAD;                          // [BM][DPAD + 2]: this block's partial (CLUSTER)
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int r = wm * 16 + g + 8 * h;
@@ -285,7 +294,15 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
             o1 += v.y * f;
         }
         const int tok = R / G, head = kvh * G + R % G;
-        if (it.splits <= 1) {
+        if (CLUSTER) {
+            float* part = cpart + (size_t)r * (DPAD + 2);
+            if (c == 0) {
+                part[0] = M;                          // base-2 units
+                part[1] = L;
+            }
+            part[2 + c] = o0;
+            part[3 + c] = o1;
+        } else if (it.splits <= 1) {
             const float inv = L > 0.f ? 1.0f / L : 0.f;
             __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)(it.q0 + tok) * p.out_stride + head * d + c;
             *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(o0 * inv, o1 * inv);
@@ -298,6 +315,38 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
             part[2 + c] = o0;
             part[3 + c] = o1;
         }
+    }
+    if (CLUSTER) {
+        // Every block of the cluster merges its share of the column pairs over all blocks'
+        // partials, read from their shared memory.
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        const int C = it.splits, rank = it.split;
+        const int pairs = d / 2;
+        for (int e = tid; e < it.rows_total * pairs; e += THREADS) {
+            const int R = e / pairs, cp = e - R * pairs;
+            if (cp % C != rank) continue;
+            const int c = cp * 2;
+            float M = -INFINITY;
+            for (int j = 0; j < C; ++j) M = fmaxf(M, cluster.map_shared_rank(cpart, j)[(size_t)R * (DPAD + 2)]);
+            float L = 0.f, o0 = 0.f, o1 = 0.f;
+            for (int j = 0; j < C; ++j) {
+                const float* pj = cluster.map_shared_rank(cpart, j) + (size_t)R * (DPAD + 2);
+                const float mj = pj[0];
+                if (mj == -INFINITY) continue;
+                const float f = fast_exp2(mj - M);
+                L += pj[1] * f;
+                const float2 v = *reinterpret_cast<const float2*>(pj + 2 + c);
+                o0 += v.x * f;
+                o1 += v.y * f;
+            }
+            const float inv = L > 0.f ? 1.0f / L : 0.f;
+            const int tok = R / G, head = kvh * G + R % G;
+            __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)(it.q0 + tok) * p.out_stride + head * d + c;
+            *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(o0 * inv, o1 * inv);
+        }
+        cluster.sync();              // nobody leaves while its shared memory is still read
+        return;
     }
     if (it.splits <= 1 || p.counters == nullptr) return;
 
@@ -377,6 +426,39 @@ int launch_attn_bf16(const AttnParams& p, cudaStream_t stream) {
     return 0;
 }
 
+// The cluster form of the small shape: p.n_work requests, p.cluster blocks per (request, kv head).
+template <int DPAD, int KPW>
+int launch_attn_cluster(const AttnParams& p, cudaStream_t stream) {
+    using Shape = AttnShape<DPAD, 1, 4, KPW>;
+    constexpr size_t smem = Shape::SMEM_BYTES > (Shape::BM * Shape::PITCH * 2 + 4 * Shape::BM * DPAD * 4)
+                                ? Shape::SMEM_BYTES + Shape::BM * (DPAD + 2) * 4
+                                : Shape::BM * Shape::PITCH * 2 + 4 * Shape::BM * DPAD * 4 + Shape::BM * (DPAD + 2) * 4;
+    auto kernel = attn_bf16_kernel<DPAD, 1, 4, KPW, true>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        PL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set = true;
+    }
+    PL_REQUIRE(p.cluster >= 1 && p.cluster <= 8, "attention_bf16: clusters of 1 to 8 blocks, not %d", p.cluster);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.n_work * p.nkv * p.cluster);
+    cfg.blockDim = dim3(Shape::THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = p.cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    static const bool no_pdl = getenv("PAGED_LLM_B200_NO_PDL") != nullptr;
+    cfg.numAttrs = no_pdl ? 1 : 2;
+    PL_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
+    return 0;
+}
+
 }  // namespace
 
 #if PL_DPAD == 64
@@ -408,6 +490,7 @@ PL_EXPORT int PL_CAT(pl_attention_bf16_d, PL_DPAD)(const AttnParams* params, cud
     PL_REQUIRE(p.q_stride % 8 == 0 && p.out_stride % 2 == 0, "attention_bf16: row strides must keep 16-byte alignment");
     PL_REQUIRE(((uintptr_t)p.q & 15) == 0 && ((uintptr_t)p.kv & 15) == 0, "attention_bf16: q and kv must be 16-byte aligned");
     constexpr int KPW_SMALL = PL_DPAD <= 128 ? 32 : 16;
+    if (p.cluster > 0) return launch_attn_cluster<PL_DPAD, KPW_SMALL>(p, stream);
     if (p.is_small) return launch_attn_bf16<PL_DPAD, 1, 4, KPW_SMALL>(p, stream);
 #if PL_DPAD == 64
     // prefill tiles of head size 64 run on tcgen05 with tensor-memory accumulators

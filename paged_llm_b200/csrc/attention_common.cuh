@@ -54,6 +54,33 @@ __device__ __forceinline__ AttnItem attn_decode_item(const AttnParams& p, int id
     return it;
 }
 
+// The same for the cluster form: the request comes from the block index, the split from the
+// block's rank in its cluster of `splits` blocks; the keys are cut evenly, in multiples of 32.
+__device__ __forceinline__ AttnItem attn_cluster_item(const AttnParams& p, int seq, int rank, int splits) {
+    AttnItem it;
+    it.valid = false;
+    it.seq = seq;
+    it.q0 = p.cu_q[seq];
+    it.nq = p.cu_q[seq + 1] - it.q0;
+    it.lk = p.k_lens[seq];
+    const int G = p.nh / p.nkv;
+    it.rows_total = it.nq * G;
+    it.row_base = 0;
+    it.scratch_base = 0;
+    it.split = rank;
+    it.splits = splits;
+    if (it.nq <= 0) return it;
+    const int pos_first = it.lk - it.nq;
+    const int lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    const int hi = it.lk;
+    int chunk = (hi - lo + splits - 1) / splits;
+    chunk = (chunk + 31) / 32 * 32;
+    it.key_lo = min(hi, lo + rank * chunk);
+    it.key_hi = min(hi, it.key_lo + chunk);
+    it.valid = true;
+    return it;
+}
+
 // Partial result of (scratch row, head, split): [m, l, acc[0..d)] with m the
 // running maximum of the scaled scores (natural-log units) and acc, l not yet
 // divided.

@@ -114,4 +114,6 @@ struct AttnParams {
     unsigned int* counters; // [requests * kv_heads] zeros, or null: the block of a request's kv head that
                             // finishes last merges the splits itself (no separate merge kernel)
     int num_pages;          // pages in `kv` (0: unknown; kernels that need it step aside)
+    int cluster;            // > 0: no work list; n_work requests of at most 16 rows each, every (request, kv head)
+                            // is a thread-block cluster of this many blocks that split the keys between them
 };

@@ -222,6 +222,50 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(SkinnyParams
     // Consumers.
     const int g = lane >> 2, t = lane & 3;
     pdl_wait();
+    const unsigned char* x_row[NT];
+    const size_t x_elem = NORM ? 4 : 2;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+        x_row[nt] = (const unsigned char*)p.X + (size_t)min(nt * 8 + g, p.M - 1) * p.ldx * x_elem;
+
+    constexpr int SLABS_PER_WARP = SK_KC / 32 / SK_CONSUMERS;     // 4
+    // With the normalising prologue the operand of a stage is fetched raw (float32 stream and
+    // norm weights) and scaled and packed afterwards.  All loads go out before the first value
+    // is used.
+    struct RawX {
+        float4 xa[NT][SLABS_PER_WARP], xb[NT][SLABS_PER_WARP];
+        float w[SLABS_PER_WARP][8];
+    };
+    auto raw_load = [&](RawX& r, int chunk) {
+        const int k_base = chunk * SK_KC + warp * SLABS_PER_WARP * 32 + 8 * t;
+#pragma unroll
+        for (int u = 0; u < SLABS_PER_WARP; ++u) {
+            const int k = min(k_base + u * 32, p.K - 8);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                r.xa[nt][u] = __ldcg(reinterpret_cast<const float4*>((const float*)x_row[nt] + k));
+                r.xb[nt][u] = __ldcg(reinterpret_cast<const float4*>((const float*)x_row[nt] + k + 4));
+            }
+            if (p.norm_w_bf16) {
+                const uint4 wv = __ldg(reinterpret_cast<const uint4*>((const __nv_bfloat16*)p.norm_w + k));
+                const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    r.w[u][2 * i] = __low2float(w2[i]);
+                    r.w[u][2 * i + 1] = __high2float(w2[i]);
+                }
+            } else {
+                const float4 w0 = __ldg(reinterpret_cast<const float4*>((const float*)p.norm_w + k));
+                const float4 w1 = __ldg(reinterpret_cast<const float4*>((const float*)p.norm_w + k + 4));
+                r.w[u][0] = w0.x; r.w[u][1] = w0.y; r.w[u][2] = w0.z; r.w[u][3] = w0.w;
+                r.w[u][4] = w1.x; r.w[u][5] = w1.y; r.w[u][6] = w1.z; r.w[u][7] = w1.w;
+            }
+        }
+    };
+    // The first stage's raw values are asked for before the sums of squares: the two round trips
+    // to L2 overlap.
+    RawX raw0;
+    if (NORM) raw_load(raw0, 0);
     float scale[NT];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) scale[nt] = 1.f;
@@ -258,18 +302,25 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(SkinnyParams
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) scale[nt] = inv[min(nt * 8 + g, 15)];
     }
-    const unsigned char* x_row[NT];
-    const size_t x_elem = NORM ? 4 : 2;
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
-        x_row[nt] = (const unsigned char*)p.X + (size_t)min(nt * 8 + g, p.M - 1) * p.ldx * x_elem;
-
-    constexpr int SLABS_PER_WARP = SK_KC / 32 / SK_CONSUMERS;     // 4
     // X does not depend on the row block, only on the chunk: the fragments of the next chunk
     // are fetched while the current one is multiplied, so their latency hides behind the
     // wait for the weights.
-    // All loads of a stage go out before the first value is used: with the normalising prologue
-    // the raw float32 values and the norm weights are fetched first, then scaled and packed.
+    auto raw_finish = [&](uint4 (&dst)[NT][SLABS_PER_WARP], const RawX& r, int chunk) {
+        const int k_base = chunk * SK_KC + warp * SLABS_PER_WARP * 32 + 8 * t;
+#pragma unroll
+        for (int u = 0; u < SLABS_PER_WARP; ++u)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const float sc = scale[nt];
+                const float4 a = r.xa[nt][u], b = r.xb[nt][u];
+                __nv_bfloat162 o[4];
+                o[0] = __floats2bfloat162_rn(a.x * sc * r.w[u][0], a.y * sc * r.w[u][1]);
+                o[1] = __floats2bfloat162_rn(a.z * sc * r.w[u][2], a.w * sc * r.w[u][3]);
+                o[2] = __floats2bfloat162_rn(b.x * sc * r.w[u][4], b.y * sc * r.w[u][5]);
+                o[3] = __floats2bfloat162_rn(b.z * sc * r.w[u][6], b.w * sc * r.w[u][7]);
+                dst[nt][u] = (k_base + u * 32 < p.K) ? *reinterpret_cast<uint4*>(o) : make_uint4(0, 0, 0, 0);
+            }
+    };
     auto fetch_x = [&](uint4 (&dst)[NT][SLABS_PER_WARP], int chunk) {
         const int k_base = chunk * SK_KC + warp * SLABS_PER_WARP * 32 + 8 * t;
         if (!NORM) {
@@ -281,44 +332,9 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(SkinnyParams
                                                          : make_uint4(0, 0, 0, 0);
             return;
         }
-        float4 xa[NT][SLABS_PER_WARP], xb[NT][SLABS_PER_WARP];
-        float w[SLABS_PER_WARP][8];
-#pragma unroll
-        for (int u = 0; u < SLABS_PER_WARP; ++u) {
-            const int k = min(k_base + u * 32, p.K - 8);
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                xa[nt][u] = __ldcg(reinterpret_cast<const float4*>((const float*)x_row[nt] + k));
-                xb[nt][u] = __ldcg(reinterpret_cast<const float4*>((const float*)x_row[nt] + k + 4));
-            }
-            if (p.norm_w_bf16) {
-                const uint4 wv = __ldg(reinterpret_cast<const uint4*>((const __nv_bfloat16*)p.norm_w + k));
-                const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    w[u][2 * i] = __low2float(w2[i]);
-                    w[u][2 * i + 1] = __high2float(w2[i]);
-                }
-            } else {
-                const float4 w0 = __ldg(reinterpret_cast<const float4*>((const float*)p.norm_w + k));
-                const float4 w1 = __ldg(reinterpret_cast<const float4*>((const float*)p.norm_w + k + 4));
-                w[u][0] = w0.x; w[u][1] = w0.y; w[u][2] = w0.z; w[u][3] = w0.w;
-                w[u][4] = w1.x; w[u][5] = w1.y; w[u][6] = w1.z; w[u][7] = w1.w;
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < SLABS_PER_WARP; ++u)
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                const float sc = scale[nt];
-                const float4 a = xa[nt][u], b = xb[nt][u];
-                __nv_bfloat162 o[4];
-                o[0] = __floats2bfloat162_rn(a.x * sc * w[u][0], a.y * sc * w[u][1]);
-                o[1] = __floats2bfloat162_rn(a.z * sc * w[u][2], a.w * sc * w[u][3]);
-                o[2] = __floats2bfloat162_rn(b.x * sc * w[u][4], b.y * sc * w[u][5]);
-                o[3] = __floats2bfloat162_rn(b.z * sc * w[u][6], b.w * sc * w[u][7]);
-                dst[nt][u] = (k_base + u * 32 < p.K) ? *reinterpret_cast<uint4*>(o) : make_uint4(0, 0, 0, 0);
-            }
+        RawX r;
+        raw_load(r, chunk);
+        raw_finish(dst, r, chunk);
     };
     auto multiply = [&](float (&acc)[NT][4], const uint4 (&x)[NT][SLABS_PER_WARP], int chunk, int it) {
         const int s = it % SK_STAGES;
@@ -345,11 +361,14 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(SkinnyParams
     uint4 xres[XR][NT][SLABS_PER_WARP];
     uint4 xv[NT][SLABS_PER_WARP], xn[NT][SLABS_PER_WARP];
     if (XC > 0) {
+        if (NORM) raw_finish(xres[0], raw0, 0);
+        else fetch_x(xres[0], 0);
 #pragma unroll
-        for (int ch = 0; ch < XR; ++ch)
+        for (int ch = 1; ch < XR; ++ch)
             if (ch < chunks) fetch_x(xres[ch], ch);
     } else {
-        fetch_x(xv, 0);
+        if (NORM) raw_finish(xv, raw0, 0);
+        else fetch_x(xv, 0);
     }
     int it = 0, blk_i = 0;
     for (int c = blockIdx.x; c < p.num_blocks; c += gridDim.x, ++blk_i) {

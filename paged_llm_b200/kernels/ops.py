@@ -12,6 +12,7 @@ package's own CUDA-core kernel so that no reduced-precision mode can slip in.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import numpy as np
@@ -45,7 +46,7 @@ class AttnParams(ctypes.Structure):
         ("k_lens", c_void_p), ("work", c_void_p), ("scratch", c_void_p), ("scratch_floats", c_longlong),
         ("q_stride", c_int), ("out_stride", c_int), ("bt_stride", c_int), ("n_work", c_int), ("max_splits", c_int),
         ("nh", c_int), ("nkv", c_int), ("d", c_int), ("ps", c_int), ("window", c_int), ("is_small", c_int),
-        ("scale", c_float), ("ps_shift", c_int), ("counters", c_void_p), ("num_pages", c_int),
+        ("scale", c_float), ("ps_shift", c_int), ("counters", c_void_p), ("num_pages", c_int), ("cluster", c_int),
     ]
 
 
@@ -98,6 +99,7 @@ class CudaOps:
         self._attn_fn = None
         self.launches = 0                 # kernels of this package launched so far
         self.use_skinny = True            # few-token products on this package's weight-streaming kernel
+        self.cluster_attention = os.environ.get("PAGED_LLM_B200_NO_CLUSTER") is None   # decode attention as clusters
         self._argmax_ws = None            # (packed winners, arrival counters) of the multi-block argmax
         self._argmax_keep: list = []
         self._attn_counters = None        # arrival counters of the split merge inside the attention kernel
@@ -348,6 +350,16 @@ class CudaOps:
             lib, fn = self._attention_bf16(d)
         else:
             lib, fn = self.core, self.core.pl_attention_f32
+        p.cluster = 0
+        if (bf16 and self.cluster_attention and plan.n_small and not plan.n_large and plan.max_splits <= 8
+                and max(ctx.host.q_lens) * (nh // nkv) <= self.SMALL_ROWS):
+            # every request is a small item: the splits of a (request, kv head) are the blocks of
+            # a thread-block cluster that merge through distributed shared memory
+            p.work, p.n_work, p.is_small, p.cluster = 0, ctx.num_seqs, 1, plan.max_splits
+            p.scratch, p.scratch_floats = 0, 0
+            _check(lib, fn(ctypes.byref(p), self._stream))
+            self.launches += 1
+            return out
         if plan.n_small:
             floats = max(plan.small_tokens, 1) * nh * plan.max_splits * (d + 2)
             scratch = self._scratch_for(floats)

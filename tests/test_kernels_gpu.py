@@ -180,6 +180,34 @@ def test_paged_attention(ops, dtype, ps, nh, nkv, d, case):
         torch.testing.assert_close(out[cu[s]:cu[s + 1]], want, atol=tol(dtype), rtol=tol(dtype), msg=f"request {s}")
 
 
+@pytest.mark.parametrize("cluster", [True, False])
+@pytest.mark.parametrize("window", [None, 50])
+@pytest.mark.parametrize("nh,nkv,d", [(32, 4, 64), (4, 2, 16), (6, 6, 128)])
+@pytest.mark.parametrize("q_lens,k_lens", [([1, 1, 1], [700, 64, 5]), ([2, 1, 2, 1, 1], [300, 2, 129, 1000, 33]), ([1], [4000])])
+def test_decode_attention_as_clusters_and_from_the_work_list(ops, cluster, window, nh, nkv, d, q_lens, k_lens):
+    """Steps in which every request brings a token or two: the splits of a request merged through
+    distributed shared memory by a thread-block cluster, or through global memory by the block
+    that finishes last."""
+    if max(q_lens) * (nh // nkv) > 16:
+        pytest.skip("more than 16 rows per request: not a decode step for this shape")
+    dtype, ps = torch.bfloat16, 16
+    ops.set_compute_dtype(dtype)
+    q, kv, bt, keys, vals = paged_case(q_lens, k_lens, nh, nkv, d, ps, dtype, seed=len(q_lens))
+    ctx = make_ctx(ops, q_lens, k_lens, nh, nkv, window, d)
+    qkv = torch.cat([q.reshape(-1, nh * d), torch.zeros(q.shape[0], 2 * nkv * d, dtype=dtype)], dim=1).cuda().contiguous()
+    before, ops.cluster_attention = ops.cluster_attention, cluster
+    try:
+        out = ops.paged_attention(qkv, nh, nkv, d, kv.cuda(), bt.cuda(), ctx, d ** -0.5, window).float().cpu()
+    finally:
+        ops.cluster_attention = before
+    cu = ctx.host.cu
+    for s, (nq, L) in enumerate(zip(q_lens, k_lens)):
+        qs = torch.zeros(L, nh, d)
+        qs[L - nq:] = q[cu[s]:cu[s + 1]].float()
+        want = plain_llama.causal_attention(qs, keys[s], vals[s], d ** -0.5, window=window)[L - nq:].reshape(nq, nh * d)
+        torch.testing.assert_close(out[cu[s]:cu[s + 1]], want, atol=tol(dtype), rtol=tol(dtype), msg=f"request {s}")
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("window", [1, 7, 16, 100])
 @pytest.mark.parametrize("nh,nkv,d", [(4, 2, 32), (8, 2, 64)])
