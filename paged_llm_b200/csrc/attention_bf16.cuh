@@ -437,9 +437,10 @@ int launch_attn_cluster(const AttnParams& p, cudaStream_t stream) {
     static bool attr_set = false;
     if (!attr_set) {
         PL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        PL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));    // up to 16 blocks
         attr_set = true;
     }
-    PL_REQUIRE(p.cluster >= 1 && p.cluster <= 8, "attention_bf16: clusters of 1 to 8 blocks, not %d", p.cluster);
+    PL_REQUIRE(p.cluster >= 1 && p.cluster <= 16, "attention_bf16: clusters of 1 to 16 blocks, not %d", p.cluster);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(p.n_work * p.nkv * p.cluster);
     cfg.blockDim = dim3(Shape::THREADS);

@@ -82,6 +82,7 @@ class CudaOps:
     supports_graphs = True
     SMALL_ROWS = 16
     MIN_SPLIT_KEYS = 128
+    MAX_CLUSTER = int(os.environ.get("PAGED_LLM_B200_MAX_CLUSTER", "8"))     # blocks of a decode-attention cluster
     MAX_SPLITS = 32
 
     def __init__(self, device="cuda"):
@@ -351,11 +352,11 @@ class CudaOps:
         else:
             lib, fn = self.core, self.core.pl_attention_f32
         p.cluster = 0
-        if (bf16 and self.cluster_attention and plan.n_small and not plan.n_large and plan.max_splits <= 8
+        if (bf16 and self.cluster_attention and plan.n_small and not plan.n_large
                 and max(ctx.host.q_lens) * (nh // nkv) <= self.SMALL_ROWS):
             # every request is a small item: the splits of a (request, kv head) are the blocks of
             # a thread-block cluster that merge through distributed shared memory
-            p.work, p.n_work, p.is_small, p.cluster = 0, ctx.num_seqs, 1, plan.max_splits
+            p.work, p.n_work, p.is_small, p.cluster = 0, ctx.num_seqs, 1, min(plan.max_splits, self.MAX_CLUSTER)
             p.scratch, p.scratch_floats = 0, 0
             _check(lib, fn(ctypes.byref(p), self._stream))
             self.launches += 1
