@@ -94,6 +94,15 @@ __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
         : "memory");
 }
+// The same with the A operand in tensor memory: row i of A in lane i, two bfloat16 per 32-bit
+// column (the even k in the low half), 8 columns per instruction.
+__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.u32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
+        : "memory");
+}
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(saddr(bar)) : "memory");
 }
@@ -406,18 +415,19 @@ inline int launch(const AttnParams& p, cudaStream_t stream) {
 // and values in with TMA: the pool of one layer is a 2-D tensor [pages * 2 * kv_heads *
 // page_size, 64] whose rows are 128 bytes, a box is the rows of one page (at most 64) and lands in
 // shared memory in the 128-byte swizzle the products read.  Scores are double-buffered in tensor
-// memory (two tiles of 64 keys), P in shared memory, keys and values in rings of three stages each;
+// memory (two tiles of 64 keys); P never leaves tensor memory: the softmax thread writes it, two
+// bfloat16 per column, over the first half of the scores it has just read, and the second product
+// takes it from there as its A operand.  Keys and values sit in rings of four stages each;
 // everything is handed over through mbarriers:
 //   k_full[s], v_full[s]    the boxes of a stage of keys / values have landed (TMA complete_tx)
 //   k_empty[s], v_empty[s]  the product reading the stage is done              (tcgen05.commit)
 //   s_full[b]    S[b] = Q K^T is in tensor memory        (tcgen05.commit)
-//   s_free[b]    the softmax has read S[b]               (softmax threads)
-//   p_full[b]    P[b] is in shared memory, O is rescaled, stray value rows are zeroed (softmax threads)
-//   pv_done[b]   O += P[b] V is done                     (tcgen05.commit)
-// The product warp issues S(t+2) before P(t) V(t), so the tensor cores work on the scores to come
-// while the softmax warps work on the current ones.  Key tiles start at multiples of 64 so that a
-// box never straddles a page; keys outside the block's range are masked by position, and their
-// value rows are zeroed in shared memory (a page may hold anything behind the last token).
+//   p_full[b]    P[b] is in tensor memory, O is rescaled, stray value rows are zeroed (softmax threads)
+//   pv_done[b]   O += P[b] V is done: S[b] may be written again (tcgen05.commit)
+// The product warp issues P(t) V(t) and then S(t+2), while the softmax warps work on S(t+1).
+// Key tiles start at multiples of 64 so that a box never straddles a page; keys outside the
+// block's range are masked by position, and their value rows are zeroed in shared memory (a page
+// may hold anything behind the last token).
 // Needs a page size that is a power of two >= 8; other page sizes run the kernel above.
 namespace tc2 {
 
@@ -427,6 +437,7 @@ using tc::mbar_wait;
 using tc::smem_desc;
 using tc::instr_desc;
 using tc::mma_f16;
+using tc::mma_f16_ts;
 using tc::mma_commit;
 using tc::fence_before_sync;
 using tc::fence_after_sync;
@@ -450,13 +461,13 @@ __device__ unsigned long long g_prof[32];
 #define PROF_FLUSH(base, n)
 #endif
 
-constexpr int BM = 128, BN = 64, D = 64, STAGES = 3;
+constexpr int BM = 128, BN = 64, D = 64, STAGES = 4;
 constexpr int SOFTMAX_WARPS = 4, MMA_WARP = 4, K_WARP = 5, V_WARP = 6;
 constexpr int THREADS = (SOFTMAX_WARPS + 3) * 32;                   // 224
-constexpr int TMEM_COLS = 256;               // S0: 0..63, S1: 64..127, O: 128..191
+constexpr int TMEM_COLS = 256;               // S0 / P0: 0..63, S1 / P1: 64..127, O: 128..191
 constexpr float LAZY_LOG2 = 8.f;
-constexpr int Q_BYTES = BM * 128, K_BYTES = BN * 128, P_BYTES = BM * 128;
-constexpr int SMEM_BYTES = Q_BYTES + 2 * STAGES * K_BYTES + 2 * P_BYTES + 1024;
+constexpr int Q_BYTES = BM * 128, K_BYTES = BN * 128;
+constexpr int SMEM_BYTES = Q_BYTES + 2 * STAGES * K_BYTES + 1024;
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(saddr(bar)) : "memory");
@@ -503,9 +514,8 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
     unsigned char* Qs = smem;                                  // [128][128 B]
     unsigned char* Ks = Qs + Q_BYTES;                          // [STAGES][64 keys][128 B]
     unsigned char* Vs = Ks + STAGES * K_BYTES;                 // [STAGES][64 keys][128 B]
-    unsigned char* Ps = Vs + STAGES * K_BYTES;                 // [2][128][128 B]
     __shared__ uint64_t k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
-    __shared__ uint64_t s_full[2], s_free[2], p_full[2], pv_done[2];
+    __shared__ uint64_t s_full[2], p_full[2], pv_done[2];
     __shared__ uint32_t tmem_base_slot;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -528,7 +538,6 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&s_full[b], 1);
-            mbar_init(&s_free[b], SOFTMAX_WARPS * 32);
             mbar_init(&p_full[b], SOFTMAX_WARPS * 32);
             mbar_init(&pv_done[b], 1);
         }
@@ -595,7 +604,7 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
                 const int b = t & 1, s = t % STAGES;
                 mbar_wait(&k_full[s], (t / STAGES) & 1);
                 PROF(0)
-                if (t >= 2) mbar_wait(&s_free[b], ((t - 2) >> 1) & 1);
+                if (t >= 2) mbar_wait(&pv_done[b], ((t - 2) >> 1) & 1);    // P(t-2), which lies over S[b], is consumed
                 PROF(1)
                 fence_after_sync();
                 const uint32_t ka = saddr(Ks + s * K_BYTES);
@@ -607,25 +616,25 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
                 mma_commit(&k_empty[s]);
                 PROF(2)
             };
-            // Scores run two tiles ahead of the second product: S(u + 2) is issued as soon as the
-            // softmax has taken S(u) into registers, long before it hands P(u) over.
+            // Scores run ahead of the second product: while the softmax works on S(u + 1), the
+            // tensor cores do P(u) V(u) and then S(u + 2) into the columns P(u) leaves.
             if (n_tiles > 0) issue_s(0);
             if (n_tiles > 1) issue_s(1);
             for (int u = 0; u < n_tiles; ++u) {
                 const int bu = u & 1, su = u % STAGES;
-                if (u + 2 < n_tiles) issue_s(u + 2);
                 mbar_wait(&v_full[su], (u / STAGES) & 1);
                 mbar_wait(&p_full[bu], (u >> 1) & 1);
                 PROF(3)
                 fence_after_sync();
-                const uint32_t pa = saddr(Ps + bu * P_BYTES), va = saddr(Vs + su * K_BYTES);
+                const uint32_t va = saddr(Vs + su * K_BYTES);
 #pragma unroll
-                for (int kk = 0; kk < BN / 16; ++kk)
-                    mma_f16(tmem_base + 128, smem_desc(pa + kk * 32, 16, 1024), smem_desc(va + kk * 2048, 16, 1024),
-                            IDESC_O, u > 0 || kk > 0);
+                for (int kk = 0; kk < BN / 16; ++kk)          // P from tensor memory: 8 packed columns per step
+                    mma_f16_ts(tmem_base + 128, tmem_base + bu * 64 + kk * 8, smem_desc(va + kk * 2048, 16, 1024),
+                               IDESC_O, u > 0 || kk > 0);
                 mma_commit(&pv_done[bu]);
                 mma_commit(&v_empty[su]);
                 PROF(4)
+                if (u + 2 < n_tiles) issue_s(u + 2);
             }
             PROF_FLUSH(10, 5)
         }
@@ -648,9 +657,6 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
             fence_after_sync();
             PROF(0)
             tmem_ld64(tmem_row + b * 64, sv);
-            // S[b] is in registers: the product warp may overwrite it
-            fence_before_sync();
-            mbar_arrive(&s_free[b]);
             const int kbase = key0 + t * BN;
             const bool row_full = p.window <= 0 && kbase >= it.key_lo && kbase + BN <= it.key_hi && kbase + BN - 1 <= pos;
             const bool warp_full = __all_sync(0xffffffffu, row_full);
@@ -673,28 +679,20 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
             if (changed) m_run = m_tile;
             const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
             PROF(1)
-            // P(t-2) must have been consumed before its buffer is written again
-            if (t >= 2) {
-                mbar_wait(&pv_done[b], ((t - 2) >> 1) & 1);
-                __syncwarp();
-            }
-            PROF(2)
-            unsigned char* prow = Ps + b * P_BYTES;
+            // P goes back to tensor memory, two bfloat16 per column, over the first half of S[b]
+            // (all of S[b] is in registers by now); the second product reads it from there.
             float ls[4] = {0.f, 0.f, 0.f, 0.f};
+            float packed[32];
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                uint32_t packed[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    // a masked score is -inf: fma gives -inf and the exponential 0
-                    const float p0 = ex2(fmaf(sv[c * 8 + 2 * i], scale_log2, neg_m));
-                    const float p1 = ex2(fmaf(sv[c * 8 + 2 * i + 1], scale_log2, neg_m));
-                    ls[i] += p0 + p1;
-                    __nv_bfloat162 bb = __floats2bfloat162_rn(p0, p1);
-                    packed[i] = *reinterpret_cast<uint32_t*>(&bb);
-                }
-                *reinterpret_cast<uint4*>(prow + swz(r, c)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            for (int i = 0; i < 32; ++i) {
+                // a masked score is -inf: fma gives -inf and the exponential 0
+                const float p0 = ex2(fmaf(sv[2 * i], scale_log2, neg_m));
+                const float p1 = ex2(fmaf(sv[2 * i + 1], scale_log2, neg_m));
+                ls[i & 3] += p0 + p1;
+                __nv_bfloat162 bb = __floats2bfloat162_rn(p0, p1);
+                packed[i] = __uint_as_float(*reinterpret_cast<uint32_t*>(&bb));
             }
+            tmem_st32(tmem_row + b * 64, packed);
             l_run = l_run * alpha + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
             PROF(3)
             // O is rescaled once the product of the tile before is done
@@ -722,8 +720,9 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
                     const int n = kbase + (e >> 3);
                     if (n < it.key_lo || n >= it.key_hi) *reinterpret_cast<uint4*>(vd + e * 16) = make_uint4(0, 0, 0, 0);
                 }
+                fence_async_smem();                                  // generic stores -> tensor-core reads
             }
-            fence_async_smem();                                      // generic stores -> tensor-core reads
+            tmem_st_wait();
             fence_before_sync();
             mbar_arrive(&p_full[b]);
             PROF(6)
