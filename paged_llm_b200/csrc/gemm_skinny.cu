@@ -221,6 +221,24 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(SkinnyParams
 
     // Consumers.
     const int g = lane >> 2, t = lane & 3;
+    // Rotary epilogue: position, request and page of the two tokens this thread finishes.  They
+    // are step metadata, complete before any kernel of the step started, so they are fetched
+    // before the wait for the kernel in front.
+    int r_seq[2] = {-1, -1}, r_pos[2] = {-1, -1}, r_page[2] = {-1, -1};
+    if (EPI == EPI_ROPE && warp < NT) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int tok = warp * 8 + 2 * t + e;
+            if (tok < p.M) {
+                r_seq[e] = p.token_seq[tok];
+                r_pos[e] = p.positions[tok];
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 2; ++e)
+            if (p.write && r_seq[e] >= 0 && r_pos[e] >= 0)
+                r_page[e] = p.block_table[(size_t)r_seq[e] * p.bt_stride + r_pos[e] / p.ps];
+    }
     pdl_wait();
     const unsigned char* x_row[NT];
     const size_t x_elem = NORM ? 4 : 2;
@@ -376,6 +394,14 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(SkinnyParams
         // What the epilogue will read is requested now, so that its latency hides behind the
         // product: the residual values of the two tokens this thread finishes (warps < NT only).
         float x_lo[2] = {0.f, 0.f}, x_hi[2] = {0.f, 0.f};
+        float2 r_cs[2] = {make_float2(1.f, 0.f), make_float2(1.f, 0.f)};      // (cos, sin) of the pair this thread rotates
+        if (EPI == EPI_ROPE && warp < NT && row_lo >= 0) {
+            const int head = row_lo / p.d, i_lo = row_lo - head * p.d;
+#pragma unroll
+            for (int e = 0; e < 2; ++e)
+                if (head < p.nh + p.nkv && r_seq[e] >= 0 && r_pos[e] >= 0 && r_pos[e] < p.table_len)
+                    r_cs[e] = __ldg(p.table + (size_t)r_pos[e] * (p.d / 2) + i_lo);
+        }
         if (EPI == EPI_ADD && warp < NT) {
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
@@ -463,10 +489,10 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(SkinnyParams
             } else {
                 const int head = row_lo / p.d, i_lo = row_lo - head * p.d, i_hi = i_lo + p.d / 2;
                 float a = __bfloat162float(__float2bfloat16_rn(lo)), b = __bfloat162float(__float2bfloat16_rn(hi));
-                const int s = p.token_seq[tok];
-                const int pos = p.positions[tok];
-                if (head < p.nh + p.nkv && s >= 0 && pos >= 0 && pos < p.table_len) {
-                    const float2 cs = p.table[(size_t)pos * (p.d / 2) + i_lo];
+                const int s = r_seq[e];
+                const int pos = r_pos[e];
+                {
+                    const float2 cs = r_cs[e];                  // (1, 0) where nothing is rotated
                     const float ra = a * cs.x - b * cs.y, rb = b * cs.x + a * cs.y;
                     a = ra;
                     b = rb;
@@ -476,7 +502,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) gemm_skinny_kernel(SkinnyParams
                 y[i_lo] = oa;
                 y[i_hi] = ob;
                 if (head >= p.nh && p.write && s >= 0) {
-                    const int page = p.block_table[(size_t)s * p.bt_stride + pos / p.ps];
+                    const int page = r_page[e];
                     if (page >= 0 && page < p.num_pages) {
                         const int kvh = head - p.nh;
                         const int sel = kvh >= p.nkv ? 1 : 0;
