@@ -25,13 +25,9 @@
 // accumulator; P rounded to bfloat16 for the second product.
 #pragma once
 
-#include <cuda.h>
-
-#include <mutex>
-#include <utility>
-#include <vector>
-
 #include "attention_common.cuh"
+#include "tcgen05.cuh"
+#include "tensor_map.cuh"
 
 namespace tc {
 
@@ -40,115 +36,6 @@ constexpr int THREADS = 256;          // two threads per query row: each takes h
 constexpr int TMEM_COLS = 256;           // S: columns 0..127, O: 128..191
 constexpr int Q_BYTES = BM * 128, KV_STAGE_BYTES = BN * 128, P_BYTES = BM * BN * 2;
 constexpr int SMEM_BYTES = Q_BYTES + 3 * KV_STAGE_BYTES + P_BYTES + 1024;     // + alignment slack
-constexpr unsigned SPIN_LIMIT = 1u << 20;
-
-__device__ int g_timeouts = 0;
-
-__device__ __forceinline__ uint32_t saddr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void cp16(void* dst, const void* src, int bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(saddr(dst)), "l"(src), "r"(bytes));
-}
-__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(saddr(bar)), "r"(count));
-}
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    for (unsigned i = 0; i < SPIN_LIMIT; ++i) {
-        uint32_t done;
-        asm volatile(
-            "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-            : "=r"(done)
-            : "r"(saddr(bar)), "r"(parity)
-            : "memory");
-        if (done) return true;
-    }
-    atomicAdd(&g_timeouts, 1);
-    return false;
-}
-
-// 64-bit shared-memory matrix descriptor: start address, leading and stride byte offsets
-// (all in units of 16 bytes), descriptor version 1, 128-byte swizzle.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)(lbo_bytes >> 4) << 16;
-    d |= (uint64_t)(sbo_bytes >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;                     // SWIZZLE_128B
-    return d;
-}
-
-// Instruction descriptor of kind::f16: float32 accumulator, bfloat16 operands.
-__host__ __device__ constexpr uint32_t instr_desc(int m, int n, bool b_mn_major) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
-           ((uint32_t)(m >> 4) << 24);
-}
-
-__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
-    asm volatile(
-        "{\n.reg .pred p;\nsetp.ne.u32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
-        : "memory");
-}
-// The same with the A operand in tensor memory: row i of A in lane i, two bfloat16 per 32-bit
-// column (the even k in the low half), 8 columns per instruction.
-__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, bool accumulate) {
-    asm volatile(
-        "{\n.reg .pred p;\nsetp.ne.u32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d_tmem),
-        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void mma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(saddr(bar)) : "memory");
-}
-__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
-    uint32_t r[32];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n" ::"r"(taddr),
-        "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
-        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
-        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
-        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
-        "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
-        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
-        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
-        "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
-        : "memory");
-}
-__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
-
-__device__ __forceinline__ float ex2(float x) {
-    float y;
-    asm volatile("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
-    return y;
-}
-
-// Byte offset of 16-byte chunk c (0..7) of row r in a [rows][128 B] tile with 128-byte swizzle.
-__device__ __forceinline__ int swz(int r, int c) { return r * 128 + ((c ^ (r & 7)) << 4); }
-
 __global__ void __launch_bounds__(THREADS, 2) attn_tc_kernel(AttnParams p) {
     pdl_launch_dependents();
     pdl_wait();
@@ -756,55 +643,9 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS));
 }
 
-// The tensor map of one layer of a pool: rows of 64 bfloat16, boxes of min(page size, 64) rows,
-// 128-byte swizzle.  Made once per (address, shape) and kept.
-struct MapKey {
-    const void* kv;
-    int pages, nkv, ps;
-    bool operator==(const MapKey& o) const { return kv == o.kv && pages == o.pages && nkv == o.nkv && ps == o.ps; }
-};
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
+// The tensor map of one layer of a pool: rows of 64 bfloat16, boxes of min(page size, 64) rows.
 inline const CUtensorMap* kv_tensor_map(const AttnParams& p) {
-    static std::mutex mu;
-    static std::vector<std::pair<MapKey, CUtensorMap*>> maps;
-    static EncodeTiledFn encode = nullptr;
-    std::lock_guard<std::mutex> lock(mu);
-    const MapKey key{p.kv, p.num_pages, p.nkv, p.ps};
-    for (auto& m : maps)
-        if (m.first == key) return m.second;
-    if (!encode) {
-        void* fn = nullptr;
-        cudaDriverEntryPointQueryResult res;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &res) != cudaSuccess ||
-            res != cudaDriverEntryPointSuccess || !fn) {
-            pl_fail("tcgen05 attention: the driver has no cuTensorMapEncodeTiled");
-            return nullptr;
-        }
-        encode = (EncodeTiledFn)fn;
-    }
-    void* mem = nullptr;
-    if (posix_memalign(&mem, 64, sizeof(CUtensorMap)) != 0) {
-        pl_fail("tcgen05 attention: out of host memory");
-        return nullptr;
-    }
-    CUtensorMap* map = (CUtensorMap*)mem;
-    const cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)p.num_pages * 2 * p.nkv * p.ps};
-    const cuuint64_t strides[1] = {(cuuint64_t)D * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)D, (cuuint32_t)(p.ps < BN ? p.ps : BN)};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult rc = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(p.kv), dims, strides, box, estr,
-                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (rc != CUDA_SUCCESS) {
-        free(mem);
-        pl_fail("tcgen05 attention: cuTensorMapEncodeTiled failed (%d)", (int)rc);
-        return nullptr;
-    }
-    maps.emplace_back(key, map);
-    return map;
+    return tensor_map_bf16(p.kv, (unsigned long long)p.num_pages * 2 * p.nkv * p.ps, D, D, p.ps < BN ? p.ps : BN);
 }
 
 // Whether this kernel takes the call: a page is a power of two of at least 8 tokens and the

@@ -31,7 +31,8 @@ NVCC_FLAGS = [
 HEAD_DIM_BUILDS = (16, 32, 64, 128, 256)
 
 MODULES: dict[str, list[str]] = {
-    "core": ["common.cu", "elementwise.cu", "gemm_f32.cu", "gemm_skinny.cu", "attention_f32.cu", "sampling.cu"],
+    "core": ["common.cu", "elementwise.cu", "gemm_f32.cu", "gemm_skinny.cu", "gemm_stream_tc.cu", "attention_f32.cu",
+             "sampling.cu"],
     **{f"attn_bf16_d{d}": ["common.cu", f"attention_bf16_d{d}.cu"] for d in HEAD_DIM_BUILDS},
     # decode attention whose scratch is a static array of the library (see attention_decode_static.h)
     "attn_static": ["common.cu", "attention_decode_static.cu"],

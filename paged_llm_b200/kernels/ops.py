@@ -100,6 +100,9 @@ class CudaOps:
         self._attn_fn = None
         self.launches = 0                 # kernels of this package launched so far
         self.use_skinny = True            # few-token products on this package's weight-streaming kernel
+        # 17..128 tokens: this package's tcgen05 kernel with cluster split-K.  Off unless asked for
+        # (PAGED_LLM_B200_STREAM_TC=1): measured at 1.5 to 2.5 times the library product's time.
+        self.use_stream_tc = os.environ.get("PAGED_LLM_B200_STREAM_TC") is not None
         self.cluster_attention = os.environ.get("PAGED_LLM_B200_NO_CLUSTER") is None   # decode attention as clusters
         self._argmax_ws = None            # (packed winners, arrival counters) of the multi-block argmax
         self._argmax_keep: list = []
@@ -196,6 +199,21 @@ class CudaOps:
         M, K = h.shape
         return self.use_skinny and h.dtype == torch.bfloat16 and 1 <= M <= 16 and K >= 32 and K % 32 == 0
 
+    def _stream_ok(self, h, w: torch.Tensor) -> bool:
+        """17 to 128 tokens in bfloat16: this package's tcgen05 weight-streaming kernel instead
+        of the library."""
+        M, K = h.shape
+        return (self.use_stream_tc and h.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 16 < M <= 128
+                and K >= 64 and K % 64 == 0 and w.is_contiguous())
+
+    def _stream_tc(self, h: torch.Tensor, w: torch.Tensor, out, resid, N: int, epi: int) -> None:
+        M, K = h.shape
+        assert h.stride(1) == 1 and h.stride(0) % 8 == 0
+        _check(self.core, self.core.pl_gemm_stream_tc(
+            self._p(h), h.stride(0), self._p(w), self._p(out), out.shape[1] if out is not None else 0,
+            self._p(resid), M, N, K, epi, self._stream))
+        self.launches += 1
+
     def linear(self, h, w: torch.Tensor, out_float32: bool = False) -> torch.Tensor:
         """h [M, K] @ w[N, K]^T.  float32: this package's CUDA-core kernel; bfloat16 with few
         tokens: this package's weight-streaming kernel; else the library product with
@@ -212,6 +230,10 @@ class CudaOps:
             return out
         h = self.materialize(h)
         assert h.is_contiguous()
+        if self._stream_ok(h, w):
+            out = torch.empty((M, N), dtype=torch.float32 if out_float32 else torch.bfloat16, device=self.device)
+            self._stream_tc(h, w, out, None, N, 1 if out_float32 else 0)
+            return out
         if h.dtype == torch.float32:
             assert w.dtype == torch.float32
             out = torch.empty((M, N), dtype=torch.float32, device=self.device)
@@ -239,6 +261,9 @@ class CudaOps:
                                                            self._p(self._norm_part), self._stream))
             self.launches += 1
             return LazyNorm(x, self._norm_part, norm_w, eps)
+        if not isinstance(h, LazyNorm) and self._stream_ok(h, w) and x.dtype == torch.float32 and x.is_contiguous():
+            self._stream_tc(h, w, None, x, N, 3)                  # the product's epilogue adds to the stream
+            return self.rms_norm(x, norm_w, eps)
         return self.add_rms_norm(x, self.linear(h, w), norm_w, eps)
 
     def gated_silu_linear(self, h, w_gate_up: torch.Tensor) -> torch.Tensor:
@@ -252,6 +277,11 @@ class CudaOps:
             _check(self.core, self.core.pl_gemm_skinny_silu(x, ldx, self._p(w_gate_up), self._p(out), I, M, I, K,
                                                             part, nw, nwc, eps, self._stream))
             self.launches += 1
+            return out
+        h = self.materialize(h)
+        if self._stream_ok(h, w_gate_up) and h.is_contiguous():
+            out = torch.empty((M, I), dtype=torch.bfloat16, device=self.device)
+            self._stream_tc(h, w_gate_up, out, None, I, 2)
             return out
         return self.silu_mul(self.linear(h, w_gate_up))
 

@@ -389,6 +389,51 @@ def test_skinny_gated_silu(ops, M, I, K):
     torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("M", [17, 32, 33, 64, 100, 128])
+@pytest.mark.parametrize("N,K", [(2048, 2048), (2560, 2048), (300, 128), (2048, 5632), (1000, 64), (129, 320)])
+def test_stream_tc_product(ops, M, N, K):
+    """17 to 128 tokens: the tcgen05 weight-streaming product with its epilogues (plain in both
+    output types, residual add, SiLU-gated) against float32 arithmetic on the same bfloat16 inputs."""
+    ops.set_compute_dtype(torch.bfloat16)
+    h = randn(M, K, seed=40 + M, dtype=torch.bfloat16)
+    w = randn(N, K, seed=41 + N, dtype=torch.bfloat16, std=K ** -0.5)
+    want = h.float() @ w.float().T
+    before = ops.launches
+    was, ops.use_stream_tc = ops.use_stream_tc, True         # the library product is the default at these sizes
+    try:
+        _stream_tc_checks(ops, h, w, want, before, M, N, K)
+    finally:
+        ops.use_stream_tc = was
+
+
+def _stream_tc_checks(ops, h, w, want, before, M, N, K):
+    got = ops.linear(h, w)
+    assert ops.launches == before + 1, "the product did not run on this package's kernel"
+    torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=2e-2)
+    got32 = ops.linear(h, w, out_float32=True)
+    assert got32.dtype == torch.float32
+    torch.testing.assert_close(got32, want, atol=2e-3, rtol=2e-3)
+    # a token's result does not depend on the other tokens of the batch
+    alone = ops.linear(h[:20].contiguous(), w, out_float32=True) if M > 20 else None
+    if alone is not None:
+        assert torch.equal(alone, got32[:20])
+    # residual add: x += bf16(h w^T), then the norm of the new x
+    x = randn(M, N, seed=42, dtype=torch.float32)
+    norm_w = randn(N, seed=43, dtype=torch.float32, std=0.1) + 1.0
+    x_new = x.clone()
+    normed = ops.linear_add_rms_norm(h, w, x_new, norm_w, 1e-5)
+    x_want = x + want.bfloat16().float()
+    torch.testing.assert_close(x_new, x_want, atol=2e-2, rtol=2e-2)
+    ref = x_new * torch.rsqrt(x_new.pow(2).mean(-1, keepdim=True) + 1e-5) * norm_w
+    torch.testing.assert_close(normed.float(), ref, atol=3e-2, rtol=3e-2)
+    if N % 2 == 0:
+        I = N // 2
+        act = ops.gated_silu_linear(h, w)
+        g, u = want[:, :I].bfloat16().float(), want[:, I:].bfloat16().float()
+        torch.testing.assert_close(act.float(), g * torch.sigmoid(g) * u, atol=3e-2, rtol=3e-2)
+    assert ops.core.pl_gemm_stream_tc_timeouts() == 0
+
+
 @pytest.mark.parametrize("nh,nkv,d", [(32, 4, 64), (4, 2, 16), (3, 3, 32), (6, 2, 48)])
 @pytest.mark.parametrize("q_lens,k_lens", [([1, 1, 1], [5, 300, 31]), ([5, 1, 7], [5, 300, 31]), ([1], [1])])
 def test_skinny_qkv_rope_write_equals_the_separate_kernels(ops, nh, nkv, d, q_lens, k_lens):
