@@ -288,7 +288,17 @@ class ModelRunner:
         if all(it.num_new_tokens == 1 and it.want == (0,) for it in items):
             if len(items) > self.GRAPH_BUCKETS[-1]:
                 return None
-            return ("decode", next(b for b in self.GRAPH_BUCKETS if b >= len(items)))
+            bucket = next(b for b in self.GRAPH_BUCKETS if b >= len(items))
+            # few requests with long contexts take other attention kernels than the same batch
+            # with short ones: a graph of its own
+            classify = getattr(self.ops, "long_context_class", None)
+            if classify is not None and self.plan_keys:
+                from ..kernels.plan import wanted_splits
+                longest = max(it.seq.num_computed_tokens for it in items) + 1
+                if any(classify(wanted_splits(bucket, key[1], self.ops.num_sms, self.ops.MAX_SPLITS), longest)
+                       for key in self.plan_keys):
+                    return ("decode", bucket, "long")
+            return ("decode", bucket)
         if len(items) == 1:
             n, want = items[0].num_new_tokens, items[0].want
             if n >= 64 and want in ((), (n - 1,)) and items[0].seq.num_computed_tokens + n <= self.config.max_model_len:

@@ -342,6 +342,15 @@ class CudaOps:
         lib = load_module(f"attn_bf16_d{b}")
         return int(getattr(lib, f"pl_attention_bf16_rows_d{b}")(0))
 
+    CLUSTER_KEYS = 512      # keys a block of a decode-attention cluster may have to walk before more splits pay
+
+    def long_context_class(self, wanted_splits: int, max_context: int) -> bool:
+        """True if a decode step of this shape should split its contexts further than a cluster
+        can (few requests with long contexts: the splits go through the work list and global
+        memory instead, up to MAX_SPLITS of them).  A step replayed from a graph must stay in the
+        class it was captured in."""
+        return wanted_splits > self.MAX_CLUSTER and max_context > self.CLUSTER_KEYS * self.MAX_CLUSTER
+
     def plan_attention(self, q_lens, k_lens, group_size, num_kv_heads, window, head_dim, pad_requests=None,
                        fixed_capacity=False) -> dict:
         return planning.plan_attention(
@@ -383,7 +392,8 @@ class CudaOps:
             lib, fn = self.core, self.core.pl_attention_f32
         p.cluster = 0
         if (bf16 and self.cluster_attention and plan.n_small and not plan.n_large
-                and max(ctx.host.q_lens) * (nh // nkv) <= self.SMALL_ROWS):
+                and max(ctx.host.q_lens) * (nh // nkv) <= self.SMALL_ROWS
+                and not self.long_context_class(plan.max_splits, max(ctx.host.k_lens))):
             # every request is a small item: the splits of a (request, kv head) are the blocks of
             # a thread-block cluster that merge through distributed shared memory
             p.work, p.n_work, p.is_small, p.cluster = 0, ctx.num_seqs, 1, min(plan.max_splits, self.MAX_CLUSTER)
