@@ -310,16 +310,20 @@ def run_ours(args) -> dict:
     peaks = load_peaks()
     with tempfile.TemporaryDirectory() as folder:
         cfg, full_layers = make_model(folder, args.size, args.layers)
-        max_len = max(PROMPT_LEN + args.steps + args.warmup + DECODE_LEN, PREFILL_TOKENS) + 64
+        prompt_len = args.context if args.only == "decode" and args.context else PROMPT_LEN
+        max_len = max(prompt_len + args.steps + args.warmup + DECODE_LEN, PREFILL_TOKENS) + 64
+        seqs = max(args.batch, 64) if prompt_len == PROMPT_LEN else args.batch
         engine = LLMEngine(folder, EngineConfig(
-            dtype="bfloat16", block_size=BLOCK_SIZE, max_model_len=max_len, max_num_seqs=64,
+            dtype="bfloat16", block_size=BLOCK_SIZE, max_model_len=max_len, max_num_seqs=max(seqs, 64),
             max_num_batched_tokens=max(2048, PREFILL_TOKENS), enable_prefix_caching=False,
-            num_gpu_blocks=64 * (-(-max_len // BLOCK_SIZE)) + 64))
+            num_gpu_blocks=seqs * (-(-max_len // BLOCK_SIZE)) + 64))
     B = args.batch
-    if args.only == "decode":            # a short run of one part, for profilers
-        ms, launches, ctx_mid = device_decode_loop(engine, B, args.steps, args.warmup, PROMPT_LEN)
-        return {"only": "decode", "batch": B, "ms_per_step": round(ms, 4), "launches_per_step": launches,
-                "layers": cfg.num_hidden_layers}
+    if args.only == "decode":            # a short run of one part, for profilers and other context lengths
+        ms, launches, ctx_mid = device_decode_loop(engine, B, args.steps, args.warmup, prompt_len)
+        step_bytes = engine.model.weight_bytes_per_step() + B * ctx_mid * (engine.kv_cache.page_bytes() // BLOCK_SIZE)
+        return {"only": "decode", "batch": B, "context": ctx_mid, "ms_per_step": round(ms, 4),
+                "launches_per_step": launches, "layers": cfg.num_hidden_layers,
+                "gb_per_s": round(step_bytes / (ms * 1e-3) / 1e9, 1)}
     if args.only == "prefill":
         pre_ms = prefill_once(engine, PREFILL_TOKENS, iters=max(1, args.steps), warmup=args.warmup)
         return {"only": "prefill", "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3), "layers": cfg.num_hidden_layers}
@@ -434,6 +438,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=None, help="with --only decode: prompt length instead of 512")
     ap.add_argument("--size", choices=sorted(SIZES), default="tinyllama-1.1b")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the named size (reported in config)")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,

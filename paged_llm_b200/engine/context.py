@@ -51,6 +51,7 @@ class AttentionPlan:
     n_large: int
     max_splits: int
     small_tokens: int = 0            # tokens of the requests in `small` (scratch rows)
+    long_context: bool = False       # a decode step whose contexts are split through the work list, not as clusters
 
 
 @dataclass

@@ -241,7 +241,7 @@ class ModelRunner:
                 small=view(f"small{key}", ns * 4).view(ns, 4) if ns else None,
                 large=view(f"large{key}", nl * 4).view(nl, 4) if nl else None,
                 splits=view(f"splits{key}"), n_small=ns, n_large=nl, max_splits=p["max_splits"],
-                small_tokens=p["num_small_tokens"])
+                small_tokens=p["num_small_tokens"], long_context=p.get("long_context", False))
         return StepContext(
             ops=self.ops, num_tokens=T, num_seqs=S, num_logits=info["L_pad"],
             input_ids=view("ids"), positions=view("pos"), token_seq=view("tseq"), cu_seqlens_q=view("cu"),
@@ -293,10 +293,8 @@ class ModelRunner:
             # with short ones: a graph of its own
             classify = getattr(self.ops, "long_context_class", None)
             if classify is not None and self.plan_keys:
-                from ..kernels.plan import wanted_splits
                 longest = max(it.seq.num_computed_tokens for it in items) + 1
-                if any(classify(wanted_splits(bucket, key[1], self.ops.num_sms, self.ops.MAX_SPLITS), longest)
-                       for key in self.plan_keys):
+                if any(not key[2] and classify(bucket, key[1], longest) for key in self.plan_keys):
                     return ("decode", bucket, "long")
             return ("decode", bucket)
         if len(items) == 1:

@@ -342,21 +342,22 @@ class CudaOps:
         lib = load_module(f"attn_bf16_d{b}")
         return int(getattr(lib, f"pl_attention_bf16_rows_d{b}")(0))
 
-    CLUSTER_KEYS = 512      # keys a block of a decode-attention cluster may have to walk before more splits pay
+    CLUSTER_KEYS = 600      # keys a block of a decode-attention cluster may have to walk before more splits pay
 
-    def long_context_class(self, wanted_splits: int, max_context: int) -> bool:
-        """True if a decode step of this shape should split its contexts further than a cluster
-        can (few requests with long contexts: the splits go through the work list and global
-        memory instead, up to MAX_SPLITS of them).  A step replayed from a graph must stay in the
-        class it was captured in."""
-        return wanted_splits > self.MAX_CLUSTER and max_context > self.CLUSTER_KEYS * self.MAX_CLUSTER
+    def long_context_class(self, num_requests: int, num_kv_heads: int, max_context: int) -> bool:
+        """True if a decode step of this shape is planned as a long-context step (see
+        plan.is_long_context).  A step replayed from a graph must stay in the class it was
+        captured in, so the runner keeps a graph per class."""
+        return planning.is_long_context(num_requests, num_kv_heads, self.num_sms, self.MAX_SPLITS,
+                                        self.MAX_CLUSTER if self.cluster_attention else 0, self.CLUSTER_KEYS, max_context)
 
     def plan_attention(self, q_lens, k_lens, group_size, num_kv_heads, window, head_dim, pad_requests=None,
                        fixed_capacity=False) -> dict:
         return planning.plan_attention(
             q_lens, k_lens, group_size, num_kv_heads, window, small_rows=self.SMALL_ROWS,
             large_rows=self._large_rows(head_dim), min_split_keys=self.MIN_SPLIT_KEYS, num_sms=self.num_sms,
-            max_splits=self.MAX_SPLITS, pad_requests=pad_requests, fixed_capacity=fixed_capacity)
+            max_splits=self.MAX_SPLITS, pad_requests=pad_requests, fixed_capacity=fixed_capacity,
+            cluster_max=self.MAX_CLUSTER if self.cluster_attention else 0, long_keys=self.CLUSTER_KEYS)
 
     def _scratch_for(self, floats: int) -> torch.Tensor:
         """Scratch for split partials.  Grown by allocating anew and keeping the
@@ -392,8 +393,7 @@ class CudaOps:
             lib, fn = self.core, self.core.pl_attention_f32
         p.cluster = 0
         if (bf16 and self.cluster_attention and plan.n_small and not plan.n_large
-                and max(ctx.host.q_lens) * (nh // nkv) <= self.SMALL_ROWS
-                and not self.long_context_class(plan.max_splits, max(ctx.host.k_lens))):
+                and max(ctx.host.q_lens) * (nh // nkv) <= self.SMALL_ROWS and not plan.long_context):
             # every request is a small item: the splits of a (request, kv head) are the blocks of
             # a thread-block cluster that merge through distributed shared memory
             p.work, p.n_work, p.is_small, p.cluster = 0, ctx.num_seqs, 1, min(plan.max_splits, self.MAX_CLUSTER)

@@ -49,3 +49,24 @@ def test_longest_tiles_first():
     plan = general([300, 40], [300, 900], 8, 4, None)
     large = plan["large"].reshape(-1, 4)
     assert large[0, 0] == 1                     # the request with the longest context leads
+
+
+def test_long_context_decode_steps_are_split_further():
+    """Few long requests: a block of a cluster of at most 8 would walk thousands of keys alone, so
+    the plan turns to about three blocks per SM through the work list; short contexts and steps
+    with prompt portions stay as they are."""
+    from paged_llm_b200.kernels.plan import is_long_context, long_context_splits, plan_attention
+
+    kw = dict(small_rows=16, large_rows=128, min_split_keys=128, num_sms=148, max_splits=32, cluster_max=8, long_keys=600)
+    short = plan_attention([1] * 8, [700] * 8, 8, 4, None, **kw)
+    assert not short["long_context"] and short["max_splits"] == 5
+    long = plan_attention([1] * 8, [16000] * 8, 8, 4, None, **kw)
+    assert long["long_context"] and long["max_splits"] == 13 == long_context_splits(8, 4, 148, 32)
+    assert len(long["small"]) // 4 == 8 * 13
+    one = plan_attention([1], [16000], 8, 4, None, **kw)
+    assert one["long_context"] and one["max_splits"] == 32
+    assert not plan_attention([1], [4000], 8, 4, None, **kw)["long_context"]           # 8 blocks x 500 keys
+    assert not plan_attention([1, 40], [16000, 16000], 8, 4, None, **kw)["long_context"]   # a prompt portion in the step
+    assert not plan_attention([1] * 8, [16000] * 8, 8, 4, None, **{**kw, "cluster_max": 0})["long_context"]
+    # the class of a padded graph bucket is that of the bucket, whatever the live requests
+    assert is_long_context(8, 4, 148, 32, 8, 600, 3001) and not is_long_context(8, 4, 148, 32, 8, 600, 3000)
