@@ -334,7 +334,8 @@ using tc::tmem_st_wait;
 using tc::ex2;
 using tc::swz;
 
-// #define PL_TC2_PROF 1   // TEMPORARY
+// Cycle counters of the three roles of block 0, read with pl_attention_tc_prof: compiled in
+// with -DPL_TC2_PROF only (they cost time).
 #ifdef PL_TC2_PROF
 __device__ unsigned long long g_prof[32];
 #define PROF_DECL long long pt_ = clock64(); const bool prof_ = blockIdx.x == 0 && (threadIdx.x & 31) == 0; unsigned long long pacc_[10] = {0,0,0,0,0,0,0,0,0,0};
