@@ -327,7 +327,48 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
     const int pos = positions[t];
     T* row = qkv + (size_t)t * row_stride;
     const int half = rotary_dim / 2;
-    if (half > 0 && pos >= 0 && pos < table_len) {
+    // the page is asked for now and used at the end of the pass: its latency hides behind the rotation
+    int page = -1;
+    if (write && pos >= 0) page = block_table[(size_t)s * bt_stride + pos / ps];
+    const bool to_cache = write && page >= 0 && page < num_pages;
+    const int off = pos >= 0 ? pos % ps : 0;
+    const bool rotate = half > 0 && pos >= 0 && pos < table_len;
+    if (vec && !interleaved && rotate && rotary_dim == d) {
+        // One pass: four pairs per step (elements j..j+3 of the first half with their partners);
+        // rotated k goes to the row and, from the same registers, to its page slot; v is copied.
+        const float2* cs = table + (size_t)pos * half;
+        const int quads_per_head = half / 4;
+        const int quads = (nh + nkv) * quads_per_head;
+        constexpr int PER = 16 / sizeof(T);
+        const int v_chunks = nkv * (d / PER);
+        for (int i = threadIdx.x; i < quads + v_chunks; i += blockDim.x) {
+            if (i < quads) {
+                const int h = i / quads_per_head, j = (i - h * quads_per_head) * 4;
+                T* head = row + h * d;
+                const float4 a = Vec4<T>::load(head + j), b = Vec4<T>::load(head + j + half);
+                const float4 c01 = *reinterpret_cast<const float4*>(cs + j);
+                const float4 c23 = *reinterpret_cast<const float4*>(cs + j + 2);
+                const float4 lo = make_float4(a.x * c01.x - b.x * c01.y, a.y * c01.z - b.y * c01.w,
+                                              a.z * c23.x - b.z * c23.y, a.w * c23.z - b.w * c23.w);
+                const float4 hi = make_float4(b.x * c01.x + a.x * c01.y, b.y * c01.z + a.y * c01.w,
+                                              b.z * c23.x + a.z * c23.y, b.w * c23.z + a.w * c23.w);
+                Vec4<T>::store(head + j, lo);
+                Vec4<T>::store(head + j + half, hi);
+                if (h >= nh && to_cache) {
+                    T* dst = kv + ((((size_t)page * 2 + 0) * nkv + (h - nh)) * ps + off) * d;
+                    Vec4<T>::store(dst + j, lo);
+                    Vec4<T>::store(dst + j + half, hi);
+                }
+            } else if (to_cache) {
+                const int e = i - quads, h = e / (d / PER), c = (e - h * (d / PER)) * PER;
+                const T* v = row + (nh + nkv) * d;
+                const size_t vdst = ((((size_t)page * 2 + 1) * nkv + h) * ps + off) * d + c;
+                *reinterpret_cast<uint4*>(kv + vdst) = *reinterpret_cast<const uint4*>(v + h * d + c);
+            }
+        }
+        return;
+    }
+    if (rotate) {
         const float2* cs = table + (size_t)pos * half;
         if (vec && !interleaved) {
             // four pairs per step: elements j..j+3 of the first half with their partners
@@ -358,11 +399,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const 
             }
         }
     }
-    if (!write) return;
+    if (!to_cache) return;
     __syncthreads();
-    const int page = block_table[(size_t)s * bt_stride + pos / ps];
-    if (page < 0 || page >= num_pages) return;
-    const int off = pos % ps;
     const T* k = row + nh * d;
     const T* v = row + (nh + nkv) * d;
     if (vec) {
