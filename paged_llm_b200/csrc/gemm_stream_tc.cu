@@ -270,8 +270,9 @@ PL_EXPORT int pl_gemm_stream_tc(const void* X, int ldx, const void* W, void* Y, 
     const int w_rows = epi == ST_SILU ? 2 * N : N;
     p.tiles = epi == ST_SILU ? (N + 63) / 64 : (N + 127) / 128;
     // blocks for about two per SM; K is cut in multiples of 64, every block of a cluster gets some
-    int split = (2 * g_st_sms) / p.tiles;
-    split = split < 1 ? 1 : split > 8 ? 8 : split;
+    // (clusters of 1, 2, 4 or 8: other sizes place badly on the GPCs and fewer of them run at a time)
+    int split = 1;
+    while (split < 8 && p.tiles * split * 2 <= 2 * g_st_sms) split *= 2;
     const int k_blocks = K / ST_BK;
     if (split > k_blocks) split = k_blocks;
     const int per = (k_blocks + split - 1) / split;
