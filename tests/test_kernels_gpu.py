@@ -255,6 +255,36 @@ def test_one_far_key_among_hundreds(ops, dtype):
         torch.testing.assert_close(out, want, atol=2e-2, rtol=2e-2, msg=f"key {target}")
 
 
+@pytest.mark.parametrize("nq,L,targets", [
+    (200, 1500, (0, 15, 16, 63, 64, 1023, 1024, 1299, 1300, 1498, 1499)),      # a prompt portion: 128-row tiles, TMA page boxes
+    (1, 6000, (0, 127, 128, 191, 192, 2999, 5998, 5999)),                      # one long request: the long-context class
+])
+def test_one_far_key_in_a_portion_and_in_a_long_context(ops, nq, L, targets):
+    """The same for the other two attention paths of bfloat16 at head size 64: the last row of a
+    prompt portion (tcgen05 kernel, keys brought in page by page with TMA) and a single decoding
+    request whose context is long enough for the work-list splits."""
+    dtype = torch.bfloat16
+    ops.set_compute_dtype(dtype)
+    nh, nkv, d, ps = 8, 2, 64, 16
+    for target in targets:
+        q, kv, bt, keys, vals = paged_case([nq], [L], nh, nkv, d, ps, dtype, seed=target)
+        direction = torch.randn(d, generator=torch.Generator().manual_seed(2))
+        direction = direction / direction.norm()
+        q[-1] = (direction * 40).to(dtype)                 # the last row looks for the target key
+        for h in range(nkv):
+            keys[0][target, h] = (direction * 40).to(dtype).float()
+            kv[bt[0, target // ps], 0, h, target % ps] = keys[0][target, h].to(dtype)
+        ctx = make_ctx(ops, [nq], [L], nh, nkv, None, d)
+        if nq == 1:
+            assert ops.long_context_class(1, nkv, L), "this case is meant for the long-context class"
+        qkv = torch.cat([q.reshape(-1, nh * d), torch.zeros(nq, 2 * nkv * d, dtype=dtype)], dim=1).cuda().contiguous()
+        out = ops.paged_attention(qkv, nh, nkv, d, kv.cuda(), bt.cuda(), ctx, d ** -0.5, None).float().cpu()
+        want = vals[0][target].repeat_interleave(nh // nkv, dim=0).reshape(1, nh * d)
+        torch.testing.assert_close(out[-1:], want, atol=2e-2, rtol=2e-2, msg=f"key {target}")
+    if nq > 1:
+        assert ops._attention_bf16(d)[0].pl_attention_tc_timeouts() == 0
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("pairing", ["half", "interleaved"])
 @pytest.mark.parametrize("nh,nkv,d,rd", [(4, 2, 16, 16), (3, 3, 32, 32), (6, 2, 48, 24), (32, 4, 64, 64)])
