@@ -84,6 +84,26 @@ def test_greedy_generation_bfloat16_follows_the_plain_model(folders):
             seq.append(tok)
 
 
+def test_decoding_across_the_context_classes(folders):
+    """A decode step is planned as clusters while contexts are short and through the work list
+    once they are long, with a CUDA graph per class.  The limit is lowered here so that a short
+    generation crosses it: tokens must follow the plain model on both sides of the change."""
+    from paged_llm_b200 import LLMEngine, SamplingParams
+    hf, _ = TINIES["C"]
+    prompts = [random_tokens(hf["vocab_size"], n, 50 + n) for n in (5, 21)]
+    eng = LLMEngine(folders["C"], dtype="bfloat16", num_gpu_blocks=64, max_model_len=256)
+    eng.ops.CLUSTER_KEYS = 5                      # 5 keys x 8 blocks: contexts above 40 tokens are "long"
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=40))
+    keys = set(eng.runner._graphs)
+    assert ("decode", 2) in keys and ("decode", 2, "long") in keys, keys
+    for p, o in zip(prompts, outs):
+        seq = list(p)
+        for tok in o.token_ids:
+            ref = plain_logits(folders["C"], seq)[-1]
+            assert ref.max() - ref[tok] <= 3e-2 * np.abs(ref).max()
+            seq.append(tok)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding(folders, dtype):
     """300 decoded tokens from a short prompt, teacher-forced, against the plain logits."""
