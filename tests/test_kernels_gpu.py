@@ -180,6 +180,26 @@ def test_paged_attention(ops, dtype, ps, nh, nkv, d, case):
         torch.testing.assert_close(out[cu[s]:cu[s + 1]], want, atol=tol(dtype), rtol=tol(dtype), msg=f"request {s}")
 
 
+@pytest.mark.parametrize("ps", [4, 2])
+def test_prefill_attention_with_pages_too_small_for_tma_boxes(ops, ps):
+    """Pages of fewer than 8 tokens: the tcgen05 kernel that copies keys through the block table
+    with cp.async takes over from the one that brings whole pages in with TMA."""
+    dtype, nh, nkv, d = torch.bfloat16, 32, 4, 64
+    ops.set_compute_dtype(dtype)
+    q_lens, k_lens = [130, 1, 40], [300, 90, 40]
+    q, kv, bt, keys, vals = paged_case(q_lens, k_lens, nh, nkv, d, ps, dtype, seed=ps)
+    ctx = make_ctx(ops, q_lens, k_lens, nh, nkv, None, d)
+    qkv = torch.cat([q.reshape(-1, nh * d), torch.zeros(q.shape[0], 2 * nkv * d, dtype=dtype)], dim=1).cuda().contiguous()
+    out = ops.paged_attention(qkv, nh, nkv, d, kv.cuda(), bt.cuda(), ctx, d ** -0.5, None).float().cpu()
+    cu = ctx.host.cu
+    for s, (nq, L) in enumerate(zip(q_lens, k_lens)):
+        qs = torch.zeros(L, nh, d)
+        qs[L - nq:] = q[cu[s]:cu[s + 1]].float()
+        want = plain_llama.causal_attention(qs, keys[s], vals[s], d ** -0.5)[L - nq:].reshape(nq, nh * d)
+        torch.testing.assert_close(out[cu[s]:cu[s + 1]], want, atol=tol(dtype), rtol=tol(dtype), msg=f"request {s}")
+    assert ops._attention_bf16(d)[0].pl_attention_tc_timeouts() == 0
+
+
 @pytest.mark.parametrize("cluster", [True, False])
 @pytest.mark.parametrize("window", [None, 50])
 @pytest.mark.parametrize("nh,nkv,d", [(32, 4, 64), (4, 2, 16), (6, 6, 128)])
