@@ -269,6 +269,29 @@ class LLMEngine:
         return [StepOutput(i.seq.seq_id, sampled.get(i.seq.seq_id) if i.needs_sampling else None,
                            i.seq.seq_id in finished) for i in live]
 
+    def warm_up(self, max_batch: int | None = None) -> int:
+        """Captures the decode graphs of the batch-size buckets up to `max_batch` (default:
+        `max_num_seqs`) by running throw-away requests of one prompt token, so that no request
+        pays for a capture later (15-150 ms each when a bucket is first seen).  Not in the
+        reference.  Returns the number of graphs held afterwards; the cache is as before."""
+        if self.has_unfinished_requests:
+            raise RuntimeError("warm_up needs an idle engine")
+        buckets = [b for b in self.runner.GRAPH_BUCKETS if b <= (max_batch or self.config.max_num_seqs)]
+        if not self.runner.use_graphs:
+            return 0
+        stats, self.stats = self.stats, EngineStats()
+        try:
+            for b in buckets:
+                params = SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True)
+                ids = [self.add_request([0], params) for _ in range(b)]
+                while self.has_unfinished_requests:
+                    self.step()
+                for i in ids:
+                    self._seqs.pop(i, None)
+        finally:
+            self.stats = stats
+        return len(self.runner._graphs)
+
     def _to_output(self, seq: Sequence) -> RequestOutput:
         text = ""
         if self.tokenizer is not None:
