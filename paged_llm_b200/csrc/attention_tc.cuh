@@ -371,6 +371,31 @@ __device__ __forceinline__ void tma_box(void* dst, const CUtensorMap* map, int r
             "r"(saddr(dst)), "l"(map), "r"(0), "r"(row), "r"(saddr(bar))
         : "memory");
 }
+// Two float32 operations in one instruction (sm_100): the pair lives in a 64-bit register.
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigned long long b) {
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 // 64 columns of this thread's lane of tensor memory, one wait for both halves.
 __device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&v)[64]) {
     uint32_t r[64];
@@ -558,7 +583,7 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
             }
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int i = 0; i < 64; ++i) mx[i & 3] = fmaxf(mx[i & 3], sv[i]);
+            for (int i = 0; i < 32; ++i) mx[i & 3] = max3(mx[i & 3], sv[2 * i], sv[2 * i + 1]);
             const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;
             // The reference maximum moves only when the tile's maximum exceeds it by more than 2^8:
             // P stays below 256, exact enough in bfloat16 and float32, and O is seldom rescaled.
@@ -569,19 +594,24 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
             PROF(1)
             // P goes back to tensor memory, two bfloat16 per column, over the first half of S[b]
             // (all of S[b] is in registers by now); the second product reads it from there.
-            float ls[4] = {0.f, 0.f, 0.f, 0.f};
+            unsigned long long ls2[4] = {0ull, 0ull, 0ull, 0ull};           // four pairs of partial sums
+            const unsigned long long scale2 = pack2(scale_log2, scale_log2), negm2 = pack2(neg_m, neg_m);
             float packed[32];
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
                 // a masked score is -inf: fma gives -inf and the exponential 0
-                const float p0 = ex2(fmaf(sv[2 * i], scale_log2, neg_m));
-                const float p1 = ex2(fmaf(sv[2 * i + 1], scale_log2, neg_m));
-                ls[i & 3] += p0 + p1;
+                float x0, x1;
+                unpack2(fma2(pack2(sv[2 * i], sv[2 * i + 1]), scale2, negm2), x0, x1);
+                const float p0 = ex2(x0), p1 = ex2(x1);
+                ls2[i & 3] = add2(ls2[i & 3], pack2(p0, p1));
                 __nv_bfloat162 bb = __floats2bfloat162_rn(p0, p1);
                 packed[i] = __uint_as_float(*reinterpret_cast<uint32_t*>(&bb));
             }
             tmem_st32(tmem_row + b * 64, packed);
-            l_run = l_run * alpha + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
+            float la, lb, lc, ld;
+            unpack2(add2(ls2[0], ls2[1]), la, lb);
+            unpack2(add2(ls2[2], ls2[3]), lc, ld);
+            l_run = l_run * alpha + ((la + lb) + (lc + ld));
             PROF(3)
             // O is rescaled once the product of the tile before is done
             if (t >= 1 && __any_sync(0xffffffffu, changed)) {
