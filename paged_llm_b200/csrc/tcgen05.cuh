@@ -11,6 +11,12 @@
 namespace tc {
 
 constexpr unsigned SPIN_LIMIT = 1u << 20;
+// How long one try may sleep before it reports "not yet" (the hardware wakes it when the phase
+// completes): fewer polls, so fewer issue slots taken from the warps that work.
+#ifndef PL_SUSPEND_HINT_NS
+#define PL_SUSPEND_HINT_NS 2000
+#endif
+constexpr unsigned SUSPEND_HINT_NS = PL_SUSPEND_HINT_NS;
 
 static __device__ int g_timeouts = 0;
 
@@ -29,9 +35,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     for (unsigned i = 0; i < SPIN_LIMIT; ++i) {
         uint32_t done;
         asm volatile(
-            "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+            "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}\n"
             : "=r"(done)
-            : "r"(saddr(bar)), "r"(parity)
+            : "r"(saddr(bar)), "r"(parity), "r"(SUSPEND_HINT_NS)
             : "memory");
         if (done) return true;
     }
