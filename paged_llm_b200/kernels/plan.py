@@ -28,6 +28,10 @@ def wanted_splits(num_small: int, num_kv_heads: int, num_sms: int, max_splits: i
     return int(min(max_splits, max(1, -(-target_items // num_small))))
 
 
+def long_context_splits(num_requests: int, num_kv_heads: int, num_sms: int, max_splits: int) -> int:
+    return int(max(1, min(max_splits, (3 * num_sms) // max(1, num_requests * max(num_kv_heads, 1)))))
+
+
 def is_long_context(num_requests: int, num_kv_heads: int, num_sms: int, max_splits: int, cluster_max: int,
                     long_keys: int, max_context: int) -> bool:
     """Whether a decode step of this shape is in the long-context class: the blocks of a cluster
@@ -37,12 +41,10 @@ def is_long_context(num_requests: int, num_kv_heads: int, num_sms: int, max_spli
     (measured: 16 k context at batch 8, 2.05 ms per step as clusters of 5, 1.50 ms as 13 splits)."""
     if cluster_max <= 0:
         return False
-    want = wanted_splits(num_requests, num_kv_heads, num_sms, max_splits)
-    return max_context > long_keys * min(want, cluster_max)
-
-
-def long_context_splits(num_requests: int, num_kv_heads: int, num_sms: int, max_splits: int) -> int:
-    return int(max(1, min(max_splits, (3 * num_sms) // max(1, num_requests * max(num_kv_heads, 1)))))
+    cluster = min(wanted_splits(num_requests, num_kv_heads, num_sms, max_splits), cluster_max)
+    if long_context_splits(num_requests, num_kv_heads, num_sms, max_splits) <= cluster:
+        return False                 # so many requests that the work list would not split further either
+    return max_context > long_keys * cluster
 
 
 def _plan_decode(S, S_pad, k_lens, num_kv_heads, min_split_keys, num_sms, max_splits, fixed_capacity,

@@ -70,3 +70,5 @@ def test_long_context_decode_steps_are_split_further():
     assert not plan_attention([1] * 8, [16000] * 8, 8, 4, None, **{**kw, "cluster_max": 0})["long_context"]
     # the class of a padded graph bucket is that of the bucket, whatever the live requests
     assert is_long_context(8, 4, 148, 32, 8, 600, 3001) and not is_long_context(8, 4, 148, 32, 8, 600, 3000)
+    # 64 requests x 4 kv heads: one block each either way, so there is no second class (and no second graph)
+    assert not is_long_context(64, 4, 148, 32, 8, 600, 100000)
