@@ -75,11 +75,16 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
     constexpr int CH = DPAD / 8;                          // 16-byte chunks per row
     constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
     pdl_launch_dependents();
-    pdl_wait();
+    // A cluster block (a decode step) waits for the kernel in front only after it has asked for its
+    // first keys: lengths, block tables and all keys but the step's own are older than the step.
+    if (!CLUSTER) pdl_wait();
     // kv heads of an item side by side: the list's longest-first order holds over heads
     const AttnItem it = CLUSTER ? attn_cluster_item(p, blockIdx.x / (p.cluster * p.nkv), blockIdx.x % p.cluster, p.cluster)
                                 : attn_decode_item(p, blockIdx.x / p.nkv, BM, BN);
-    if (!it.valid) return;           // the same for all blocks of a cluster
+    if (!it.valid) {                 // the same for all blocks of a cluster
+        if (CLUSTER) pdl_wait();
+        return;
+    }
 
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
@@ -98,7 +103,8 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
     // One key tile: every thread first looks up the pages of all its rows (independent loads
     // that travel together), then issues the copies.
     constexpr int LOAD_ITERS = (BN * CH + THREADS - 1) / THREADS;
-    auto load_tile = [&](int stage, int kt) {
+    // Keys of the range at or behind `skip_from` are left alone (neither copied nor zero-filled).
+    auto load_tile = [&](int stage, int kt, int skip_from = 0x7fffffff) {
         __nv_bfloat16* kd = Ks + stage * BN * PITCH;
         __nv_bfloat16* vd = Vs + stage * BN * PITCH;
         int pg[LOAD_ITERS];
@@ -107,7 +113,7 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
             const int e = tid + i * THREADS;
             const int j = e / CH, c8 = e - j * CH;
             const int n = kt + j;
-            const bool ok = e < BN * CH && n < it.key_hi && c8 * 8 < d;
+            const bool ok = e < BN * CH && n < it.key_hi && n < skip_from && c8 * 8 < d;
             const int pi = p.ps_shift >= 0 ? n >> p.ps_shift : n / p.ps;
             pg[i] = ok ? bt[pi] : -1;
         }
@@ -117,6 +123,7 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
             if (e >= BN * CH) break;
             const int j = e / CH, c8 = e - j * CH;
             const int n = kt + j;
+            if (n >= skip_from && n < it.key_hi) continue;        // keys past the range are still zero-filled
             const int po = p.ps_shift >= 0 ? n & (p.ps - 1) : n % p.ps;
             const bool ok = pg[i] >= 0;
             const __nv_bfloat16* src = ok ? kv + ((((size_t)pg[i] * 2) * p.nkv + kvh) * p.ps + po) * d + c8 * 8 : kv;
@@ -142,7 +149,30 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
     const float scale_log2 = p.scale * LOG2E;
 
     const int n_tiles = (it.key_hi - it.key_lo + BN - 1) / BN;
-    if (n_tiles > 0) load_tile(0, it.key_lo);        // the first keys are on their way while Q is fetched
+    // The first keys are on their way while Q is fetched.  A cluster block has not waited for the
+    // kernel in front yet: the keys and values of this step's own tokens, which that kernel
+    // writes, are left out of the first copy and fetched after the wait, in a group of their own
+    // that the loop waits for together with the tile.
+    const int own_lo = CLUSTER ? it.lk - it.nq : 0x7fffffff;
+    if (n_tiles > 0) load_tile(0, it.key_lo, own_lo);
+    if (CLUSTER) {
+        pdl_wait();
+        const int new_lo = max(own_lo, it.key_lo), new_hi = min(it.key_hi, it.key_lo + BN);
+        if (n_tiles > 0 && new_lo < new_hi) {
+            for (int e = tid; e < (new_hi - new_lo) * CH; e += THREADS) {
+                const int j = new_lo - it.key_lo + e / CH, c8 = e % CH;
+                const int n = it.key_lo + j;
+                const int pi = p.ps_shift >= 0 ? n >> p.ps_shift : n / p.ps;
+                const int po = p.ps_shift >= 0 ? n & (p.ps - 1) : n % p.ps;
+                const int pg = bt[pi];
+                const bool ok = pg >= 0 && c8 * 8 < d;
+                const __nv_bfloat16* src = ok ? kv + ((((size_t)pg * 2) * p.nkv + kvh) * p.ps + po) * d + c8 * 8 : kv;
+                cp_async16(Ks + j * PITCH + c8 * 8, src, ok ? 16 : 0);
+                cp_async16(Vs + j * PITCH + c8 * 8, ok ? src + v_off : kv, ok ? 16 : 0);
+            }
+        }
+        cp_async_commit();
+    }
     for (int e = tid; e < BM * CH; e += THREADS) {
         const int r = e / CH, c8 = e - r * CH;
         const int R = it.row_base + r;
