@@ -285,6 +285,8 @@ def test_one_far_key_in_a_portion_and_in_a_long_context(ops, nq, L, targets):
     request whose context is long enough for the work-list splits."""
     dtype = torch.bfloat16
     ops.set_compute_dtype(dtype)
+    if nq == 1 and not ops.cluster_attention:
+        pytest.skip("without clusters there is one decode class only")
     nh, nkv, d, ps = 8, 2, 64, 16
     for target in targets:
         q, kv, bt, keys, vals = paged_case([nq], [L], nh, nkv, d, ps, dtype, seed=target)
