@@ -675,8 +675,8 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
 }
 
 // The tensor map of one layer of a pool: rows of 64 bfloat16, boxes of min(page size, 64) rows.
-inline const CUtensorMap* kv_tensor_map(const AttnParams& p) {
-    return tensor_map_bf16(p.kv, (unsigned long long)p.num_pages * 2 * p.nkv * p.ps, D, D, p.ps < BN ? p.ps : BN);
+inline bool kv_tensor_map(CUtensorMap* out, const AttnParams& p) {
+    return tensor_map_bf16(out, p.kv, (unsigned long long)p.num_pages * 2 * p.nkv * p.ps, D, D, p.ps < BN ? p.ps : BN);
 }
 
 // Whether this kernel takes the call: a page is a power of two of at least 8 tokens and the
@@ -694,9 +694,9 @@ inline int launch(const AttnParams& p, cudaStream_t stream) {
                                      (int)cudaSharedmemCarveoutMaxShared));
         attr_set = true;
     }
-    const CUtensorMap* map = kv_tensor_map(p);
-    if (!map) return 1;
-    PL_CUDA(launch_pdl(attn_tc2_kernel, dim3(p.n_work * p.nkv), dim3(THREADS), (size_t)SMEM_BYTES, stream, p, *map));
+    alignas(64) CUtensorMap map;
+    if (!kv_tensor_map(&map, p)) return 1;
+    PL_CUDA(launch_pdl(attn_tc2_kernel, dim3(p.n_work * p.nkv), dim3(THREADS), (size_t)SMEM_BYTES, stream, p, map));
     return 0;
 }
 

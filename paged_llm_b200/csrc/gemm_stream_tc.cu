@@ -279,10 +279,11 @@ PL_EXPORT int pl_gemm_stream_tc(const void* X, int ldx, const void* W, void* Y, 
     p.k_per_split = per * ST_BK;
     p.splitk = (k_blocks + per - 1) / per;
     const int mpad = M <= 32 ? 32 : M <= 64 ? 64 : 128;
-    const CUtensorMap* w_map = tensor_map_bf16(W, (unsigned long long)w_rows, (unsigned long long)K, (unsigned long long)K, 64);
-    const CUtensorMap* x_map = tensor_map_bf16(X, (unsigned long long)M, (unsigned long long)K, (unsigned long long)ldx, mpad);
-    if (!w_map || !x_map) return 1;
-    if (mpad == 32) return launch_stream<32>(p, w_map, x_map, stream);
-    if (mpad == 64) return launch_stream<64>(p, w_map, x_map, stream);
-    return launch_stream<128>(p, w_map, x_map, stream);
+    alignas(64) CUtensorMap w_map, x_map;
+    if (!tensor_map_bf16(&w_map, W, (unsigned long long)w_rows, (unsigned long long)K, (unsigned long long)K, 64) ||
+        !tensor_map_bf16(&x_map, X, (unsigned long long)M, (unsigned long long)K, (unsigned long long)ldx, mpad))
+        return 1;
+    if (mpad == 32) return launch_stream<32>(p, &w_map, &x_map, stream);
+    if (mpad == 64) return launch_stream<64>(p, &w_map, &x_map, stream);
+    return launch_stream<128>(p, &w_map, &x_map, stream);
 }

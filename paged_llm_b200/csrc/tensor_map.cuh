@@ -24,10 +24,10 @@ struct TensorMapKey {
 };
 
 // The map for `rows` x `cols` bfloat16 at `base`, rows `row_stride` elements apart (a multiple
-// of 8), boxes of box_rows x 64.  Out-of-range parts of a box read zeros.  nullptr (with the
-// error recorded) if the driver refuses.
-inline const CUtensorMap* tensor_map_bf16(const void* base, unsigned long long rows, unsigned long long cols,
-                                          unsigned long long row_stride, unsigned box_rows) {
+// of 8), boxes of box_rows x 64, copied to `out`.  Out-of-range parts of a box read zeros.  False
+// (with the error recorded) if the driver refuses.
+inline bool tensor_map_bf16(CUtensorMap* out, const void* base, unsigned long long rows, unsigned long long cols,
+                            unsigned long long row_stride, unsigned box_rows) {
     typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                       const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                       CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -37,25 +37,34 @@ inline const CUtensorMap* tensor_map_bf16(const void* base, unsigned long long r
     std::lock_guard<std::mutex> lock(mu);
     const TensorMapKey key{base, rows, cols, row_stride, box_rows};
     for (auto& m : maps)
-        if (m.first == key) return m.second;
+        if (m.first == key) {
+            *out = *m.second;
+            return true;
+        }
+    // Activations come at ever new addresses when steps are not replayed from graphs: the list is
+    // kept short by starting over (callers get copies).
+    if (maps.size() >= 1024) {
+        for (auto& m : maps) free(m.second);
+        maps.clear();
+    }
     if (!encode) {
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult res;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &res) != cudaSuccess ||
             res != cudaDriverEntryPointSuccess || !fn) {
             pl_fail("tensor map: the driver has no cuTensorMapEncodeTiled");
-            return nullptr;
+            return false;
         }
         encode = (EncodeTiledFn)fn;
     }
     if (((uintptr_t)base & 15) != 0 || row_stride % 8 != 0 || box_rows == 0 || box_rows > 256 || rows == 0 || cols == 0) {
         pl_fail("tensor map: base must be 16-byte aligned, rows a multiple of 16 bytes apart, boxes of 1..256 rows");
-        return nullptr;
+        return false;
     }
     void* mem = nullptr;
     if (posix_memalign(&mem, 64, sizeof(CUtensorMap)) != 0) {
         pl_fail("tensor map: out of host memory");
-        return nullptr;
+        return false;
     }
     CUtensorMap* map = (CUtensorMap*)mem;
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -68,8 +77,9 @@ inline const CUtensorMap* tensor_map_bf16(const void* base, unsigned long long r
     if (rc != CUDA_SUCCESS) {
         free(mem);
         pl_fail("tensor map: cuTensorMapEncodeTiled failed (%d)", (int)rc);
-        return nullptr;
+        return false;
     }
     maps.emplace_back(key, map);
-    return map;
+    *out = *map;
+    return true;
 }
