@@ -31,9 +31,12 @@ NVCC_FLAGS = [
 HEAD_DIM_BUILDS = (16, 32, 64, 128, 256)
 
 MODULES: dict[str, list[str]] = {
-    "core": ["common.cu", "elementwise.cu", "gemm_f32.cu", "gemm_skinny.cu", "gemm_stream_tc.cu", "attention_f32.cu",
+    "core": ["common.cu", "elementwise.cu", "gemm_f32.cu", "gemm_skinny.cu", "gemm_stream_tc.cu", "gemm_tc.cu", "attention_f32.cu",
              "sampling.cu"],
     **{f"attn_bf16_d{d}": ["common.cu", f"attention_bf16_d{d}.cu"] for d in HEAD_DIM_BUILDS},
+    # the many-token tcgen05 product with blocks in pairs that share W tiles (optional: the package runs without
+    # this file, see module_available)
+    "gemm_tc_pair": ["common.cu", "gemm_tc_pair.cu"],
     # decode attention whose scratch is a static array of the library (see attention_decode_static.h)
     "attn_static": ["common.cu", "attention_decode_static.cu"],
 }
@@ -99,6 +102,11 @@ def find_built(name: str) -> str | None:
     return None
 
 
+def module_available(name: str) -> bool:
+    """Whether all sources of an optional module are there."""
+    return name in MODULES and all(os.path.exists(os.path.join(HERE, src)) for src in MODULES[name])
+
+
 def _run(cmd: list[str]) -> None:
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
@@ -158,7 +166,7 @@ def build_module(name: str, verbose: bool = True) -> str:
 
 
 def build_all(verbose: bool = True) -> dict[str, str]:
-    return {name: build_module(name, verbose) for name in MODULES}
+    return {name: build_module(name, verbose) for name in MODULES if module_available(name)}
 
 
 if __name__ == "__main__":

@@ -103,6 +103,18 @@ class CudaOps:
         # 17..128 tokens: this package's tcgen05 kernel with cluster split-K.  Off unless asked for
         # (PAGED_LLM_B200_STREAM_TC=1): measured at 1.5 to 2.5 times the library product's time.
         self.use_stream_tc = os.environ.get("PAGED_LLM_B200_STREAM_TC") is not None
+        # Many tokens: this package's tcgen05 kernel (128 x 256 tiles, fused epilogues) where it is at least
+        # as fast as the library product followed by the elementwise kernel.  Measured: the gate/up product
+        # with SiLU-mul from 2,048 tokens on (78 us against 80 us); the narrower products and fewer tokens are
+        # faster through the library.  PAGED_LLM_B200_GEMM_TC lists the kinds ("silu", "add", "plain", "all",
+        # "" for none) to run on it from 129 tokens on instead.
+        tc_for = os.environ.get("PAGED_LLM_B200_GEMM_TC")
+        self.gemm_tc_min_tokens = 2048 if tc_for is None else 129
+        tc_for = "silu" if tc_for is None else tc_for
+        self.gemm_tc_for = {"silu", "add", "plain"} if tc_for == "all" else {t for t in tc_for.split(",") if t}
+        # its form with blocks in pairs that share W tiles is a module of its own, which may be absent
+        self.gemm_tc_pair = (os.environ.get("PAGED_LLM_B200_NO_GEMM_TC_PAIR") is None
+                             and build.module_available("gemm_tc_pair"))
         self.cluster_attention = os.environ.get("PAGED_LLM_B200_NO_CLUSTER") is None   # decode attention as clusters
         self._argmax_ws = None            # (packed winners, arrival counters) of the multi-block argmax
         self._argmax_keep: list = []
@@ -206,6 +218,24 @@ class CudaOps:
         return (self.use_stream_tc and h.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 16 < M <= 128
                 and K >= 64 and K % 64 == 0 and w.is_contiguous())
 
+    def _gemm_tc_ok(self, h, w: torch.Tensor, kind: str) -> bool:
+        M, K = h.shape
+        return (kind in self.gemm_tc_for and h.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+                and M >= self.gemm_tc_min_tokens
+                and K >= 64 and K % 64 == 0 and w.is_contiguous())
+
+    def _gemm_tc(self, h: torch.Tensor, w: torch.Tensor, out, resid, N: int, epi: int) -> None:
+        M, K = h.shape
+        assert h.stride(1) == 1 and h.stride(0) % 8 == 0
+        if self.gemm_tc_pair:
+            lib = load_module("gemm_tc_pair")
+            fn = lib.pl_gemm_tc_pair
+        else:
+            lib, fn = self.core, self.core.pl_gemm_tc
+        _check(lib, fn(self._p(h), h.stride(0), self._p(w), self._p(out), out.shape[1] if out is not None else 0,
+                       self._p(resid), M, N, K, epi, self._stream))
+        self.launches += 1
+
     def _stream_tc(self, h: torch.Tensor, w: torch.Tensor, out, resid, N: int, epi: int) -> None:
         M, K = h.shape
         assert h.stride(1) == 1 and h.stride(0) % 8 == 0
@@ -233,6 +263,10 @@ class CudaOps:
         if self._stream_ok(h, w):
             out = torch.empty((M, N), dtype=torch.float32 if out_float32 else torch.bfloat16, device=self.device)
             self._stream_tc(h, w, out, None, N, 1 if out_float32 else 0)
+            return out
+        if self._gemm_tc_ok(h, w, "plain") and N % 8 == 0:
+            out = torch.empty((M, N), dtype=torch.float32 if out_float32 else torch.bfloat16, device=self.device)
+            self._gemm_tc(h, w, out, None, N, 1 if out_float32 else 0)
             return out
         if h.dtype == torch.float32:
             assert w.dtype == torch.float32
@@ -264,6 +298,10 @@ class CudaOps:
         if not isinstance(h, LazyNorm) and self._stream_ok(h, w) and x.dtype == torch.float32 and x.is_contiguous():
             self._stream_tc(h, w, None, x, N, 3)                  # the product's epilogue adds to the stream
             return self.rms_norm(x, norm_w, eps)
+        if (not isinstance(h, LazyNorm) and self._gemm_tc_ok(h, w, "add") and x.dtype == torch.float32
+                and x.is_contiguous() and N % 4 == 0):
+            self._gemm_tc(h, w, None, x, N, 3)
+            return self.rms_norm(x, norm_w, eps)
         return self.add_rms_norm(x, self.linear(h, w), norm_w, eps)
 
     def gated_silu_linear(self, h, w_gate_up: torch.Tensor) -> torch.Tensor:
@@ -282,6 +320,10 @@ class CudaOps:
         if self._stream_ok(h, w_gate_up) and h.is_contiguous():
             out = torch.empty((M, I), dtype=torch.bfloat16, device=self.device)
             self._stream_tc(h, w_gate_up, out, None, I, 2)
+            return out
+        if self._gemm_tc_ok(h, w_gate_up, "silu") and h.is_contiguous() and I % 8 == 0:
+            out = torch.empty((M, I), dtype=torch.bfloat16, device=self.device)
+            self._gemm_tc(h, w_gate_up, out, None, I, 2)
             return out
         return self.silu_mul(self.linear(h, w_gate_up))
 

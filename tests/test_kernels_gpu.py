@@ -486,6 +486,51 @@ def _stream_tc_checks(ops, h, w, want, before, M, N, K):
     assert ops.core.pl_gemm_stream_tc_timeouts() == 0
 
 
+@pytest.mark.parametrize("pair", [True, False])
+@pytest.mark.parametrize("M", [129, 256, 300, 2048])
+@pytest.mark.parametrize("N,K", [(2048, 2048), (2560, 2048), (520, 128), (2048, 5632), (1000, 64), (11264, 2048)])
+def test_gemm_tc_product(ops, M, N, K, pair):
+    """More than 128 tokens: the tcgen05 product with 128 x 256 tiles and its epilogues against
+    float32 arithmetic on the same bfloat16 inputs."""
+    if M == 2048 and K != 2048:
+        pytest.skip("the largest M only at the benchmark's K")
+    from paged_llm_b200.csrc import build
+    if pair and not build.module_available("gemm_tc_pair"):
+        pytest.skip("the paired form is not in this checkout")
+    ops.set_compute_dtype(torch.bfloat16)
+    h = randn(M, K, seed=50 + M % 97, dtype=torch.bfloat16)
+    w = randn(N, K, seed=51 + N % 89, dtype=torch.bfloat16, std=K ** -0.5)
+    want = h.float() @ w.float().T
+    was, ops.gemm_tc_for = ops.gemm_tc_for, {"silu", "add", "plain"}
+    was_pair, ops.gemm_tc_pair = ops.gemm_tc_pair, pair
+    was_min, ops.gemm_tc_min_tokens = ops.gemm_tc_min_tokens, 129
+    try:
+        before = ops.launches
+        got = ops.linear(h, w)
+        assert ops.launches == before + 1, "the product did not run on this package's kernel"
+        torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=2e-2)
+        got32 = ops.linear(h, w, out_float32=True)
+        torch.testing.assert_close(got32, want, atol=2e-3, rtol=2e-3)
+        x = randn(M, N, seed=52, dtype=torch.float32)
+        norm_w = randn(N, seed=53, dtype=torch.float32, std=0.1) + 1.0
+        x_new = x.clone()
+        normed = ops.linear_add_rms_norm(h, w, x_new, norm_w, 1e-5)
+        torch.testing.assert_close(x_new, x + want.bfloat16().float(), atol=2e-2, rtol=2e-2)
+        ref = x_new * torch.rsqrt(x_new.pow(2).mean(-1, keepdim=True) + 1e-5) * norm_w
+        torch.testing.assert_close(normed.float(), ref, atol=3e-2, rtol=3e-2)
+        I = N // 2
+        if I % 8 == 0:
+            act = ops.gated_silu_linear(h, w)
+            g, u = want[:, :I].bfloat16().float(), want[:, I:].bfloat16().float()
+            torch.testing.assert_close(act.float(), g * torch.sigmoid(g) * u, atol=3e-2, rtol=3e-2)
+        assert ops.core.pl_gemm_tc_timeouts() == 0
+        if pair:
+            from paged_llm_b200.kernels.ops import load_module
+            assert load_module("gemm_tc_pair").pl_gemm_tc_pair_timeouts() == 0
+    finally:
+        ops.gemm_tc_for, ops.gemm_tc_pair, ops.gemm_tc_min_tokens = was, was_pair, was_min
+
+
 @pytest.mark.parametrize("nh,nkv,d", [(32, 4, 64), (4, 2, 16), (3, 3, 32), (6, 2, 48)])
 @pytest.mark.parametrize("q_lens,k_lens", [([1, 1, 1], [5, 300, 31]), ([5, 1, 7], [5, 300, 31]), ([1], [1])])
 def test_skinny_qkv_rope_write_equals_the_separate_kernels(ops, nh, nkv, d, q_lens, k_lens):
