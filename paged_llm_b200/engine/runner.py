@@ -92,7 +92,8 @@ class ModelRunner:
         self._dev_meta = None
         self._graphs: dict[tuple, object] = {}
         self._portion_seen: dict[tuple, int] = {}
-        self.use_graphs = (not config.enforce_eager) and self.device.type == "cuda" and getattr(ops, "supports_graphs", False)
+        self.use_graphs = ((not config.enforce_eager) and self.device.type == "cuda"
+                           and getattr(ops, "supports_graphs", False) and getattr(model, "capturable", True))
         self.num_graph_steps = 0
         self.num_eager_steps = 0
         self.graph_launches = 0            # kernels of this package launched by graph replays

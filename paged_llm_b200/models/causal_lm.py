@@ -12,9 +12,8 @@ from dataclasses import dataclass
 
 import torch
 
-from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, FixedState, LazyLinear, ModelSpec,
-                          PagedKV, PartSpec, TensorSpec, make_part)
-from ..parts.embedding import LMHead, TokenEmbedding
+from ..parts.base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, FixedState,
+                          LazyLinear, ModelSpec, PagedKV, PartSpec, TensorSpec, make_part)
 
 
 @dataclass(frozen=True)
@@ -40,7 +39,8 @@ class CausalLM:
         self.spec = spec
         self.positions = {name: make_part(POSITION_ENCODINGS, "position encoding", ps)
                           for name, ps in spec.positions.items()}
-        self.embedding = TokenEmbedding(weights=spec.embedding.weights, **spec.embedding.params)
+        emb_spec, extra = _resolve_positions(spec.embedding, self.positions)
+        self.embedding = make_part(EMBEDDINGS, "embedding", emb_spec, **extra)
         self.blocks = []
         for layer in spec.layers:
             mixer_spec, extra = _resolve_positions(layer.mixer, self.positions)
@@ -53,7 +53,7 @@ class CausalLM:
                 raise KeyError(f"unknown block {layer.block!r}; registered: {sorted(BLOCKS)}") from None
             self.blocks.append(block_cls(mixer, ffn, norms))
         self.final_norm = make_part(NORMS, "norm", spec.final_norm)
-        self.head = LMHead(weights=spec.head.weights, **spec.head.params)
+        self.head = make_part(HEADS, "head", spec.head)
         self.schedule = list(spec.schedule)
         for i, entry in enumerate(self.schedule):
             if not 0 <= entry.layer < len(self.blocks):
@@ -87,6 +87,11 @@ class CausalLM:
     def prepare(self, max_positions: int, device, ops) -> None:
         for pos in self.positions.values():
             pos.prepare(max_positions, device, ops)
+
+    @property
+    def capturable(self) -> bool:
+        """True if every part allows a step to be captured and replayed."""
+        return all(part.capturable for part in self._parts())
 
     def weight_bytes_per_step(self) -> int:
         """Bytes of weights a decode step reads: every scheduled run reads its

@@ -143,6 +143,12 @@ class Part:
     # one into a tensor).  Parts that look at their input themselves leave this False.
     accepts_lazy_input = False
 
+    # True if `forward` only launches work on the step's stream from the step's device
+    # metadata, so that a decode step may be captured once and replayed.  A part that reads
+    # `ctx.host`, waits for the device (e.g. to count rows) or allocates by data sets it
+    # False; a model with one such part runs every step eagerly.
+    capturable = True
+
     def tensor_specs(self) -> dict[str, TensorSpec]:
         """Checkpoint tensor name -> expectation."""
         return {}
@@ -171,6 +177,23 @@ class PositionEncoding(Part):
     """Owns what positions turn into (for rotary: the cos/sin table)."""
 
     def prepare(self, max_positions: int, device, ops) -> None:
+        raise NotImplementedError
+
+
+class Embedding(Part):
+    """Turns the step's token ids into the residual stream."""
+
+    def forward(self, ids: torch.Tensor, ctx) -> torch.Tensor:
+        """ids: [T] int32 -> [T, hidden] float32 (the residual dtype).  A spec may give the
+        part a `position` parameter naming a position encoding; it arrives as the object."""
+        raise NotImplementedError
+
+
+class Head(Part):
+    """Turns normalised rows into logits."""
+
+    def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
+        """h: [rows, hidden] in the compute dtype -> [rows, vocab] float32."""
         raise NotImplementedError
 
 
@@ -219,6 +242,10 @@ class Block(Part):
     def bytes_read_per_step(self):
         return sum(p.bytes_read_per_step() for p in (self.mixer, self.feed_forward, *self.norms.values()))
 
+    @property
+    def capturable(self):
+        return all(p.capturable for p in (self.mixer, self.feed_forward, *self.norms.values()))
+
 
 # --------------------------------------------------------------------------- registries
 
@@ -227,6 +254,8 @@ FEED_FORWARDS: dict[str, Callable[..., FeedForward]] = {}
 NORMS: dict[str, Callable[..., Norm]] = {}
 POSITION_ENCODINGS: dict[str, Callable[..., PositionEncoding]] = {}
 BLOCKS: dict[str, Callable[..., Block]] = {}
+EMBEDDINGS: dict[str, Callable[..., Embedding]] = {}
+HEADS: dict[str, Callable[..., Head]] = {}
 
 
 def _register(table: dict, what: str):
@@ -245,6 +274,8 @@ register_feed_forward = _register(FEED_FORWARDS, "feed-forward")
 register_norm = _register(NORMS, "norm")
 register_position_encoding = _register(POSITION_ENCODINGS, "position encoding")
 register_block = _register(BLOCKS, "block")
+register_embedding = _register(EMBEDDINGS, "embedding")
+register_head = _register(HEADS, "head")
 
 
 def make_part(table: dict, what: str, spec: PartSpec, **extra):

@@ -8,10 +8,11 @@ then ignored, as tying means the embedding is used.
 
 from __future__ import annotations
 
-from .base import Part, TensorSpec
+from .base import Embedding, Head, TensorSpec, register_embedding, register_head
 
 
-class TokenEmbedding(Part):
+@register_embedding("embedding")
+class TokenEmbedding(Embedding):
     def __init__(self, weights: dict[str, str], vocab_size: int, hidden_size: int):
         self.vocab_size, self.hidden_size = vocab_size, hidden_size
         self.name = weights["weight"]
@@ -27,7 +28,8 @@ class TokenEmbedding(Part):
         return ctx.ops.embedding(self.weight, ids)
 
 
-class LMHead(Part):
+@register_head("lm_head")
+class LMHead(Head):
     accepts_lazy_input = True
 
     def __init__(self, weights: dict[str, str], vocab_size: int, hidden_size: int, tied_to: str | None = None):

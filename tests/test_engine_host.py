@@ -12,6 +12,7 @@ from paged_llm_b200.engine.replay import TraceReplayer
 from paged_llm_b200.engine.runner import StepItem
 from paged_llm_b200.engine.sequence import Sequence
 from tests import plain_llama, schedules
+from tests.helpers import assert_logits_close
 from tests.tiny import TINIES, make_folder, random_tokens, read_folder
 from tests.torch_ops import TorchOps
 
@@ -223,3 +224,36 @@ def test_toy_architecture_with_state_steps_on_the_host(tmp_path):
     for rid, toks in reqs.items():
         assert np.abs(got[rid] - plain_toy_logits(cfg, w, toks).numpy()).max() < 2e-5, rid
     assert rp.cm.num_free_state_slots == rp.cm.num_state_slots
+
+
+@pytest.mark.parametrize("which", ["A", "B"])
+def test_routed_toy_steps_on_the_host(tmp_path, which):
+    """A position encoding, an embedding and a routed feed-forward of the test's own:
+    registered, built from a written folder and stepped, no change to the package."""
+    from paged_llm_b200.weights import write_model_folder
+    from tests.toy_parts import ROUTED_TOY_A, ROUTED_TOY_B, RoutedToyConfig, plain_routed_toy_logits
+
+    hf = {"A": ROUTED_TOY_A, "B": ROUTED_TOY_B}[which]
+    write_model_folder(str(tmp_path), RoutedToyConfig.from_hf_dict(hf), seed=6, std=0.1, norm_std=0.05)
+    cfg, w = read_folder(tmp_path)
+    assert cfg == hf
+    V = hf["vocab_size"]
+    reqs = {"a": random_tokens(V, 45, 1), "b": random_tokens(V, 70, 2), "c": random_tokens(V, 33, 3)}
+    steps, max_tokens = schedules.mixed(reqs, live=2, seed=5)
+    rp = TraceReplayer(str(tmp_path), "float32", max_tokens, device="cpu", ops=TorchOps())
+    assert rp.storage.num_state_slots == 0 and rp.storage.num_groups == 1
+    outputs = {rec["step"]: out for rec in steps if (out := rp.step(rec)) is not None}
+    got = schedules.collect(steps, outputs)
+    for rid, toks in reqs.items():
+        assert_logits_close(got[rid], plain_routed_toy_logits(cfg, w, toks).numpy(), "float32", rid)
+
+
+def test_learned_positions_refuse_a_position_beyond_the_table(tmp_path):
+    from paged_llm_b200.weights import write_model_folder
+    from tests.toy_parts import ROUTED_TOY_A, RoutedToyConfig
+
+    hf = {**ROUTED_TOY_A, "max_position_embeddings": 8}
+    write_model_folder(str(tmp_path), RoutedToyConfig.from_hf_dict(hf), seed=6, std=0.2)
+    rp = TraceReplayer(str(tmp_path), "float32", 64, device="cpu", ops=TorchOps())
+    with pytest.raises(ValueError, match="the table has 8 rows"):
+        rp.step({"step": 0, "entries": [{"id": "a", "tokens": list(range(9)), "want": []}], "end": []})

@@ -137,6 +137,30 @@ def test_toy_architecture_with_state(tmp_path, dtype):
     assert rp.cm.num_free_state_slots == rp.cm.num_state_slots and rp.runner.num_graph_steps == 0
 
 
+@pytest.mark.parametrize("which,dtype", [("A", "float32"), ("B", "float32"), ("B", "bfloat16")])
+def test_routed_toy_architecture(tmp_path, which, dtype):
+    """A learned table of positions added by an embedding of the test's own, attention that
+    rotates nothing, and a feed-forward that routes tokens to experts: registered by the test,
+    run through the real loader, cache manager, step function and kernels."""
+    from paged_llm_b200.engine.replay import TraceReplayer
+    from paged_llm_b200.weights import write_model_folder
+    from tests.toy_parts import ROUTED_TOY_A, ROUTED_TOY_B, RoutedToyConfig, plain_routed_toy_logits
+
+    hf = {"A": ROUTED_TOY_A, "B": ROUTED_TOY_B}[which]
+    # the folder holds the weights in the dtype under test, so both sides read the same values
+    write_model_folder(str(tmp_path), RoutedToyConfig.from_hf_dict(hf), seed=6, std=0.1, norm_std=0.05, dtype=dtype)
+    cfg, w = read_folder(tmp_path)
+    V = hf["vocab_size"]
+    reqs = {"a": random_tokens(V, 45, 1), "b": random_tokens(V, 70, 2), "c": random_tokens(V, 33, 3)}
+    steps, max_tokens = schedules.mixed(reqs, live=2, seed=5)
+    rp = TraceReplayer(str(tmp_path), dtype, max_tokens, poison=float("nan"))
+    outputs = {rec["step"]: out for rec in steps if (out := rp.step(rec)) is not None}
+    got = schedules.collect(steps, outputs)
+    for rid, toks in reqs.items():
+        assert_logits_close(got[rid], plain_routed_toy_logits(cfg, w, toks).numpy(), dtype, f"routed toy/{rid}")
+    assert rp.runner.num_graph_steps == 0, "a model with a part that is not capturable steps eagerly"
+
+
 def test_layers_of_one_model_may_differ(tmp_path):
     """Per-layer choice of parts: a Llama whose second layer has a window and
     other head counts gets two cache groups and still matches the plain model."""

@@ -3,7 +3,10 @@ position encoding can be registered, built and stepped without touching the
 package: a mixer with per-request state of fixed size (a running mean of the
 request's hidden vectors), written in plain tensor code on top of the step
 context, and an architecture that alternates it with attention layers, runs one
-layer twice and lets one run read another run's cache."""
+layer twice and lets one run read another run's cache; and a second architecture
+with a learned table of absolute positions that its embedding adds (attention
+then rotates nothing), a feed-forward that routes each token to some of its
+experts, and a head of its own."""
 
 from __future__ import annotations
 
@@ -13,12 +16,16 @@ import torch
 
 from paged_llm_b200.config.model import ModelConfig
 from paged_llm_b200.config.registry import ARCHITECTURES, register_architecture
-from paged_llm_b200.parts import (MIXERS, FixedState, LayerSpec, Mixer, ModelSpec, PartSpec, ScheduleEntry,
-                                  TensorSpec, register_mixer)
+from paged_llm_b200.parts import (EMBEDDINGS, FEED_FORWARDS, MIXERS, POSITION_ENCODINGS, Embedding, FeedForward,
+                                  FixedState, LayerSpec, Mixer, ModelSpec, PartSpec, PositionEncoding, ScheduleEntry,
+                                  TensorSpec, materialize, register_embedding, register_feed_forward, register_mixer,
+                                  register_position_encoding)
 
 
 class RunningMeanMixer(Mixer):
     """state = (sum of h over the request so far, count); out[t] = W (sum_t / count_t)."""
+
+    capturable = False          # walks the requests on the host
 
     def __init__(self, weights, hidden_size: int):
         self.hidden_size = hidden_size
@@ -148,3 +155,193 @@ def plain_toy_logits(cfg: dict, w: dict, tokens) -> torch.Tensor:
             kv1 = kv
     x, _ = layer(x, 1, shared_kv=kv1)
     return pl.rms_norm(x, w["toy.norm.weight"], 1e-5) @ w["toy.embed.weight"].T
+
+
+# --------------------------------------------------------------------------- a second toy: learned positions, routing
+
+class LearnedAbsolutePositions(PositionEncoding):
+    """A table with one vector of the model's width per position, read from the checkpoint."""
+
+    capturable = False          # `encode` checks the step's positions on the host
+
+    def __init__(self, weights, max_positions: int, hidden_size: int):
+        self.rows, self.hidden_size = max_positions, hidden_size
+        self.name = weights["table"]
+        self.table = None
+
+    def tensor_specs(self):
+        return {self.name: TensorSpec((self.rows, self.hidden_size))}
+
+    def load(self, tensors):
+        self.table = tensors[self.name].contiguous()
+
+    def prepare(self, max_positions, device, ops):
+        pass        # nothing to compute: the table is a weight; `encode` refuses positions beyond it
+
+    def encode(self, ctx):
+        """[T, hidden] float32: the vectors of the step's positions."""
+        if max(ctx.host.k_lens) > self.rows:
+            raise ValueError(f"a request reaches position {max(ctx.host.k_lens) - 1}, the table has {self.rows} rows")
+        return ctx.ops.embedding(self.table, ctx.positions)
+
+
+class PositionedEmbedding(Embedding):
+    """x[t] = E[ids[t]] + P[position[t]], summed in float32."""
+
+    def __init__(self, weights, vocab_size: int, hidden_size: int, position):
+        self.vocab_size, self.hidden_size, self.position = vocab_size, hidden_size, position
+        self.name = weights["weight"]
+        self.weight = None
+
+    def tensor_specs(self):
+        return {self.name: TensorSpec((self.vocab_size, self.hidden_size))}
+
+    def load(self, tensors):
+        self.weight = tensors[self.name].contiguous()
+
+    def forward(self, ids, ctx):
+        return ctx.ops.embedding(self.weight, ids).add_(self.position.encode(ctx))
+
+
+class RoutedMLP(FeedForward):
+    """Router logits in float32, the `top_k` largest kept and softmaxed over the kept ones;
+    out[t] = sum over kept experts e of p[t, e] * down_e(silu(gate_e h[t]) * up_e h[t])."""
+
+    capturable = False          # counts each expert's rows on the host
+
+    def __init__(self, weights, hidden_size: int, intermediate_size: int, num_experts: int, top_k: int):
+        if not 0 < top_k <= num_experts:
+            raise ValueError(f"top_k={top_k} must lie in 1..num_experts={num_experts}")
+        self.h, self.i, self.e, self.k = hidden_size, intermediate_size, num_experts, top_k
+        self.names = weights
+        self.router = self.gate_up = self.down = None
+
+    def _expert(self, e, which):
+        return self.names["experts"].format(expert=e, proj=which)
+
+    def tensor_specs(self):
+        out = {self.names["router"]: TensorSpec((self.e, self.h))}
+        for e in range(self.e):
+            out[self._expert(e, "gate_proj")] = TensorSpec((self.i, self.h))
+            out[self._expert(e, "up_proj")] = TensorSpec((self.i, self.h))
+            out[self._expert(e, "down_proj")] = TensorSpec((self.h, self.i))
+        return out
+
+    def load(self, tensors):
+        self.router = tensors[self.names["router"]].float()
+        self.gate_up = [torch.cat([tensors[self._expert(e, "gate_proj")], tensors[self._expert(e, "up_proj")]]).contiguous()
+                        for e in range(self.e)]
+        self.down = [tensors[self._expert(e, "down_proj")].contiguous() for e in range(self.e)]
+
+    def forward(self, h, ctx):
+        ops = ctx.ops
+        logits = h.float() @ self.router.T
+        top, chosen = logits.topk(self.k, dim=-1)
+        probs = torch.softmax(top, dim=-1)
+        out = torch.zeros(h.shape, dtype=torch.float32, device=h.device)
+        for e in range(self.e):
+            rows, slot = (chosen == e).nonzero(as_tuple=True)
+            if rows.numel() == 0:
+                continue
+            y = materialize(ops.linear(ops.gated_silu_linear(h[rows].contiguous(), self.gate_up[e]), self.down[e]), ops)
+            out.index_add_(0, rows, y.float() * probs[rows, slot][:, None])
+        return out.to(h.dtype)
+
+
+if "toy_learned_absolute" not in POSITION_ENCODINGS:
+    register_position_encoding("toy_learned_absolute")(LearnedAbsolutePositions)
+if "toy_positioned_embedding" not in EMBEDDINGS:
+    register_embedding("toy_positioned_embedding")(PositionedEmbedding)
+if "toy_routed_mlp" not in FEED_FORWARDS:
+    register_feed_forward("toy_routed_mlp")(RoutedMLP)
+
+
+@dataclass(frozen=True)
+class RoutedToyConfig(ModelConfig):
+    intermediate_size: int = 0
+    num_heads: int = 0
+    num_kv_heads: int = 0
+    head_dim: int = 0
+    num_experts: int = 0
+    top_k: int = 0
+    eps: float = 1e-5
+
+    KEYS = ("intermediate_size", "num_heads", "num_kv_heads", "head_dim", "num_experts", "top_k", "eps")
+
+    @classmethod
+    def from_hf_dict(cls, d, architecture="RoutedToyForCausalLM"):
+        return cls(architecture, d["vocab_size"], d["hidden_size"], d["num_hidden_layers"],
+                   d["max_position_embeddings"], d.get("torch_dtype", "float32"), *(d[k] for k in cls.KEYS))
+
+    def to_hf_dict(self):
+        return {"architectures": [self.architecture], "vocab_size": self.vocab_size, "hidden_size": self.hidden_size,
+                "num_hidden_layers": self.num_hidden_layers, "max_position_embeddings": self.max_position_embeddings,
+                "torch_dtype": self.torch_dtype, **{k: getattr(self, k) for k in self.KEYS}}
+
+
+def routed_toy_spec(cfg: RoutedToyConfig) -> ModelSpec:
+    h = cfg.hidden_size
+    layers = []
+    for i in range(cfg.num_hidden_layers):
+        p = f"rt.layers.{i}."
+        mixer = PartSpec("paged_attention", dict(hidden_size=h, num_heads=cfg.num_heads, num_kv_heads=cfg.num_kv_heads,
+                                                 head_dim=cfg.head_dim, position=None),
+                         {k: f"{p}attn.{k}.weight" for k in ("q_proj", "k_proj", "v_proj", "o_proj")})
+        ffn = PartSpec("toy_routed_mlp", dict(hidden_size=h, intermediate_size=cfg.intermediate_size,
+                                              num_experts=cfg.num_experts, top_k=cfg.top_k),
+                       {"router": p + "router.weight", "experts": p + "experts.{expert}.{proj}.weight"})
+        norms = {"input": PartSpec("rms_norm", dict(dim=h, eps=cfg.eps), {"weight": p + "norm1.weight"}),
+                 "post_mixer": PartSpec("rms_norm", dict(dim=h, eps=cfg.eps), {"weight": p + "norm2.weight"})}
+        layers.append(LayerSpec("pre_norm", mixer, ffn, norms))
+    return ModelSpec(
+        hidden_size=h, vocab_size=cfg.vocab_size,
+        embedding=PartSpec("toy_positioned_embedding", dict(vocab_size=cfg.vocab_size, hidden_size=h, position="learned"),
+                           {"weight": "rt.embed.weight"}),
+        layers=layers, schedule=[ScheduleEntry(i) for i in range(cfg.num_hidden_layers)],
+        final_norm=PartSpec("rms_norm", dict(dim=h, eps=cfg.eps), {"weight": "rt.norm.weight"}),
+        head=PartSpec("lm_head", dict(vocab_size=cfg.vocab_size, hidden_size=h), {"weight": "rt.head.weight"}),
+        positions={"learned": PartSpec("toy_learned_absolute", dict(max_positions=cfg.max_position_embeddings,
+                                                                    hidden_size=h), {"table": "rt.positions.weight"})})
+
+
+if "RoutedToyForCausalLM" not in ARCHITECTURES:
+    register_architecture("RoutedToyForCausalLM", RoutedToyConfig, routed_toy_spec)
+
+# top_k < num_experts: a token's experts change with its hidden vector (float32 only: in bfloat16 a
+# near-tie may fall to the other side, which is a property of routing, not a fault of the engine).
+ROUTED_TOY_A = {"architectures": ["RoutedToyForCausalLM"], "vocab_size": 53, "hidden_size": 40, "num_hidden_layers": 2,
+                "intermediate_size": 24, "num_heads": 4, "num_kv_heads": 2, "head_dim": 16, "num_experts": 4,
+                "top_k": 2, "eps": 1e-5, "max_position_embeddings": 160, "torch_dtype": "float32"}
+# top_k == num_experts: every expert weighs in, so the output is continuous in the router's logits.
+ROUTED_TOY_B = {"architectures": ["RoutedToyForCausalLM"], "vocab_size": 47, "hidden_size": 96, "num_hidden_layers": 3,
+                "intermediate_size": 64, "num_heads": 3, "num_kv_heads": 1, "head_dim": 32, "num_experts": 3,
+                "top_k": 3, "eps": 1e-6, "max_position_embeddings": 192, "torch_dtype": "float32"}
+
+
+def plain_routed_toy_logits(cfg: dict, w: dict, tokens) -> torch.Tensor:
+    """Whole-sequence float32 oracle of the routed toy, from tests/plain_llama.py's parts."""
+    from tests import plain_llama as pl
+
+    w = {k: v.float() for k, v in w.items()}
+    heads, kvh, d = cfg["num_heads"], cfg["num_kv_heads"], cfg["head_dim"]
+    toks = torch.as_tensor(tokens, dtype=torch.long)
+    T = toks.numel()
+    x = w["rt.embed.weight"][toks] + w["rt.positions.weight"][:T]
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"rt.layers.{i}."
+        y = pl.rms_norm(x, w[p + "norm1.weight"], cfg["eps"])
+        q = (y @ w[p + "attn.q_proj.weight"].T).view(T, heads, d)
+        k = (y @ w[p + "attn.k_proj.weight"].T).view(T, kvh, d)
+        v = (y @ w[p + "attn.v_proj.weight"].T).view(T, kvh, d)
+        x = x + pl.causal_attention(q, k, v, d ** -0.5).reshape(T, -1) @ w[p + "attn.o_proj.weight"].T
+        y = pl.rms_norm(x, w[p + "norm2.weight"], cfg["eps"])
+        top, chosen = (y @ w[p + "router.weight"].T).topk(cfg["top_k"], dim=-1)
+        probs = torch.softmax(top, dim=-1)
+        f = torch.zeros_like(x)
+        for t in range(T):
+            for j in range(cfg["top_k"]):
+                e = f"{p}experts.{int(chosen[t, j])}."
+                f[t] += probs[t, j] * pl.gated_mlp(y[t:t + 1], w[e + "gate_proj.weight"], w[e + "up_proj.weight"],
+                                                   w[e + "down_proj.weight"])[0]
+        x = x + f
+    return pl.rms_norm(x, w["rt.norm.weight"], cfg["eps"]) @ w["rt.head.weight"].T
