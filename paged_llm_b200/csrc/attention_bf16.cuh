@@ -492,7 +492,7 @@ int launch_attn_cluster(const AttnParams& p, cudaStream_t stream) {
 
 }  // namespace
 
-#if PL_DPAD == 64
+#if PL_DPAD == 64 || PL_DPAD == 128
 #include "attention_tc.cuh"
 // Waits inside the tcgen05 kernel that gave up since the library was loaded (0 unless something is broken).
 PL_EXPORT int pl_attention_tc_timeouts() {
@@ -523,11 +523,15 @@ PL_EXPORT int PL_CAT(pl_attention_bf16_d, PL_DPAD)(const AttnParams* params, cud
     constexpr int KPW_SMALL = PL_DPAD <= 128 ? 32 : 16;
     if (p.cluster > 0) return launch_attn_cluster<PL_DPAD, KPW_SMALL>(p, stream);
     if (p.is_small) return launch_attn_bf16<PL_DPAD, 1, 4, KPW_SMALL>(p, stream);
-#if PL_DPAD == 64
-    // prefill tiles of head size 64 run on tcgen05 with tensor-memory accumulators
+#if PL_DPAD == 64 || PL_DPAD == 128
+    // prefill tiles of head sizes 64 and 128 run on tcgen05 with tensor-memory accumulators
     static const bool no_tc = getenv("PAGED_LLM_B200_NO_TCGEN05") != nullptr;
+#if PL_DPAD == 64
     static const bool serial_tc = getenv("PAGED_LLM_B200_TC_SERIAL") != nullptr;     // the block-synchronous variant
-    if (p.d == 64 && !no_tc) return serial_tc || !tc2::takes(p) ? tc::launch(p, stream) : tc2::launch(p, stream);
+    if (p.d == 64 && !no_tc) return serial_tc || !tc2::takes(p) ? tc::launch(p, stream) : tc2::launch<64>(p, stream);
+#else
+    if (p.d == 128 && !no_tc && tc2::takes(p)) return tc2::launch<128>(p, stream);
+#endif
 #endif
     return launch_attn_bf16<PL_DPAD, PL_LARGE_MW, 1, 64>(p, stream);
 }

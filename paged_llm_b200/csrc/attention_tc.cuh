@@ -349,13 +349,23 @@ __device__ unsigned long long g_prof[32];
 #define PROF_FLUSH(base, n)
 #endif
 
-constexpr int BM = 128, BN = 64, D = 64, STAGES = 4;
+constexpr int BM = 128, BN = 64;
 constexpr int SOFTMAX_WARPS = 4, MMA_WARP = 4, K_WARP = 5, V_WARP = 6;
 constexpr int THREADS = (SOFTMAX_WARPS + 3) * 32;                   // 224
-constexpr int TMEM_COLS = 256;               // S0 / P0: 0..63, S1 / P1: 64..127, O: 128..191
+constexpr int TMEM_COLS = 256;               // S0 / P0: 0..63, S1 / P1: 64..127, O: 128..128+D-1
 constexpr float LAZY_LOG2 = 8.f;
-constexpr int Q_BYTES = BM * 128, K_BYTES = BN * 128;
-constexpr int SMEM_BYTES = Q_BYTES + 2 * STAGES * K_BYTES + 1024;
+// A head of D elements is D / 64 panels of 64 elements (128 bytes, the span of the swizzle): Q,
+// a stage of keys and a stage of values are each `PANELS` tiles of [rows][128 B], one behind the
+// other.  Two blocks share an SM for either head size, so the deeper rows get the shallower ring.
+template <int D>
+struct Shape {
+    static_assert(D == 64 || D == 128, "head sizes 64 and 128");
+    static constexpr int PANELS = D / 64;
+    static constexpr int STAGES = D == 64 ? 4 : 2;
+    static constexpr int Q_PANEL = BM * 128, K_PANEL = BN * 128;
+    static constexpr int Q_BYTES = PANELS * Q_PANEL, K_BYTES = PANELS * K_PANEL;
+    static constexpr int SMEM_BYTES = Q_BYTES + 2 * STAGES * K_BYTES + 1024;
+};
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(saddr(bar)) : "memory");
@@ -363,12 +373,12 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 __device__ __forceinline__ void mbar_arrive_expect(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(saddr(bar)), "r"(bytes) : "memory");
 }
-// One box of the tensor map at rows [row, row + box rows), all 64 columns, to shared memory;
-// the bytes are counted on `bar`.
-__device__ __forceinline__ void tma_box(void* dst, const CUtensorMap* map, int row, uint64_t* bar) {
+// One box of the tensor map at rows [row, row + box rows), columns [col, col + 64) (col a
+// multiple of 64), to shared memory; the bytes are counted on `bar`.
+__device__ __forceinline__ void tma_box(void* dst, const CUtensorMap* map, int col, int row, uint64_t* bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::
-            "r"(saddr(dst)), "l"(map), "r"(0), "r"(row), "r"(saddr(bar))
+            "r"(saddr(dst)), "l"(map), "r"(col), "r"(row), "r"(saddr(bar))
         : "memory");
 }
 // Two float32 operations in one instruction (sm_100): the pair lives in a 64-bit register.
@@ -416,7 +426,13 @@ __device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&v)[64]) {
     for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// WIDE (head size 128 only): O += P V as one product 128 x 128 x 16 per step, the value panels
+// being the two 64-column groups of its MN-major operand, instead of one product per panel.
+template <int D, bool WIDE>
 __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, const __grid_constant__ CUtensorMap kv_map) {
+    using SH = Shape<D>;
+    constexpr int PANELS = SH::PANELS, STAGES = SH::STAGES, Q_PANEL = SH::Q_PANEL, K_PANEL = SH::K_PANEL;
+    constexpr int Q_BYTES = SH::Q_BYTES, K_BYTES = SH::K_BYTES;
     pdl_launch_dependents();
     pdl_wait();
     const AttnItem it = attn_decode_item(p, blockIdx.x / p.nkv, BM, BN);
@@ -424,9 +440,9 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
 
     extern __shared__ unsigned char smem_unaligned[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_unaligned + 1023) & ~(uintptr_t)1023);
-    unsigned char* Qs = smem;                                  // [128][128 B]
-    unsigned char* Ks = Qs + Q_BYTES;                          // [STAGES][64 keys][128 B]
-    unsigned char* Vs = Ks + STAGES * K_BYTES;                 // [STAGES][64 keys][128 B]
+    unsigned char* Qs = smem;                                  // [PANELS][128][128 B]
+    unsigned char* Ks = Qs + Q_BYTES;                          // [STAGES][PANELS][64 keys][128 B]
+    unsigned char* Vs = Ks + STAGES * K_BYTES;                 // [STAGES][PANELS][64 keys][128 B]
     __shared__ uint64_t k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
     __shared__ uint64_t s_full[2], p_full[2], pv_done[2];
     __shared__ uint32_t tmem_base_slot;
@@ -456,14 +472,14 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
         }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    // Q tile: row R = token * G + head; eight 16-byte chunks per row
-    for (int e = tid; e < BM * 8; e += THREADS) {
-        const int r = e >> 3, c = e & 7;
+    // Q tile: row R = token * G + head; eight 16-byte chunks per row and panel
+    for (int e = tid; e < BM * 8 * PANELS; e += THREADS) {
+        const int r = e / (8 * PANELS), c16 = e % (8 * PANELS);
         const int R = it.row_base + r;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (R < it.rows_total)
-            v = *reinterpret_cast<const uint4*>(q + (size_t)(it.q0 + R / G) * p.q_stride + (kvh * G + R % G) * D + c * 8);
-        *reinterpret_cast<uint4*>(Qs + swz(r, c)) = v;
+            v = *reinterpret_cast<const uint4*>(q + (size_t)(it.q0 + R / G) * p.q_stride + (kvh * G + R % G) * D + c16 * 8);
+        *reinterpret_cast<uint4*>(Qs + (c16 >> 3) * Q_PANEL + swz(r, c16 & 7)) = v;
     }
     fence_async_smem();
     fence_before_sync();
@@ -497,12 +513,14 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
             PROF(1)
             const bool ok = pg >= 0;
             const int n_ok = __popc(__ballot_sync(0xffffffffu, ok));
-            if (lane == 0) mbar_arrive_expect(&full[s], n_ok * box_bytes);
+            if (lane == 0) mbar_arrive_expect(&full[s], n_ok * box_bytes * PANELS);
             __syncwarp();
             if (ok) {
                 const int n0 = key0 + t * BN + lane * box_rows;
                 const int row = (pg * 2 * p.nkv + kvh) * p.ps + (n0 & (p.ps - 1)) + row_add;
-                tma_box(ring + s * K_BYTES + lane * box_bytes, &kv_map, row, &full[s]);
+#pragma unroll
+                for (int c = 0; c < PANELS; ++c)
+                    tma_box(ring + s * K_BYTES + c * K_PANEL + lane * box_bytes, &kv_map, c * 64, row, &full[s]);
             }
             PROF(2)
         }
@@ -510,7 +528,7 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
     } else if (warp == MMA_WARP) {
         // ---------------------------------------------------------------- product warp: one thread issues
         if (lane == 0) {
-            constexpr uint32_t IDESC_S = instr_desc(BM, BN, false), IDESC_O = instr_desc(BM, D, true);
+            constexpr uint32_t IDESC_S = instr_desc(BM, BN, false), IDESC_O = instr_desc(BM, WIDE ? D : 64, true);
             const uint32_t qa = saddr(Qs);
             PROF_DECL
             auto issue_s = [&](int t) {                     // S[t & 1] = Q K(t)^T
@@ -522,9 +540,9 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
                 fence_after_sync();
                 const uint32_t ka = saddr(Ks + s * K_BYTES);
 #pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk)
-                    mma_f16(tmem_base + b * 64, smem_desc(qa + kk * 32, 16, 1024), smem_desc(ka + kk * 32, 16, 1024),
-                            IDESC_S, kk > 0);
+                for (int kk = 0; kk < D / 16; ++kk)          // four steps of 16 elements per panel
+                    mma_f16(tmem_base + b * 64, smem_desc(qa + (kk >> 2) * Q_PANEL + (kk & 3) * 32, 16, 1024),
+                            smem_desc(ka + (kk >> 2) * K_PANEL + (kk & 3) * 32, 16, 1024), IDESC_S, kk > 0);
                 mma_commit(&s_full[b]);
                 mma_commit(&k_empty[s]);
                 PROF(2)
@@ -541,9 +559,18 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
                 fence_after_sync();
                 const uint32_t va = saddr(Vs + su * K_BYTES);
 #pragma unroll
-                for (int kk = 0; kk < BN / 16; ++kk)          // P from tensor memory: 8 packed columns per step
-                    mma_f16_ts(tmem_base + 128, tmem_base + bu * 64 + kk * 8, smem_desc(va + kk * 2048, 16, 1024),
-                               IDESC_O, u > 0 || kk > 0);
+                for (int kk = 0; kk < BN / 16; ++kk) {        // P from tensor memory: 8 packed columns per step
+                    if (WIDE) {
+                        // groups of 64 columns of the MN-major operand lie a panel apart
+                        mma_f16_ts(tmem_base + 128, tmem_base + bu * 64 + kk * 8, smem_desc(va + kk * 2048, K_PANEL, 1024),
+                                   IDESC_O, u > 0 || kk > 0);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < PANELS; ++c)
+                            mma_f16_ts(tmem_base + 128 + c * 64, tmem_base + bu * 64 + kk * 8,
+                                       smem_desc(va + c * K_PANEL + kk * 2048, 16, 1024), IDESC_O, u > 0 || kk > 0);
+                    }
+                }
                 mma_commit(&pv_done[bu]);
                 mma_commit(&v_empty[su]);
                 PROF(4)
@@ -619,12 +646,13 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
                 __syncwarp();
                 fence_after_sync();
                 PROF(4)
-                {
-                    tmem_ld64(tmem_o, sv);
+#pragma unroll
+                for (int c = 0; c < PANELS; ++c) {
+                    tmem_ld64(tmem_o + c * 64, sv);
 #pragma unroll
                     for (int i = 0; i < 64; ++i) sv[i] *= alpha;
-                    tmem_st32(tmem_o, reinterpret_cast<const float(&)[32]>(sv[0]));
-                    tmem_st32(tmem_o + 32, reinterpret_cast<const float(&)[32]>(sv[32]));
+                    tmem_st32(tmem_o + c * 64, reinterpret_cast<const float(&)[32]>(sv[0]));
+                    tmem_st32(tmem_o + c * 64 + 32, reinterpret_cast<const float(&)[32]>(sv[32]));
                     tmem_st_wait();
                 }
                 PROF(5)
@@ -634,8 +662,8 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
                 // page may hold anything behind the last token).
                 mbar_wait(&v_full[t % STAGES], (t / STAGES) & 1);
                 unsigned char* vd = Vs + (t % STAGES) * K_BYTES;
-                for (int e = tid; e < BN * 8; e += SOFTMAX_WARPS * 32) {
-                    const int n = kbase + (e >> 3);
+                for (int e = tid; e < BN * 8 * PANELS; e += SOFTMAX_WARPS * 32) {      // panels are [64 keys][8 chunks]
+                    const int n = kbase + ((e >> 3) & (BN - 1));
                     if (n < it.key_lo || n >= it.key_hi) *reinterpret_cast<uint4*>(vd + e * 16) = make_uint4(0, 0, 0, 0);
                 }
                 fence_async_smem();                                  // generic stores -> tensor-core reads
@@ -653,17 +681,20 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
             __syncwarp();
             fence_after_sync();
             const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-            tmem_ld64(tmem_o, sv);
-            if (pos >= 0) {
-                const int tok = R / G, head = kvh * G + R % G;
-                __nv_bfloat16* o_row = (__nv_bfloat16*)p.out + (size_t)(it.q0 + tok) * p.out_stride + head * D;
+            const int tok = R / G, head = kvh * G + R % G;
 #pragma unroll
-                for (int c8 = 0; c8 < 8; ++c8) {
-                    __nv_bfloat162 bb[4];
+            for (int c = 0; c < PANELS; ++c) {
+                tmem_ld64(tmem_o + c * 64, sv);                      // every thread of the warp takes part in the load
+                if (pos >= 0) {
+                    __nv_bfloat16* o_row = (__nv_bfloat16*)p.out + (size_t)(it.q0 + tok) * p.out_stride + head * D + c * 64;
 #pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        bb[i] = __floats2bfloat162_rn(sv[c8 * 8 + 2 * i] * inv, sv[c8 * 8 + 2 * i + 1] * inv);
-                    *reinterpret_cast<uint4*>(o_row + c8 * 8) = *reinterpret_cast<uint4*>(bb);
+                    for (int c8 = 0; c8 < 8; ++c8) {
+                        __nv_bfloat162 bb[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            bb[i] = __floats2bfloat162_rn(sv[c8 * 8 + 2 * i] * inv, sv[c8 * 8 + 2 * i + 1] * inv);
+                        *reinterpret_cast<uint4*>(o_row + c8 * 8) = *reinterpret_cast<uint4*>(bb);
+                    }
                 }
             }
         }
@@ -674,9 +705,10 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS));
 }
 
-// The tensor map of one layer of a pool: rows of 64 bfloat16, boxes of min(page size, 64) rows.
+// The tensor map of one layer of a pool: rows of one head (p.d bfloat16), boxes of min(page
+// size, 64) rows by 64 columns.
 inline bool kv_tensor_map(CUtensorMap* out, const AttnParams& p) {
-    return tensor_map_bf16(out, p.kv, (unsigned long long)p.num_pages * 2 * p.nkv * p.ps, D, D, p.ps < BN ? p.ps : BN);
+    return tensor_map_bf16(out, p.kv, (unsigned long long)p.num_pages * 2 * p.nkv * p.ps, p.d, p.d, p.ps < BN ? p.ps : BN);
 }
 
 // Whether this kernel takes the call: a page is a power of two of at least 8 tokens and the
@@ -686,18 +718,30 @@ inline bool takes(const AttnParams& p) {
            ((uintptr_t)p.kv & 15) == 0;
 }
 
-inline int launch(const AttnParams& p, cudaStream_t stream) {
+template <int D, bool WIDE>
+inline int launch_as(const AttnParams& p, cudaStream_t stream) {
     static bool attr_set = false;
+    auto kernel = attn_tc2_kernel<D, WIDE>;
     if (!attr_set) {
-        PL_CUDA(cudaFuncSetAttribute(attn_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        PL_CUDA(cudaFuncSetAttribute(attn_tc2_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+        PL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<D>::SMEM_BYTES));
+        PL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                                      (int)cudaSharedmemCarveoutMaxShared));
         attr_set = true;
     }
     alignas(64) CUtensorMap map;
     if (!kv_tensor_map(&map, p)) return 1;
-    PL_CUDA(launch_pdl(attn_tc2_kernel, dim3(p.n_work * p.nkv), dim3(THREADS), (size_t)SMEM_BYTES, stream, p, map));
+    PL_CUDA(launch_pdl(kernel, dim3(p.n_work * p.nkv), dim3(THREADS), (size_t)Shape<D>::SMEM_BYTES, stream, p, map));
     return 0;
+}
+
+// p.d must be D.
+template <int D>
+inline int launch(const AttnParams& p, cudaStream_t stream) {
+    if constexpr (D == 128) {
+        static const bool narrow = getenv("PAGED_LLM_B200_TC2_NARROW") != nullptr;   // one product per value panel
+        return narrow ? launch_as<D, false>(p, stream) : launch_as<D, true>(p, stream);
+    }
+    return launch_as<D, false>(p, stream);
 }
 
 #ifdef PL_TC2_PROF

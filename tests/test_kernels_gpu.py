@@ -165,8 +165,8 @@ ATTN_LENGTHS = [
 @pytest.mark.parametrize("case", range(len(ATTN_LENGTHS)))
 def test_paged_attention(ops, dtype, ps, nh, nkv, d, case):
     q_lens, k_lens = ATTN_LENGTHS[case]
-    if (ps, case) not in ((8, 0), (16, 1), (16, 2), (32, 3), (8, 4), (16, 3)) and (nh, nkv, d) != (32, 4, 64):
-        pytest.skip("full cross product only for the benchmark head shape")
+    if (ps, case) not in ((8, 0), (16, 1), (16, 2), (32, 3), (8, 4), (16, 3)) and (nh, nkv, d) not in ((32, 4, 64), (32, 8, 128)):
+        pytest.skip("full cross product only for the head shapes of the tcgen05 kernel")
     ops.set_compute_dtype(dtype)
     q, kv, bt, keys, vals = paged_case(q_lens, k_lens, nh, nkv, d, ps, dtype, seed=case)
     ctx = make_ctx(ops, q_lens, k_lens, nh, nkv, None, d)
@@ -230,7 +230,7 @@ def test_decode_attention_as_clusters_and_from_the_work_list(ops, cluster, windo
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("window", [1, 7, 16, 100])
-@pytest.mark.parametrize("nh,nkv,d", [(4, 2, 32), (8, 2, 64)])
+@pytest.mark.parametrize("nh,nkv,d", [(4, 2, 32), (8, 2, 64), (6, 3, 128)])
 def test_paged_attention_window(ops, dtype, window, nh, nkv, d):
     ops.set_compute_dtype(dtype)
     ps = 16
@@ -275,19 +275,20 @@ def test_one_far_key_among_hundreds(ops, dtype):
         torch.testing.assert_close(out, want, atol=2e-2, rtol=2e-2, msg=f"key {target}")
 
 
+@pytest.mark.parametrize("d", [64, 128])
 @pytest.mark.parametrize("nq,L,targets", [
     (200, 1500, (0, 15, 16, 63, 64, 1023, 1024, 1299, 1300, 1498, 1499)),      # a prompt portion: 128-row tiles, TMA page boxes
     (1, 6000, (0, 127, 128, 191, 192, 2999, 5998, 5999)),                      # one long request: the long-context class
 ])
-def test_one_far_key_in_a_portion_and_in_a_long_context(ops, nq, L, targets):
-    """The same for the other two attention paths of bfloat16 at head size 64: the last row of a
-    prompt portion (tcgen05 kernel, keys brought in page by page with TMA) and a single decoding
-    request whose context is long enough for the work-list splits."""
+def test_one_far_key_in_a_portion_and_in_a_long_context(ops, nq, L, targets, d):
+    """The same for the other two attention paths of bfloat16 at head sizes 64 and 128: the last
+    row of a prompt portion (tcgen05 kernel, keys brought in page by page with TMA) and a single
+    decoding request whose context is long enough for the work-list splits."""
     dtype = torch.bfloat16
     ops.set_compute_dtype(dtype)
     if nq == 1 and not ops.cluster_attention:
         pytest.skip("without clusters there is one decode class only")
-    nh, nkv, d, ps = 8, 2, 64, 16
+    nh, nkv, ps = 8, 2, 16
     for target in targets:
         q, kv, bt, keys, vals = paged_case([nq], [L], nh, nkv, d, ps, dtype, seed=target)
         direction = torch.randn(d, generator=torch.Generator().manual_seed(2))
@@ -585,7 +586,7 @@ def test_skinny_add_then_normalising_products(ops, M, N, K, wdtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("d", [32, 64])
+@pytest.mark.parametrize("d", [32, 64, 128])
 def test_window_edge_is_exact(ops, dtype, d):
     """Random scores would hide an off-by-one at the window's edge: put a key with an
     overwhelming score just outside the window (it must change nothing) and one just inside
