@@ -47,6 +47,16 @@ SIZES = {
     "tinyllama-1.1b": dict(vocab_size=32000, hidden_size=2048, intermediate_size=5632, num_hidden_layers=22,
                            num_attention_heads=32, num_key_value_heads=4, head_dim=64, rope_theta=10000.0,
                            rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=2048),
+    # Llama-3.2-1B layer sizes (16 layers, 32 query / 8 kv heads of 64, llama3 rotary scaling, tied head)
+    "llama-3.2-1b": dict(vocab_size=128256, hidden_size=2048, intermediate_size=8192, num_hidden_layers=16,
+                         num_attention_heads=32, num_key_value_heads=8, head_dim=64, rope_theta=500000.0,
+                         rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                           original_max_position_embeddings=8192),
+                         rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=8192),
+    # Llama-3-8B layer sizes (32 layers, 32 query / 8 kv heads of 128, hidden 4096); about 16 GB at full depth
+    "llama-3-8b": dict(vocab_size=128256, hidden_size=4096, intermediate_size=14336, num_hidden_layers=32,
+                       num_attention_heads=32, num_key_value_heads=8, head_dim=128, rope_theta=500000.0,
+                       rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=8192),
     # for trying the script out on small hardware; never the default
     "tiny-a": dict(vocab_size=256, hidden_size=64, intermediate_size=172, num_hidden_layers=2,
                    num_attention_heads=4, num_key_value_heads=2, head_dim=16, max_position_embeddings=4096),
@@ -326,7 +336,10 @@ def run_ours(args) -> dict:
                 "gb_per_s": round(step_bytes / (ms * 1e-3) / 1e9, 1)}
     if args.only == "prefill":
         pre_ms = prefill_once(engine, PREFILL_TOKENS, iters=max(1, args.steps), warmup=args.warmup)
-        return {"only": "prefill", "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3), "layers": cfg.num_hidden_layers}
+        tflops = step_flops(cfg, PREFILL_TOKENS) / (pre_ms * 1e-3) / 1e12
+        return {"only": "prefill", "size": args.size, "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
+                "layers": cfg.num_hidden_layers, "tflops": round(tflops, 1),
+                "frac": round(tflops / peaks["bf16_tflops"], 4), "peaks_source": peaks["source"]}
     weight_bytes = engine.model.weight_bytes_per_step()
     kv_bytes_per_token = engine.kv_cache.page_bytes() // BLOCK_SIZE
 

@@ -1,5 +1,6 @@
 // Paged prefill attention on the 5th-generation tensor cores (tcgen05) with the
-// accumulators in tensor memory, for head size 64 in bfloat16.
+// accumulators in tensor memory, in bfloat16: a block-synchronous kernel for head size 64
+// (namespace tc) and a warp-specialised one for head sizes 64 and 128 (namespace tc2).
 //
 // One thread block takes a tile of 128 query rows of one kv head (row = token * G
 // + head within the group, as in attention_bf16.cuh) and walks its keys 128 at a
@@ -315,7 +316,11 @@ inline int launch(const AttnParams& p, cudaStream_t stream) {
 // Key tiles start at multiples of 64 so that a box never straddles a page; keys outside the
 // block's range are masked by position, and their value rows are zeroed in shared memory (a page
 // may hold anything behind the last token).
-// Needs a page size that is a power of two >= 8; other page sizes run the kernel above.
+// Head size 128 has the same shape with rows of two 64-element panels (the 128-byte swizzle spans
+// one): a TMA box per page and panel, the first product over both panels, the second one 128
+// columns wide (O takes 128 columns of tensor memory), rings of two stages.
+// Needs a page size that is a power of two >= 8; other page sizes run the kernel above (head size
+// 64) or the mma.sync kernel (head size 128).
 namespace tc2 {
 
 using tc::saddr;
