@@ -321,11 +321,12 @@ def run_ours(args) -> dict:
     with tempfile.TemporaryDirectory() as folder:
         cfg, full_layers = make_model(folder, args.size, args.layers)
         prompt_len = args.context if args.only == "decode" and args.context else PROMPT_LEN
-        max_len = max(prompt_len + args.steps + args.warmup + DECODE_LEN, PREFILL_TOKENS) + 64
+        pre_tokens = args.prefill_tokens if args.only == "prefill" and args.prefill_tokens else PREFILL_TOKENS
+        max_len = max(prompt_len + args.steps + args.warmup + DECODE_LEN, pre_tokens) + 64
         seqs = max(args.batch, 64) if prompt_len == PROMPT_LEN else args.batch
         engine = LLMEngine(folder, EngineConfig(
             dtype="bfloat16", block_size=BLOCK_SIZE, max_model_len=max_len, max_num_seqs=max(seqs, 64),
-            max_num_batched_tokens=max(2048, PREFILL_TOKENS), enable_prefix_caching=False,
+            max_num_batched_tokens=max(2048, pre_tokens), enable_prefix_caching=False,
             num_gpu_blocks=seqs * (-(-max_len // BLOCK_SIZE)) + 64))
     B = args.batch
     if args.only == "decode":            # a short run of one part, for profilers and other context lengths
@@ -335,9 +336,9 @@ def run_ours(args) -> dict:
                 "launches_per_step": launches, "layers": cfg.num_hidden_layers,
                 "gb_per_s": round(step_bytes / (ms * 1e-3) / 1e9, 1)}
     if args.only == "prefill":
-        pre_ms = prefill_once(engine, PREFILL_TOKENS, iters=max(1, args.steps), warmup=args.warmup)
-        tflops = step_flops(cfg, PREFILL_TOKENS) / (pre_ms * 1e-3) / 1e12
-        return {"only": "prefill", "size": args.size, "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3),
+        pre_ms = prefill_once(engine, pre_tokens, iters=max(1, args.steps), warmup=args.warmup)
+        tflops = step_flops(cfg, pre_tokens) / (pre_ms * 1e-3) / 1e12
+        return {"only": "prefill", "size": args.size, "tokens": pre_tokens, "ms": round(pre_ms, 3),
                 "layers": cfg.num_hidden_layers, "tflops": round(tflops, 1),
                 "frac": round(tflops / peaks["bf16_tflops"], 4), "peaks_source": peaks["source"]}
     weight_bytes = engine.model.weight_bytes_per_step()
@@ -452,6 +453,8 @@ def main() -> int:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=None, help="with --only decode: prompt length instead of 512")
+    ap.add_argument("--prefill-tokens", type=int, default=None,
+                    help="with --only prefill: length of the prompt (one step) instead of 2,048")
     ap.add_argument("--size", choices=sorted(SIZES), default="tinyllama-1.1b")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the named size (reported in config)")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
