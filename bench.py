@@ -62,6 +62,7 @@ SIZES = {
                    num_attention_heads=4, num_key_value_heads=2, head_dim=16, max_position_embeddings=4096),
 }
 PROMPT_LEN, DECODE_LEN, PREFILL_TOKENS, BLOCK_SIZE = 512, 256, 2048, 16
+RAGGED_PROMPTS, RAGGED_OUTPUTS = (128, 4096), (64, 512)      # the ragged serving workload: lengths drawn uniformly
 
 
 def load_peaks() -> dict:
@@ -289,6 +290,32 @@ def e2e_decode(engine, batch: int, steps: int, warmup: int, prompt_len: int):
     return n_tokens / dt, h2d, batch * 4
 
 
+def ragged_generate(engine, num_requests: int, prompt_range, output_range, seed: int = 0):
+    """Ragged requests through the public `LLMEngine.generate`: prompt and output lengths drawn
+    uniformly, uniform token ids, greedy, prompts cut into portions under the token budget while
+    others decode.  Wall-clock seconds around the call, tokens counted from what comes back."""
+    import random
+    from paged_llm_b200.config import SamplingParams
+
+    rng = random.Random(seed)
+    vocab = engine.model_config.vocab_size
+    prompts, params = [], []
+    for _ in range(num_requests):
+        n = rng.randint(*prompt_range)
+        prompts.append([rng.randrange(vocab) for _ in range(n)])
+        params.append(SamplingParams(temperature=0.0, max_tokens=rng.randint(*output_range), ignore_eos=True))
+    steps0, pre0 = engine.stats.num_steps, engine.stats.num_preemptions
+    t0 = time.perf_counter()
+    outs = engine.generate(prompts, params)
+    dt = time.perf_counter() - t0
+    generated = sum(len(o.token_ids) for o in outs)
+    assert generated == sum(p.max_tokens for p in params), "every request runs to its own length"
+    return {"seconds": round(dt, 3), "requests": num_requests, "prompt_tokens": sum(map(len, prompts)),
+            "generated_tokens": generated, "generated_tok_s": round(generated / dt, 1),
+            "total_tok_s": round((generated + sum(map(len, prompts))) / dt, 1),
+            "steps": engine.stats.num_steps - steps0, "preemptions": engine.stats.num_preemptions - pre0}
+
+
 def prefill_once(engine, tokens: int, iters: int = 5, warmup: int = 3):
     import torch
     from paged_llm_b200.config import SamplingParams
@@ -323,12 +350,19 @@ def run_ours(args) -> dict:
         prompt_len = args.context if args.only == "decode" and args.context else PROMPT_LEN
         pre_tokens = args.prefill_tokens if args.only == "prefill" and args.prefill_tokens else PREFILL_TOKENS
         max_len = max(prompt_len + args.steps + args.warmup + DECODE_LEN, pre_tokens) + 64
+        if args.only == "ragged":
+            max_len = RAGGED_PROMPTS[1] + RAGGED_OUTPUTS[1] + 64
         seqs = max(args.batch, 64) if prompt_len == PROMPT_LEN else args.batch
         engine = LLMEngine(folder, EngineConfig(
             dtype="bfloat16", block_size=BLOCK_SIZE, max_model_len=max_len, max_num_seqs=max(seqs, 64),
             max_num_batched_tokens=max(2048, pre_tokens), enable_prefix_caching=False,
             num_gpu_blocks=seqs * (-(-max_len // BLOCK_SIZE)) + 64))
     B = args.batch
+    if args.only == "ragged":            # 64 ragged requests under a 2,048-token budget, end to end
+        engine.warm_up()
+        ragged_generate(engine, 8, (128, 512), (16, 32), seed=1)          # untimed: first-use costs
+        return {"only": "ragged", "size": args.size, "layers": cfg.num_hidden_layers,
+                **ragged_generate(engine, 64, RAGGED_PROMPTS, RAGGED_OUTPUTS, seed=0)}
     if args.only == "decode":            # a short run of one part, for profilers and other context lengths
         ms, launches, ctx_mid = device_decode_loop(engine, B, args.steps, args.warmup, prompt_len)
         step_bytes = engine.model.weight_bytes_per_step() + B * ctx_mid * (engine.kv_cache.page_bytes() // BLOCK_SIZE)
@@ -457,8 +491,9 @@ def main() -> int:
                     help="with --only prefill: length of the prompt (one step) instead of 2,048")
     ap.add_argument("--size", choices=sorted(SIZES), default="tinyllama-1.1b")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the named size (reported in config)")
-    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
-                    help="run only the decode loop or only the prefill step and print a short line (for profilers)")
+    ap.add_argument("--only", choices=["decode", "prefill", "ragged"], default=None,
+                    help="run only the decode loop, only the prefill step, or the ragged serving workload through "
+                         "LLMEngine.generate, and print a short line")
     args = ap.parse_args()
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
         if int(os.environ.get("RANK", "0")) == 0:
