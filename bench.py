@@ -305,6 +305,7 @@ def ragged_generate(engine, num_requests: int, prompt_range, output_range, seed:
         prompts.append([rng.randrange(vocab) for _ in range(n)])
         params.append(SamplingParams(temperature=0.0, max_tokens=rng.randint(*output_range), ignore_eos=True))
     steps0, pre0 = engine.stats.num_steps, engine.stats.num_preemptions
+    graph0 = engine.runner.num_graph_steps
     t0 = time.perf_counter()
     outs = engine.generate(prompts, params)
     dt = time.perf_counter() - t0
@@ -313,7 +314,8 @@ def ragged_generate(engine, num_requests: int, prompt_range, output_range, seed:
     return {"seconds": round(dt, 3), "requests": num_requests, "prompt_tokens": sum(map(len, prompts)),
             "generated_tokens": generated, "generated_tok_s": round(generated / dt, 1),
             "total_tok_s": round((generated + sum(map(len, prompts))) / dt, 1),
-            "steps": engine.stats.num_steps - steps0, "preemptions": engine.stats.num_preemptions - pre0}
+            "steps": engine.stats.num_steps - steps0,
+            "graph_steps": engine.runner.num_graph_steps - graph0, "preemptions": engine.stats.num_preemptions - pre0}
 
 
 def prefill_once(engine, tokens: int, iters: int = 5, warmup: int = 3):
