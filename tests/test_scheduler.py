@@ -170,3 +170,73 @@ def test_abort():
     assert a.status is SequenceStatus.FINISHED_ABORTED and sched.running == [b]
     sched.abort(b.seq_id)
     assert cm.num_free_blocks == cm.num_blocks
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_arrivals_and_aborts_keep_the_rules(seed):
+    """Requests arrive, are aborted and finish in random order on a pool so small that
+    preemption happens: every step honours the token budget and the request limit, a
+    step's entries are distinct running requests, prompts are never sampled midway, the
+    cache's books balance, and in the end every request finished with its own length and
+    every page is free."""
+    import random
+
+    rng = random.Random(seed)
+    bs = rng.choice([2, 4, 8])
+    budget = rng.choice([8, 16, 24])
+    chunked = seed % 4 != 3
+    max_seqs = rng.choice([2, 3, 5])
+    num_blocks = rng.randrange(12, 28)
+    max_len = 48
+    sched, cm = make(num_blocks=num_blocks, block_size=bs, max_num_batched_tokens=budget, max_model_len=max_len,
+                     max_num_seqs=max_seqs, enable_chunked_prefill=chunked, enable_prefix_caching=seed % 2 == 0)
+    pending = []
+    for i in range(25):
+        n = rng.randrange(1, budget + 1 if not chunked else 30)
+        pending.append(Sequence([rng.randrange(3, 40) for _ in range(n)],
+                                SamplingParams(temperature=0.0, max_tokens=rng.randrange(1, 9), ignore_eos=True)))
+    added, aborted, refused = [], set(), set()
+    steps = 0
+    while pending or sched.has_unfinished:
+        steps += 1
+        assert steps < 5000, "the scheduler makes no progress"
+        while pending and rng.random() < 0.4:
+            s = pending.pop()
+            try:
+                sched.add(s)
+                added.append(s)
+            except ValueError:
+                refused.add(s.seq_id)               # a request the pool or the budget can never hold
+        if added and rng.random() < 0.05:
+            victim = rng.choice(added)
+            if not victim.is_finished:
+                sched.abort(victim.seq_id)
+                aborted.add(victim.seq_id)
+        out = sched.schedule()
+        ids = [x.seq.seq_id for x in out.scheduled]
+        assert len(set(ids)) == len(ids) and out.total_tokens <= budget and len(sched.running) <= max_seqs
+        assert sum(x.num_new_tokens for x in out.scheduled) == out.total_tokens
+        for x in out.scheduled:
+            assert x.seq in sched.running and x.num_new_tokens >= 1
+            reaches_end = x.seq.num_computed_tokens + x.num_new_tokens == x.seq.num_tokens
+            assert x.needs_sampling == reaches_end
+            if not chunked:
+                assert x.num_new_tokens in (1, x.seq.num_tokens - x.seq.num_computed_tokens)
+        for v in out.preempted:                     # back in the queue, or admitted again in this very step
+            assert v.seq_id in ids or (v.status is SequenceStatus.WAITING and v.num_computed_tokens == 0
+                                       and not v.block_table)
+        cm.check_invariants(list(sched.running))
+        sched.update(out, {x.seq.seq_id: rng.randrange(3, 40) for x in out.scheduled if x.needs_sampling})
+        cm.check_invariants(list(sched.running))
+    assert cm.num_free_blocks == cm.num_blocks
+    for s in added:
+        if s.seq_id in aborted:
+            assert s.status is SequenceStatus.FINISHED_ABORTED
+        else:
+            # its own length, cut to what the model length, the pool and (without chunking: a preempted
+            # request comes back as one portion) the token budget can ever hold
+            n = s.num_prompt_tokens
+            want = min(s.sampling_params.max_tokens, max_len - n, cm.max_tokens_per_request() - n + 1)
+            if not chunked:
+                want = min(want, budget - n + 1)
+            assert s.status is SequenceStatus.FINISHED_LENGTH and s.num_generated_tokens == max(1, want), s
