@@ -25,6 +25,8 @@ namespace {
 
 namespace cg = cooperative_groups;
 
+constexpr int kAttnMaxDevices = 64;
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, int src_bytes) {
@@ -337,6 +339,7 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
             __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)(it.q0 + tok) * p.out_stride + head * d + c;
             *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(o0 * inv, o1 * inv);
         } else {
+            if (!attn_partial_fits(p, it.scratch_base + tok)) continue;      // a row outside the declared scratch
             float* part = attn_partial(p, it.scratch_base + tok, head, it.split);
             if (c == 0) {
                 part[0] = M == -INFINITY ? -INFINITY : M * LN2;
@@ -445,11 +448,14 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
 template <int DPAD, int MW, int NW, int KPW>
 int launch_attn_bf16(const AttnParams& p, cudaStream_t stream) {
     using Shape = AttnShape<DPAD, MW, NW, KPW>;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static bool attr_set[kAttnMaxDevices] = {};         // function attributes are per device
+    int dev = 0;
+    PL_CUDA(cudaGetDevice(&dev));
+    PL_REQUIRE(dev >= 0 && dev < kAttnMaxDevices, "attention_bf16: device index %d is out of range", dev);
+    if (!attr_set[dev]) {
         PL_CUDA(cudaFuncSetAttribute(attn_bf16_kernel<DPAD, MW, NW, KPW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      Shape::SMEM_BYTES));
-        attr_set = true;
+        attr_set[dev] = true;
     }
     PL_CUDA(launch_pdl(attn_bf16_kernel<DPAD, MW, NW, KPW>, dim3(p.n_work * p.nkv), dim3(Shape::THREADS),
                        (size_t)Shape::SMEM_BYTES, stream, p));
@@ -464,11 +470,14 @@ int launch_attn_cluster(const AttnParams& p, cudaStream_t stream) {
                                 ? Shape::SMEM_BYTES + Shape::BM * (DPAD + 2) * 4
                                 : Shape::BM * Shape::PITCH * 2 + 4 * Shape::BM * DPAD * 4 + Shape::BM * (DPAD + 2) * 4;
     auto kernel = attn_bf16_kernel<DPAD, 1, 4, KPW, true>;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static bool attr_set[kAttnMaxDevices] = {};
+    int dev = 0;
+    PL_CUDA(cudaGetDevice(&dev));
+    PL_REQUIRE(dev >= 0 && dev < kAttnMaxDevices, "attention_bf16: device index %d is out of range", dev);
+    if (!attr_set[dev]) {
         PL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         PL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));    // up to 16 blocks
-        attr_set = true;
+        attr_set[dev] = true;
     }
     PL_REQUIRE(p.cluster >= 1 && p.cluster <= 16, "attention_bf16: clusters of 1 to 16 blocks, not %d", p.cluster);
     cudaLaunchConfig_t cfg = {};
@@ -500,9 +509,6 @@ PL_EXPORT int pl_attention_tc_timeouts() {
     if (cudaMemcpyFromSymbol(&n, tc::g_timeouts, sizeof(int)) != cudaSuccess) return -1;
     return n;
 }
-#ifdef PL_TC2_PROF
-PL_EXPORT int pl_attention_tc_prof(unsigned long long* out) { return tc2::read_prof(out); }
-#endif
 #endif
 
 #define PL_CAT_(a, b) a##b

@@ -87,3 +87,11 @@ __device__ __forceinline__ AttnItem attn_cluster_item(const AttnParams& p, int s
 __device__ __forceinline__ float* attn_partial(const AttnParams& p, int scratch_row, int head, int split) {
     return p.scratch + (((size_t)scratch_row * p.nh + head) * p.max_splits + split) * (size_t)(p.d + 2);
 }
+
+// Whether all partials of a scratch row lie inside the scratch the caller declared
+// (p.scratch_floats).  A work item that names a row beyond it is skipped, never written.
+__device__ __forceinline__ bool attn_partial_fits(const AttnParams& p, int scratch_row) {
+    return scratch_row >= 0 &&
+           (unsigned long long)(scratch_row + 1) * p.nh * p.max_splits * (unsigned long long)(p.d + 2) <=
+               (unsigned long long)p.scratch_floats;
+}

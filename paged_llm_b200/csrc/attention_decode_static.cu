@@ -34,8 +34,11 @@ __global__ void static_combine_kernel(AttnParams p) {
     const int4 w = p.work[blockIdx.x];
     if (w.x < 0 || w.z != 0 || w.w <= 1) return;
     const int head = blockIdx.y, splits = w.w, d = p.d;
-    const int q0 = p.cu_q[w.x], nq = p.cu_q[w.x + 1] - q0;
+    // The attention kernel takes at most 16 query rows per request and kv head and skips scratch rows
+    // outside the array: the same two limits here, so that no partial is read that was not written.
+    const int q0 = p.cu_q[w.x], nq = min(p.cu_q[w.x + 1] - q0, 16 / (p.nh / p.nkv));
     for (int i = 0; i < nq; ++i) {
+        if (!attn_partial_fits(p, w.y + i)) continue;
         float M = -INFINITY;
         for (int j = 0; j < splits; ++j) M = fmaxf(M, attn_partial(p, w.y + i, head, j)[0]);
         float L = 0.f;
@@ -84,7 +87,7 @@ PL_EXPORT int pl_attention_decode_static(const void* q, int q_stride, const void
     float* scratch = nullptr;
     if (int rc = static_scratch(&scratch)) return rc;
 
-    AttnParams p;
+    AttnParams p = {};
     p.q = q;
     p.kv = kv_layer;
     p.out = out;
@@ -93,7 +96,8 @@ PL_EXPORT int pl_attention_decode_static(const void* q, int q_stride, const void
     p.k_lens = k_lens;
     p.work = reinterpret_cast<const int4*>(work);
     p.scratch = scratch;
-    p.scratch_floats = PL_STATIC_SCRATCH_BYTES / sizeof(float);
+    // what the caller declared, which was checked against the array above; rows beyond it are skipped
+    p.scratch_floats = (long long)(need / sizeof(float));
     p.q_stride = q_stride;
     p.out_stride = out_stride;
     p.bt_stride = bt_stride;

@@ -339,20 +339,6 @@ using tc::tmem_st_wait;
 using tc::ex2;
 using tc::swz;
 
-// Cycle counters of the three roles of block 0, read with pl_attention_tc_prof: compiled in
-// with -DPL_TC2_PROF only (they cost time).
-#ifdef PL_TC2_PROF
-__device__ unsigned long long g_prof[32];
-#define PROF_DECL long long pt_ = clock64(); const bool prof_ = blockIdx.x == 0 && (threadIdx.x & 31) == 0; unsigned long long pacc_[10] = {0,0,0,0,0,0,0,0,0,0};
-#define PROF(i) { long long n_ = clock64(); pacc_[i] += n_ - pt_; pt_ = n_; }
-#define PROF_SET(i, v) pacc_[i] = (v);
-#define PROF_FLUSH(base, n) if (prof_) for (int i_ = 0; i_ < n; ++i_) atomicAdd(&g_prof[base + i_], pacc_[i_]);
-#else
-#define PROF_DECL
-#define PROF(i)
-#define PROF_SET(i, v)
-#define PROF_FLUSH(base, n)
-#endif
 
 constexpr int BM = 128, BN = 64;
 constexpr int SOFTMAX_WARPS = 4, MMA_WARP = 4, K_WARP = 5, V_WARP = 6;
@@ -507,15 +493,12 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
             if (t >= n_tiles || lane >= boxes || n0 >= it.key_hi || n0 + box_rows <= it.key_lo) return -1;
             return bt[n0 >> p.ps_shift];
         };
-        PROF_DECL
         int pg_next = page_of(0);
         for (int t = 0; t < n_tiles; ++t) {
             const int s = t % STAGES;
             const int pg = pg_next;
             pg_next = page_of(t + 1);
-            PROF(0)
             if (t >= STAGES) mbar_wait(&empty[s], ((t / STAGES) - 1) & 1);
-            PROF(1)
             const bool ok = pg >= 0;
             const int n_ok = __popc(__ballot_sync(0xffffffffu, ok));
             if (lane == 0) mbar_arrive_expect(&full[s], n_ok * box_bytes * PANELS);
@@ -527,21 +510,16 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
                 for (int c = 0; c < PANELS; ++c)
                     tma_box(ring + s * K_BYTES + c * K_PANEL + lane * box_bytes, &kv_map, c * 64, row, &full[s]);
             }
-            PROF(2)
         }
-        if (!values) { PROF_FLUSH(16, 3) }
     } else if (warp == MMA_WARP) {
         // ---------------------------------------------------------------- product warp: one thread issues
         if (lane == 0) {
             constexpr uint32_t IDESC_S = instr_desc(BM, BN, false), IDESC_O = instr_desc(BM, WIDE ? D : 64, true);
             const uint32_t qa = saddr(Qs);
-            PROF_DECL
             auto issue_s = [&](int t) {                     // S[t & 1] = Q K(t)^T
                 const int b = t & 1, s = t % STAGES;
                 mbar_wait(&k_full[s], (t / STAGES) & 1);
-                PROF(0)
                 if (t >= 2) mbar_wait(&pv_done[b], ((t - 2) >> 1) & 1);    // P(t-2), which lies over S[b], is consumed
-                PROF(1)
                 fence_after_sync();
                 const uint32_t ka = saddr(Ks + s * K_BYTES);
 #pragma unroll
@@ -550,7 +528,6 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
                             smem_desc(ka + (kk >> 2) * K_PANEL + (kk & 3) * 32, 16, 1024), IDESC_S, kk > 0);
                 mma_commit(&s_full[b]);
                 mma_commit(&k_empty[s]);
-                PROF(2)
             };
             // Scores run ahead of the second product: while the softmax works on S(u + 1), the
             // tensor cores do P(u) V(u) and then S(u + 2) into the columns P(u) leaves.
@@ -560,7 +537,6 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
                 const int bu = u & 1, su = u % STAGES;
                 mbar_wait(&v_full[su], (u / STAGES) & 1);
                 mbar_wait(&p_full[bu], (u >> 1) & 1);
-                PROF(3)
                 fence_after_sync();
                 const uint32_t va = saddr(Vs + su * K_BYTES);
 #pragma unroll
@@ -578,10 +554,8 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
                 }
                 mma_commit(&pv_done[bu]);
                 mma_commit(&v_empty[su]);
-                PROF(4)
                 if (u + 2 < n_tiles) issue_s(u + 2);
             }
-            PROF_FLUSH(10, 5)
         }
         __syncwarp();
     } else {
@@ -594,13 +568,11 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
         const float scale_log2 = p.scale * 1.4426950408889634f;
         float m_run = -INFINITY, l_run = 0.f;
         float sv[64];
-        PROF_DECL
         for (int t = 0; t < n_tiles; ++t) {
             const int b = t & 1;
             mbar_wait(&s_full[b], (t >> 1) & 1);
             __syncwarp();
             fence_after_sync();
-            PROF(0)
             tmem_ld64(tmem_row + b * 64, sv);
             const int kbase = key0 + t * BN;
             const bool row_full = p.window <= 0 && kbase >= it.key_lo && kbase + BN <= it.key_hi && kbase + BN - 1 <= pos;
@@ -623,7 +595,6 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
             const float alpha = !changed ? 1.f : m_run == -INFINITY ? 0.f : ex2(m_run - m_tile);
             if (changed) m_run = m_tile;
             const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
-            PROF(1)
             // P goes back to tensor memory, two bfloat16 per column, over the first half of S[b]
             // (all of S[b] is in registers by now); the second product reads it from there.
             unsigned long long ls2[4] = {0ull, 0ull, 0ull, 0ull};           // four pairs of partial sums
@@ -644,13 +615,11 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
             unpack2(add2(ls2[0], ls2[1]), la, lb);
             unpack2(add2(ls2[2], ls2[3]), lc, ld);
             l_run = l_run * alpha + ((la + lb) + (lc + ld));
-            PROF(3)
             // O is rescaled once the product of the tile before is done
             if (t >= 1 && __any_sync(0xffffffffu, changed)) {
                 mbar_wait(&pv_done[b ^ 1], ((t - 1) >> 1) & 1);
                 __syncwarp();
                 fence_after_sync();
-                PROF(4)
 #pragma unroll
                 for (int c = 0; c < PANELS; ++c) {
                     tmem_ld64(tmem_o + c * 64, sv);
@@ -660,7 +629,6 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
                     tmem_st32(tmem_o + c * 64 + 32, reinterpret_cast<const float(&)[32]>(sv[32]));
                     tmem_st_wait();
                 }
-                PROF(5)
             }
             if (kbase < it.key_lo || kbase + BN > it.key_hi) {
                 // Value rows of keys outside the range are zeroed, so that 0 * anything stays 0 (a
@@ -676,10 +644,7 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
             tmem_st_wait();
             fence_before_sync();
             mbar_arrive(&p_full[b]);
-            PROF(6)
         }
-        PROF_SET(9, n_tiles)
-        if (tid == 0) { PROF_FLUSH(0, 10) }
         if (n_tiles > 0) {
             const int last = n_tiles - 1;
             mbar_wait(&pv_done[last & 1], (last >> 1) & 1);
@@ -749,9 +714,4 @@ inline int launch(const AttnParams& p, cudaStream_t stream) {
     return launch_as<D, false>(p, stream);
 }
 
-#ifdef PL_TC2_PROF
-inline int read_prof(unsigned long long* out) {
-    return cudaMemcpyFromSymbol(out, g_prof, sizeof(g_prof)) == cudaSuccess ? 0 : -1;
-}
-#endif
 }  // namespace tc2

@@ -9,6 +9,7 @@ the model folder has tokenizer files.
 
 from __future__ import annotations
 
+import dataclasses
 import logging
 import os
 import time
@@ -22,7 +23,7 @@ from ..config.engine import EngineConfig
 from ..config.sampling import SamplingParams
 from ..sampling.sampler import Sampler
 from ..weights.loader import load_model, read_hf_config
-from .runner import ModelRunner
+from .runner import ModelRunner, StepItem
 from .scheduler import Scheduler
 from .sequence import Sequence
 
@@ -106,15 +107,16 @@ class LLMEngine:
         log.info("loaded %s in %.1fs (dtype=%s)", model, time.perf_counter() - t0, self.dtype)
 
         slots = self.model.cache_slots()
-        has_state = any(type(s.requirement).__name__ == "FixedState" for s in slots)
-        num_blocks = cfg.num_gpu_blocks or self._size_pool(slots)
+        has_state = self.model.has_fixed_state
+        self.sampler = Sampler(ops, cfg.seed)
+        self.activation_peak_bytes = None      # measured when the pool is sized here (num_gpu_blocks not given)
+        num_blocks = cfg.num_gpu_blocks or self._size_pool(slots, has_state)
         self.kv_cache = CacheStorage(slots, num_blocks, cfg.block_size, self.dtype, self.device,
                                      num_state_slots=cfg.max_num_seqs if has_state else 0)
         self.block_manager = CacheManager(self.kv_cache.group_specs() or num_blocks, cfg.block_size,
                                           cfg.enable_prefix_caching, num_state_slots=self.kv_cache.num_state_slots)
         eos = self.tokenizer.eos_token_id if self.tokenizer is not None else _eos_from_config(hf_config)
         self.scheduler = Scheduler(cfg, self.block_manager, eos)
-        self.sampler = Sampler(ops, cfg.seed)
         self.runner = ModelRunner(self.model, self.kv_cache, self.block_manager, cfg, ops, self.sampler)
         self.stats = EngineStats()
         self._seqs: dict[int, Sequence] = {}
@@ -122,26 +124,56 @@ class LLMEngine:
         self._unreported: list[StepOutput] = []
         self._pinned: list[torch.Tensor] = []
         self._pinned_pos = 0
+        self._steps_since_check = 0
         log.info("KV cache: %d blocks x %d tokens = %d tokens (%.2f GiB)", num_blocks, cfg.block_size,
                  num_blocks * cfg.block_size, num_blocks * self.kv_cache.page_bytes() / 2 ** 30)
 
     # ---- sizing -------------------------------------------------------------------
-    def _size_pool(self, slots) -> int:
-        """Pages that fit in `gpu_memory_utilization` of the device after the
-        weights and a reserve for one step's activations.  The reference measures
-        the activation peak with a dummy forward (engine.py:161-179); here it is
-        computed from the sizes: the widest buffers of a step of
-        `max_num_batched_tokens` tokens."""
+    def _activation_peak(self, slots, has_state: bool) -> int:
+        """Bytes the largest step needs beyond weights and cache: measured, as the reference does
+        (engine.py:161-179), by running one step of `max_num_batched_tokens` tokens of one request
+        that samples at `max_num_seqs` places, on a throw-away pool just large enough for it, and
+        reading the allocator's peak."""
+        cfg = self.config
+        n_tok = min(cfg.max_num_batched_tokens, cfg.max_model_len)
+        pages = -(-n_tok // cfg.block_size) + 1
+        torch.cuda.synchronize(self.device)
+        torch.cuda.empty_cache()
+        base = torch.cuda.memory_allocated(self.device)
+        storage = CacheStorage(slots, pages, cfg.block_size, self.dtype, self.device,
+                               num_state_slots=1 if has_state else 0)
+        manager = CacheManager(storage.group_specs() or pages, cfg.block_size, False,
+                               num_state_slots=storage.num_state_slots)
+        eager = dataclasses.replace(cfg, enforce_eager=True, num_gpu_blocks=pages)
+        runner = ModelRunner(self.model, storage, manager, eager, self.ops)
+        seq = Sequence([0] * n_tok, SamplingParams())
+        manager.acquire_state_slot(seq)
+        if manager.allocate_slots(seq, n_tok) is None:
+            raise RuntimeError("the throw-away pool of the sizing step is too small")
+        held = torch.cuda.memory_allocated(self.device) - base
+        torch.cuda.reset_peak_memory_stats(self.device)
+        rows = min(n_tok, cfg.max_num_seqs)
+        logits = runner.step([StepItem(seq, n_tok, tuple(range(n_tok - rows, n_tok)))])
+        if logits is not None and self.sampler is not None:
+            self.ops.argmax(logits)
+        torch.cuda.synchronize(self.device)
+        peak = torch.cuda.max_memory_allocated(self.device) - base - held
+        del logits, runner, manager, storage
+        torch.cuda.empty_cache()
+        return int(peak)
+
+    def _size_pool(self, slots, has_state: bool = False) -> int:
+        """Pages that fit in `gpu_memory_utilization` of the device beside the weights, what other
+        processes hold, and the measured peak of one largest step (`_activation_peak`)."""
         cfg = self.config
         page_bytes = CacheStorage.page_bytes_for(slots, cfg.block_size, self.dtype)
         if self.device.type != "cuda" or page_bytes == 0:
             return max(64, cfg.max_model_len * 4 // cfg.block_size)
+        peak = self._activation_peak(slots, has_state)
         free, total = torch.cuda.mem_get_info(self.device)
-        used_by_others = total - free - torch.cuda.memory_allocated(self.device)
-        widest = max(getattr(self.model_config, "intermediate_size", 0) * 3, self.model_config.hidden_size * 8)
-        activations = cfg.max_num_batched_tokens * widest * 4 * 2 + cfg.max_num_seqs * self.model_config.vocab_size * 4 * 3
-        budget = int(total * cfg.gpu_memory_utilization) - used_by_others - torch.cuda.memory_allocated(self.device) \
-            - activations
+        ours = torch.cuda.memory_reserved(self.device)
+        used_by_others = total - free - ours
+        budget = int(total * cfg.gpu_memory_utilization) - used_by_others - torch.cuda.memory_allocated(self.device) - peak
         num_blocks = budget // page_bytes
         # no request can use more than max_model_len tokens: more pages than every
         # running request at full length would never be touched
@@ -149,6 +181,7 @@ class LLMEngine:
         if num_blocks < 16:
             raise RuntimeError(f"not enough GPU memory for the KV cache ({num_blocks} blocks); lower "
                                "max_num_batched_tokens or raise gpu_memory_utilization")
+        self.activation_peak_bytes = peak
         return int(num_blocks)
 
     # ---- requests -----------------------------------------------------------------
@@ -200,6 +233,7 @@ class LLMEngine:
                 return outputs
         self._in_flight = self._launch(flight, t0) if self._may_run_ahead(flight) else None
         outputs += self._resolve(flight)
+        self._check_kernels(force=not self.scheduler.has_unfinished and self._in_flight is None)
         self.stats.step_times.append(time.perf_counter() - t0)
         return outputs
 
@@ -253,6 +287,20 @@ class LLMEngine:
         # a page each at most, and none must be taken from a running request
         bm = self.block_manager
         return min(bm.num_free_in_group(g) for g in range(len(bm.pools))) >= len(sch.running)
+
+    HEALTH_CHECK_STEPS = 256      # steps between two looks at the kernels' fault counters
+
+    def _check_kernels(self, force: bool = False) -> None:
+        """Looks at the kernel library's fault counters (bounded waits that gave up) every
+        `HEALTH_CHECK_STEPS` steps, and when the engine runs dry: a fault raises `KernelError`
+        instead of passing for tokens.  Reading them waits for the device, hence not every step."""
+        check = getattr(self.ops, "check_kernels", None)
+        if check is None:
+            return
+        self._steps_since_check += 1
+        if force or self._steps_since_check >= self.HEALTH_CHECK_STEPS:
+            self._steps_since_check = 0
+            check()
 
     def _resolve(self, flight: _InFlight) -> list[StepOutput]:
         """Reads the tokens of a launched step and lets the scheduler take them in."""

@@ -39,7 +39,8 @@ from .sequence import Sequence
 
 class TraceReplayer:
     def __init__(self, model_dir: str, dtype: str, max_tokens: int, device: str = "cuda", ops=None,
-                 block_size: int = 16, enforce_eager: bool = False, poison: float | None = None):
+                 block_size: int = 16, enforce_eager: bool = False, poison: float | None = None,
+                 max_num_seqs: int = 64):
         import torch
 
         self.device = torch.device(device)
@@ -53,13 +54,12 @@ class TraceReplayer:
         max_len = num_pages * block_size
         self.model.prepare(max_len, self.device, ops)
         self.config = EngineConfig(block_size=block_size, num_gpu_blocks=num_pages, max_model_len=max(max_len, 2),
-                                   max_num_batched_tokens=max(max_len, block_size), max_num_seqs=64,
+                                   max_num_batched_tokens=max(max_len, block_size), max_num_seqs=max_num_seqs,
                                    enable_prefix_caching=False, dtype=dtype, device=device,
                                    enforce_eager=enforce_eager)
         slots = self.model.cache_slots()
-        has_state = any(type(s.requirement).__name__ == "FixedState" for s in slots)
         self.storage = CacheStorage(slots, num_pages, block_size, self.dtype, self.device,
-                                    num_state_slots=64 if has_state else 0)
+                                    num_state_slots=max_num_seqs if self.model.has_fixed_state else 0)
         if poison is not None:
             self.storage.fill(poison)
         self.cm = CacheManager(self.storage.group_specs() or num_pages, block_size, enable_prefix_caching=False,
@@ -84,7 +84,8 @@ class TraceReplayer:
                 seq = Sequence(tokens, SamplingParams())
                 self.live[rid] = seq
                 if not self.cm.acquire_state_slot(seq):
-                    raise RuntimeError("no state slot free")
+                    raise RuntimeError(f"no state slot free: more than {self.config.max_num_seqs} live requests "
+                                       "(raise --max-requests)")
             else:
                 seq.token_ids.extend(tokens)
             if self.cm.allocate_slots(seq, len(tokens)) is None:
@@ -103,7 +104,11 @@ class TraceReplayer:
                 self.cm.free(seq)
         if logits is None:
             return None
-        return logits.float().cpu().numpy().astype("<f4", copy=False)
+        out = logits.float().cpu().numpy().astype("<f4", copy=False)
+        check = getattr(self.ops, "check_kernels", None)
+        if check is not None:
+            check()                      # a wait inside a kernel that gave up is an error, not a row of logits
+        return out
 
 
 def main(argv=None) -> int:
@@ -114,11 +119,12 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
     ap.add_argument("--block-size", type=int, default=16)
+    ap.add_argument("--max-requests", type=int, default=64, help="most requests live at a time (state slots)")
     ap.add_argument("--enforce-eager", action="store_true", help="no CUDA-graph replay of decode steps")
     args = ap.parse_args(argv)
     os.makedirs(args.out, exist_ok=True)
     replayer = TraceReplayer(args.model, args.dtype, args.max_tokens, block_size=args.block_size,
-                             enforce_eager=args.enforce_eager)
+                             enforce_eager=args.enforce_eager, max_num_seqs=args.max_requests)
     for line in sys.stdin:
         line = line.strip()
         if not line:

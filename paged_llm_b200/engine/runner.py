@@ -63,6 +63,7 @@ class _Graph:
         self.versions = None
         self.strides = None
         self.plan_tag = None
+        self.plan_shapes = None      # per plan key: (sizes of its three sections, max_splits, long_context) as captured
 
 
 class _Staging:
@@ -110,6 +111,10 @@ class ModelRunner:
         q_lens = [it.num_new_tokens for it in items]
         starts = [it.seq.num_computed_tokens for it in items]
         T = sum(q_lens)
+        limit = self.config.max_model_len         # position tables are prepared for this many positions
+        for it, st, n in zip(items, starts, q_lens):
+            if st + n > limit:
+                raise ValueError(f"request {it.seq.seq_id}: tokens {st}..{st + n} reach past max_model_len={limit}")
         if T == S and all(it.want == (0,) for it in items):
             # every request brings one token and wants its logits: no per-token loops
             for it, st in zip(items, starts):
@@ -292,11 +297,13 @@ class ModelRunner:
             bucket = next(b for b in self.GRAPH_BUCKETS if b >= len(items))
             # few requests with long contexts take other attention kernels than the same batch
             # with short ones: a graph of its own
+            # (and since the plan keys of a model may differ in kv heads, the class is kept per key)
             classify = getattr(self.ops, "long_context_class", None)
             if classify is not None and self.plan_keys:
                 longest = max(it.seq.num_computed_tokens for it in items) + 1
-                if any(not key[2] and classify(bucket, key[1], longest) for key in self.plan_keys):
-                    return ("decode", bucket, "long")
+                classes = tuple(bool(not key[2] and classify(bucket, key[1], longest)) for key in self.plan_keys)
+                if any(classes):
+                    return ("decode", bucket, classes)
             return ("decode", bucket)
         if len(items) == 1:
             n, want = items[0].num_new_tokens, items[0].want
@@ -328,8 +335,10 @@ class ModelRunner:
             pk, host, info = self._gather(items, pad_to=pad, table_stride=self._table_stride())
             if entry is None:
                 entry = self._capture(key, pk, host, info)
-            if pk.size != entry.size:
-                raise RuntimeError("metadata layout changed between capture and replay")
+                entry.plan_shapes = self._plan_shapes(info["plans"])
+            if pk.size != entry.size or self._plan_shapes(info["plans"]) != entry.plan_shapes:
+                raise RuntimeError("metadata layout or attention plan changed between capture and replay of "
+                                   f"graph {key}: the captured kernels would read it wrongly")
             packed = np.zeros(pk.size, np.int32)
             for _, off, data in pk.sections:
                 packed[off:off + data.size] = data
@@ -350,6 +359,13 @@ class ModelRunner:
             return None
         return entry.logits[:len(items)] if key[0] == "decode" else entry.logits
 
+    @staticmethod
+    def _plan_shapes(plans: dict) -> dict:
+        """What a captured graph has baked in of each attention plan: the capacity of its lists,
+        the number of splits its kernels were launched for, and its class."""
+        return {key: (tuple(int(np.asarray(p[name]).size) for name in ("small", "large", "splits")),
+                      int(p["max_splits"]), bool(p.get("long_context", False))) for key, p in plans.items()}
+
     def _patch_decode(self, items: list[StepItem], entry) -> bool:
         """Steady decoding: the same requests as in the last replay of this graph, one token
         further.  Only what moved is rewritten in the packed metadata: token ids, positions,
@@ -359,6 +375,8 @@ class ModelRunner:
             return False
         S = len(items)
         starts = [it.seq.num_computed_tokens for it in items]
+        if max(starts) >= self.config.max_model_len:
+            raise ValueError(f"a request reaches past max_model_len={self.config.max_model_len}")
         try:
             ids = [it.seq.token_ids[st] for it, st in zip(items, starts)]
         except IndexError:
@@ -385,8 +403,14 @@ class ModelRunner:
         if tag is None or tag != entry.plan_tag:
             entry.plan_tag = tag
             ones = [1] * S
-            for key in self.plan_keys:
-                plan = self.ops.plan_attention(ones, klen, *key, pad_requests=entry.bucket, fixed_capacity=True)
+            plans = {key: self.ops.plan_attention(ones, klen, *key, pad_requests=entry.bucket, fixed_capacity=True)
+                     for key in self.plan_keys}
+            if self._plan_shapes(plans) != entry.plan_shapes:
+                # another list capacity, split count or class than the graph was captured with: nothing is
+                # patched (a longer list would run over the next section); the caller gathers anew and checks
+                entry.packed = None
+                return False
+            for key, plan in plans.items():
                 for name in ("small", "large", "splits"):
                     data = plan[name]
                     o = off[f"{name}{key}"]

@@ -20,13 +20,10 @@ import torch
 
 from ..csrc import build
 from . import plan as planning
+from .errors import KernelError
 
 PL_F32, PL_BF16 = 0, 1
 _DTYPE_CODE = {torch.float32: PL_F32, torch.bfloat16: PL_BF16}
-
-
-class KernelError(RuntimeError):
-    pass
 
 
 class LazyNorm:
@@ -62,6 +59,12 @@ def load_module(name: str) -> ctypes.CDLL:
         lib.pl_last_error.restype = ctypes.c_char_p
         _LIBS[name] = lib
     return lib
+
+
+# Every wait inside a kernel (on an mbarrier of a TMA ring or of tcgen05) is bounded; a wait that
+# gives up adds one to a counter of its module, which these exports read.
+_TIMEOUT_EXPORTS = ("pl_gemm_skinny_timeouts", "pl_gemm_tc_timeouts", "pl_gemm_tc_pair_timeouts",
+                    "pl_attention_tc_timeouts")
 
 
 def _check(lib, rc: int) -> None:
@@ -143,6 +146,29 @@ class CudaOps:
             return _DTYPE_CODE[t.dtype]
         except KeyError:
             raise KernelError(f"tensor of dtype {t.dtype} where float32 or bfloat16 is expected") from None
+
+    def kernel_timeouts(self) -> int:
+        """Bounded waits inside kernels that gave up since the process started, over all loaded
+        modules.  Reading the counters waits for the device."""
+        total = 0
+        for lib in list(_LIBS.values()):
+            for name in _TIMEOUT_EXPORTS:
+                try:
+                    fn = getattr(lib, name)
+                except AttributeError:
+                    continue
+                n = int(fn())
+                if n < 0:
+                    raise KernelError(f"{name}: the counter could not be read")
+                total += n
+        return total
+
+    def check_kernels(self) -> None:
+        """Raises if a kernel gave up on a wait: what it computed afterwards is not to be trusted."""
+        n = self.kernel_timeouts()
+        if n:
+            raise KernelError(f"{n} bounded wait(s) inside kernels gave up (a TMA copy or a tensor-core product "
+                              "never signalled its barrier); results since the last check may be wrong")
 
     def copy_h2d(self, dst: torch.Tensor, src: torch.Tensor, nbytes: int) -> None:
         """Asynchronous copy of `nbytes` from pinned host memory to the device on the current stream."""

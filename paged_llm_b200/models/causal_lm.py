@@ -104,6 +104,11 @@ class CausalLM:
         return [CacheSlot(i, self.blocks[e.layer].mixer.cache_requirement(), e.cache_from)
                 for i, e in enumerate(self.schedule)]
 
+    @property
+    def has_fixed_state(self) -> bool:
+        """True if a scheduled run keeps per-request state of fixed size (the engine then holds state slots)."""
+        return any(isinstance(slot.requirement, FixedState) for slot in self.cache_slots())
+
     # ---- forward ---------------------------------------------------------------
     def forward(self, ctx) -> torch.Tensor | None:
         """Runs the tokens of `ctx` and returns float32 logits [wanted, vocab] at

@@ -20,3 +20,13 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_terminal_summary(terminalreporter):
+    from tests import helpers
+    seen = helpers.BF16_VS_F32_SEEN
+    if seen:
+        what, worst = max(seen, key=lambda x: x[1])
+        terminalreporter.write_line(
+            f"bfloat16 against float32 engine: {len(seen)} comparisons, largest difference {worst:.2e} of the largest "
+            f"logit ({what}); tolerance {helpers.BF16_VS_F32_TOL:.1e}")

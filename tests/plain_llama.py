@@ -146,11 +146,13 @@ def decoder_layer(x, w, i, c, cos, sin):
 
 # --------------------------------------------------------------------------- whole model
 
-def forward_logits(cfg: dict, weights: dict, tokens, dtype=torch.float32) -> torch.Tensor:
+def forward_logits(cfg: dict, weights: dict, tokens, dtype=torch.float32, rows=None) -> torch.Tensor:
     """Logits [T, vocab] at every position of one whole sequence (llama.py:196-216).
 
     `weights` holds tensors under HuggingFace names; they are used in `dtype`
-    (float32 or float64) whatever they are stored in.
+    (float32 or float64) whatever they are stored in.  `rows`: the positions whose
+    logits are wanted (the head is then applied to those rows only, which the
+    reference does too: llama.py:214-216); None means all of them.
     """
     c = read_config(cfg)
     w = {k: t.to(dtype) for k, t in weights.items()}
@@ -160,6 +162,8 @@ def forward_logits(cfg: dict, weights: dict, tokens, dtype=torch.float32) -> tor
     cos, sin = rotary_cos_sin(torch.arange(tokens.numel()), inv_freq)
     for i in range(c["layers"]):
         x = decoder_layer(x, w, i, c, cos, sin)
+    if rows is not None:
+        x = x[torch.as_tensor(rows, dtype=torch.long)]
     x = rms_norm(x, w["model.norm.weight"], c["eps"])
     head = w["model.embed_tokens.weight"] if c["tied"] and "lm_head.weight" not in w else w["lm_head.weight"]
     return (x @ head.T).to(torch.float32)

@@ -56,7 +56,8 @@ def portions(requests: dict[str, list[int]], sizes=PORTIONS):
     return steps, max(_round64(len(t)) for t in requests.values())
 
 
-def mixed(requests: dict[str, list[int]], live: int = 4, seed: int = 0, prompt_fraction: float = 0.6):
+def mixed(requests: dict[str, list[int]], live: int = 4, seed: int = 0, prompt_fraction: float = 0.6,
+          choices=(2, 3, 5, 8, 13, 16, 21, 40)):
     """Up to `live` requests at a time: portions of some beside single decoded
     tokens of others in the same step; a request may sit a step out; requests
     start and end mid-trace, and the pool is so small that pages of finished
@@ -76,7 +77,7 @@ def mixed(requests: dict[str, list[int]], live: int = 4, seed: int = 0, prompt_f
                 continue                                  # sits this step out
             left = len(st["toks"]) - st["done"]
             if st["done"] < st["prompt"]:
-                n = int(min(st["prompt"] - st["done"], rng.choice([2, 3, 5, 8, 13, 16, 21, 40])))
+                n = int(min(st["prompt"] - st["done"], rng.choice(list(choices))))
             else:
                 n = 1
             n = min(n, left)
@@ -91,6 +92,33 @@ def mixed(requests: dict[str, list[int]], live: int = 4, seed: int = 0, prompt_f
             del active[rid]
         steps.append({"step": len(steps), "entries": entries, "end": ended})
     return steps, peak
+
+
+def keep_wanted(steps, keep) -> list[dict]:
+    """The same trace with logits asked for only at the positions `keep(request, position)`
+    allows (wide models: a row of logits is large)."""
+    at: dict[str, int] = {}
+    out = []
+    for rec in steps:
+        entries = []
+        for e in rec["entries"]:
+            p0 = at.get(e["id"], 0)
+            entries.append({**e, "want": [w for w in e["want"] if keep(e["id"], p0 + w)]})
+            at[e["id"]] = p0 + len(e["tokens"])
+        out.append({**rec, "entries": entries})
+    return out
+
+
+def wanted_positions(steps) -> dict[str, list[int]]:
+    """Per request, the positions whose logits the trace asks for, in the order `collect` returns them."""
+    at: dict[str, int] = {}
+    pos: dict[str, list[int]] = {}
+    for rec in steps:
+        for e in rec["entries"]:
+            p0 = at.get(e["id"], 0)
+            pos.setdefault(e["id"], []).extend(p0 + w for w in e["want"])
+            at[e["id"]] = p0 + len(e["tokens"])
+    return pos
 
 
 def collect(steps, outputs: dict[int, np.ndarray]) -> dict[str, np.ndarray]:

@@ -257,3 +257,133 @@ def test_learned_positions_refuse_a_position_beyond_the_table(tmp_path):
     rp = TraceReplayer(str(tmp_path), "float32", 64, device="cpu", ops=TorchOps())
     with pytest.raises(ValueError, match="the table has 8 rows"):
         rp.step({"step": 0, "entries": [{"id": "a", "tokens": list(range(9)), "want": []}], "end": []})
+
+
+# ---- what a replayed graph has baked in -----------------------------------------------------
+
+class PlanningOps(TorchOps):
+    """The test double with the B200's planning figures, so that the runner's graph keys and
+    in-place metadata patches can be exercised on the host."""
+
+    num_sms, MAX_SPLITS, MAX_CLUSTER, CLUSTER_KEYS, MIN_SPLIT_KEYS = 148, 32, 8, 600, 128
+
+    def long_context_class(self, num_requests, num_kv_heads, max_context):
+        from paged_llm_b200.kernels.plan import is_long_context
+        return is_long_context(num_requests, num_kv_heads, self.num_sms, self.MAX_SPLITS, self.MAX_CLUSTER,
+                               self.CLUSTER_KEYS, max_context)
+
+    def plan_attention(self, q_lens, k_lens, group_size, num_kv_heads, window, head_dim, pad_requests=None,
+                       fixed_capacity=False):
+        from paged_llm_b200.kernels.plan import plan_attention
+        return plan_attention(q_lens, k_lens, group_size, num_kv_heads, window, small_rows=16, large_rows=64,
+                              min_split_keys=self.MIN_SPLIT_KEYS, num_sms=self.num_sms, max_splits=self.MAX_SPLITS,
+                              pad_requests=pad_requests, fixed_capacity=fixed_capacity,
+                              cluster_max=self.MAX_CLUSTER, long_keys=self.CLUSTER_KEYS)
+
+
+def runner_with_two_plan_keys(folder, max_tokens=8192):
+    rp = TraceReplayer(folder, "float32", max_tokens, device="cpu", ops=PlanningOps(), block_size=16)
+    runner = rp.runner
+    runner.use_graphs = True
+    # two attention shapes in one model: 4 kv heads and 37 kv heads (the second splits less, so the
+    # two change class at different context lengths)
+    runner.plan_keys = [(8, 4, None, 64), (1, 37, None, 64)]
+    return rp, runner
+
+
+def test_graph_key_keeps_the_context_class_of_every_attention_shape(folders):
+    rp, runner = runner_with_two_plan_keys(folders["A"])
+    ops = rp.ops
+
+    def key_at(context):
+        seq = Sequence([1] * (context + 1), SamplingParams())
+        seq.num_computed_tokens = context
+        return runner._graph_key([StepItem(seq, 1, (0,))])
+
+    assert key_at(100) == ("decode", 1)
+    edges = [min(c for c in range(1, 20000, 7) if ops.long_context_class(1, nkv, c + 1)) for nkv in (4, 37)]
+    assert edges[0] != edges[1], "the two shapes must change class at different contexts for this test"
+    lo, hi = sorted(edges)
+    first = (edges[0] == lo, edges[1] == lo)
+    assert key_at(lo + 7) == ("decode", 1, first)
+    assert key_at(hi + 7) == ("decode", 1, (True, True))
+    # every class tuple is a graph of its own, so no graph is replayed with a plan of another class
+    assert len({key_at(c) for c in (100, lo + 7, hi + 7)}) == 3
+
+
+def test_patched_metadata_never_outgrows_the_captured_sections(folders):
+    """A plan whose lists, split count or class differ from what the graph was captured with is
+    not patched into the packed buffer (it would overrun the next section)."""
+    from paged_llm_b200.engine.runner import _Graph
+    rp, runner = runner_with_two_plan_keys(folders["A"], max_tokens=8 * 4096)
+    seqs = []
+    for _ in range(8):
+        seq = Sequence([1] * 4000, SamplingParams())
+        seq.num_computed_tokens = 100
+        seq.block_tables = [list(range(250))]
+        seqs.append(seq)
+    items = [StepItem(seq, 1, (0,)) for seq in seqs]
+    pk, host, info = runner._gather(items, pad_to=8, table_stride=runner._table_stride())
+    entry = _Graph(None, None, None, pk.size, 0, 8)
+    entry.packed = np.zeros(pk.size, np.int32)
+    for _, off, data in pk.sections:
+        entry.packed[off:off + data.size] = data
+    entry.offsets = {name: off for name, off, _ in pk.sections}
+    entry.seq_ids, entry.versions, entry.strides = tuple(s.seq_id for s in seqs), [s.table_version for s in seqs], info["strides"]
+    entry.plan_shapes = runner._plan_shapes(info["plans"])
+    for seq in seqs:
+        seq.num_computed_tokens = 101
+    assert runner._patch_decode(items, entry) and entry.packed[entry.offsets["pos"]] == 101
+    for seq in seqs:
+        seq.num_computed_tokens = 3900                # long-context class for the first shape: other capacity
+    assert not runner._patch_decode(items, entry) and entry.packed is None
+    sizes = {name: data.size for name, _, data in pk.sections}
+    key = runner.plan_keys[0]
+    other = rp.ops.plan_attention([1] * 8, [3901] * 8, *key, pad_requests=8, fixed_capacity=True)
+    assert other["small"].size > sizes[f"small{key}"], "the other class has longer lists: patching would overrun"
+    assert other["max_splits"] != info["plans"][key]["max_splits"]
+
+
+def test_step_refuses_positions_past_the_table(folders):
+    rp = TraceReplayer(folders["A"], "float32", 64, device="cpu", ops=TorchOps(), block_size=16)
+    seq = Sequence([1] * 80, SamplingParams())
+    with pytest.raises(ValueError, match="max_model_len"):
+        rp.runner.step([StepItem(seq, 65, ())])
+
+
+class FaultyOps(TorchOps):
+    """A kernel library one of whose bounded waits has given up."""
+
+    def check_kernels(self):
+        from paged_llm_b200.kernels.errors import KernelError
+        raise KernelError("1 bounded wait(s) inside kernels gave up")
+
+
+def test_a_kernel_fault_is_an_error_not_a_token(folders):
+    from paged_llm_b200.kernels.errors import KernelError
+    eng = LLMEngine(folders["A"], ops=FaultyOps(), dtype="float32", device="cpu", block_size=8, num_gpu_blocks=64,
+                    max_model_len=128)
+    with pytest.raises(KernelError, match="gave up"):
+        eng.generate([random_tokens(256, 5, 1)], SamplingParams(temperature=0.0, max_tokens=3))
+    rp = TraceReplayer(folders["A"], "float32", 64, device="cpu", ops=FaultyOps(), block_size=16)
+    with pytest.raises(KernelError, match="gave up"):
+        rp.step({"step": 0, "entries": [{"id": "a", "tokens": [1, 2, 3], "want": [2]}], "end": []})
+
+
+def test_tiny_b_workload_preempts_and_hits_the_prefix_cache(folders):
+    """The workload of tests/test_generate_gpu.py::tiny_b_workload on the host: its requests are
+    preempted, one of them finds the shared prefix in the cache, and every token is the plain draw."""
+    from tests.plain_sampling import gumbel_scores
+    from tests.test_generate_gpu import tiny_b_workload
+    prompts, sps = tiny_b_workload()
+    eng = engine(folders["B"], num_gpu_blocks=24, max_model_len=256, max_num_batched_tokens=32)
+    outs = eng.generate(prompts, sps)
+    assert eng.stats.num_preemptions > 0 and eng.block_manager.num_cache_hits > 0
+    assert max(o.num_cached_tokens for o in outs) >= 16 and eng.block_manager.num_free_blocks == 24
+    cfg, w = read_folder(folders["B"])
+    for p, sp, o in zip(prompts, sps, outs):
+        seq = list(p)
+        for tok in o.token_ids:
+            scores = gumbel_scores(plain_llama.forward_logits(cfg, w, seq)[-1].numpy(), 0.7, -1, 1.0, sp.seed, len(seq))
+            assert scores.max() - scores[tok] < 1e-3
+            seq.append(tok)

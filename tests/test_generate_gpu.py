@@ -109,7 +109,7 @@ def test_decoding_across_the_context_classes(folders):
     eng.ops.CLUSTER_KEYS = 5                      # 5 keys x 8 blocks: contexts above 40 tokens are "long"
     outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=40))
     keys = set(eng.runner._graphs)
-    assert ("decode", 2) in keys and ("decode", 2, "long") in keys, keys
+    assert ("decode", 2) in keys and ("decode", 2, (True,)) in keys, keys
     for p, o in zip(prompts, outs):
         seq = list(p)
         for tok in o.token_ids:
@@ -162,6 +162,120 @@ def test_temperature_sampling_follows_the_plain_draw(folders):
             seq.append(tok)
     again = LLMEngine(folders["B"], dtype="float32", block_size=8, num_gpu_blocks=24, max_model_len=256).generate(prompts, sps)
     assert [o.token_ids for o in again] == [o.token_ids for o in outs]
+
+
+def tiny_b_workload():
+    """The second tiny configuration's workload: prompts of 1, 9, 40, 64 and 100 tokens, the
+    100-token one opening with the first 16 tokens (two pages of 8) of the 40-token one,
+    temperature 0.7 with seed 3, 12 tokens each, on 24 pages of 8 tokens."""
+    from paged_llm_b200 import SamplingParams
+    hf, _ = TINIES["B"]
+    prompts = [random_tokens(hf["vocab_size"], n, 60 + n) for n in (1, 9, 40, 64, 100)]
+    prompts[4][:16] = prompts[2][:16]
+    sps = [SamplingParams(temperature=0.7, max_tokens=12, seed=3, ignore_eos=True) for _ in prompts]
+    return prompts, sps
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_tiny_b_workload_with_preemption_and_a_shared_prefix(tmp_path_factory, dtype):
+    """Sampled generation under preemption by recompute with a prefix hit, in both precisions:
+    every token is what the plain sampler draws from the plain logits of the same prefix.  The
+    folder holds bfloat16 values, so both precisions and the plain model use the same weights."""
+    from paged_llm_b200 import LLMEngine
+    from tests.helpers import BF16_VS_F32_TOL
+    from tests.plain_sampling import gumbel_scores
+    folder = model_folder(tmp_path_factory, "B", dtype="bfloat16")
+    prompts, sps = tiny_b_workload()
+    eng = LLMEngine(folder, dtype=dtype, block_size=8, num_gpu_blocks=24, max_model_len=256, max_num_batched_tokens=32)
+    outs = eng.generate(prompts, sps)
+    assert eng.stats.num_preemptions > 0, "24 pages of 8 tokens cannot hold all five requests"
+    assert eng.block_manager.num_cache_hits > 0 and max(o.num_cached_tokens for o in outs) >= 16
+    assert eng.block_manager.num_free_blocks == 24
+    for p, sp, o in zip(prompts, sps, outs):
+        assert len(o.token_ids) == 12
+        seq = list(p)
+        for tok in o.token_ids:
+            row = plain_logits(folder, seq)[-1]
+            scores = gumbel_scores(row, 0.7, -1, 1.0, sp.seed, len(seq))
+            slack = 1e-3 if dtype == "float32" else 2 * BF16_VS_F32_TOL * float(np.abs(row).max()) / 0.7
+            assert scores.max() - scores[tok] <= slack, (dtype, len(p), len(seq))
+            seq.append(tok)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_fork_copies_the_shared_page_on_the_device(folders, dtype):
+    """fork -> both children write into the shared, partly filled page -> copy-on-write -> both
+    decode: the copied page is read through the attention kernels (reference:
+    pagedllm/block_manager.py:195-231)."""
+    from paged_llm_b200 import LLMEngine, SamplingParams
+    from paged_llm_b200.engine.sequence import Sequence
+    eng = LLMEngine(folders["A"], dtype=dtype, block_size=8, num_gpu_blocks=32, max_model_len=128,
+                    enable_prefix_caching=False)
+    eng.kv_cache.fill(float("nan"))
+    sched, cm, runner = eng.scheduler, eng.block_manager, eng.runner
+    base = random_tokens(256, 11, 3)                        # one full page and 3 slots of the next
+    root = Sequence(base, SamplingParams(temperature=0.0, max_tokens=100))
+    sched.add(root)
+    out = sched.schedule()
+    sched.update(out, runner.run(out))
+    children = []
+    for tok in (50, 60):
+        child = Sequence(base, SamplingParams(temperature=0.0, max_tokens=4))
+        cm.fork(root, child)
+        child.token_ids = base + [tok]
+        child.status = root.status
+        sched.running.append(child)
+        children.append(child)
+    sched.abort(root.seq_id)
+    assert cm.blocks[children[0].block_table[1]].ref_count == 2
+    copies, take = [], cm.take_pending_copies
+
+    def counted():
+        got = take()
+        copies.extend(got)
+        return got
+    cm.take_pending_copies = counted
+    while sched.has_unfinished:
+        out = sched.schedule()
+        sched.update(out, runner.run(out))
+    assert len(copies) == 1, "the first child to write gets a copy of the shared page, the second keeps the page"
+    for child, tok in zip(children, (50, 60)):
+        seq = base + [tok]
+        for got in child.output_token_ids[1:]:
+            ref = plain_logits(folders["A"], seq)[-1]
+            assert ref.max() - ref[got] <= (1e-4 if dtype == "float32" else 3e-2 * np.abs(ref).max())
+            seq.append(got)
+        assert len(child.output_token_ids) == 4
+    assert cm.num_free_blocks == 32
+
+
+def test_pool_sized_from_measured_memory(folders):
+    """`num_gpu_blocks=None`: the pool is sized from the device's free memory and the measured
+    peak of one largest step (reference: pagedllm/engine.py:161-179)."""
+    import torch
+    from paged_llm_b200 import LLMEngine, SamplingParams
+    hf, _ = TINIES["A"]
+    free0, total = torch.cuda.mem_get_info()
+    eng = LLMEngine(folders["A"], dtype="bfloat16", block_size=16, max_model_len=128, max_num_seqs=8,
+                    max_num_batched_tokens=256, gpu_memory_utilization=0.5)
+    blocks = eng.block_manager.num_blocks
+    # capped by what eight requests of full length can use; far below half of the device
+    assert blocks == 8 * (128 // 16) + 16
+    assert eng.activation_peak_bytes is not None and eng.activation_peak_bytes > 256 * hf["hidden_size"] * 4
+    free1, _ = torch.cuda.mem_get_info()
+    assert total - free1 <= 0.5 * total + (total - free0)
+    prompt = random_tokens(hf["vocab_size"], 9, 3)
+    out = eng.generate([prompt], SamplingParams(temperature=0.0, max_tokens=6))[0]
+    seq = list(prompt)
+    for tok in out.token_ids:
+        ref = plain_logits(folders["A"], seq)[-1]
+        assert ref.max() - ref[tok] <= 3e-2 * np.abs(ref).max()
+        seq.append(tok)
+    # without the cap of the request limit the pool takes what the budget allows
+    big = LLMEngine(folders["A"], dtype="bfloat16", block_size=16, max_model_len=4096, max_num_seqs=256,
+                    max_num_batched_tokens=256, gpu_memory_utilization=0.02 + (total - free1) / total)
+    page_bytes = big.kv_cache.page_bytes()
+    assert 16 <= big.block_manager.num_blocks * page_bytes <= 0.025 * total
 
 
 def test_prefix_hit_and_stats(folders):

@@ -6,7 +6,8 @@ arena, code inside somebody else's capture, a plug-in that must stay out of the
 allocator) get the split-context decode attention with its scratch inside the
 library.  This test drives it with ctypes exactly as such a caller would, twice
 in a row with different inputs (the built-in scratch keeps the first call's
-contents), and holds the results to the regular entry point's.
+contents), on a stream of its own, and holds the results to the regular entry
+point's and to the plain float32 attention of tests/plain_llama.py.
 
 It is collected last so that a run that stops at the first failure has already
 run every other test; it needs nothing from them and also passes alone.
@@ -36,8 +37,23 @@ def _call(lib, qkv, kv, out, bt, ctx, plan, nh, nkv, d, window, scale):
         int(window or 0), ctypes.c_float(scale), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
 
 
-@pytest.mark.parametrize("nh,nkv,d,ps", [(32, 4, 64, 16), (6, 2, 48, 8), (8, 8, 128, 32)])
-def test_static_scratch_entry_point_matches_the_regular_one(nh, nkv, d, ps):
+def _plain_attention(q, keys, vals, q_lens, k_lens, nh, nkv, d, window):
+    """The same attention by the plain float32 formulation on the CPU (tests/plain_llama.py),
+    request by request: the new tokens are the last rows of the request's whole sequence."""
+    from tests import plain_llama
+    rows, o = [], 0
+    for s, (nq, lk) in enumerate(zip(q_lens, k_lens)):
+        full_q = torch.zeros(lk, nh, d)
+        full_q[lk - nq:] = q[o:o + nq].float()
+        out = plain_llama.causal_attention(full_q, keys[s], vals[s], d ** -0.5, window)
+        rows.append(out[lk - nq:].reshape(nq, nh * d))
+        o += nq
+    return torch.cat(rows)
+
+
+@pytest.mark.parametrize("nh,nkv,d,ps,window", [(32, 4, 64, 16, None), (6, 2, 48, 8, None), (8, 8, 128, 32, None),
+                                                (32, 4, 64, 16, 50)])
+def test_static_scratch_entry_point_matches_the_regular_one(nh, nkv, d, ps, window):
     from paged_llm_b200.kernels.ops import CudaOps
     from tests.test_kernels_gpu import make_ctx, paged_case
 
@@ -45,25 +61,61 @@ def test_static_scratch_entry_point_matches_the_regular_one(nh, nkv, d, ps):
     ops.set_compute_dtype(torch.bfloat16)
     lib = _load()
     assert lib.pl_attention_decode_static_capacity() == 8 << 20
+    side = torch.cuda.Stream()                       # a caller's own stream, not the default one
     cases = [([1, 1, 1], [700, 33, 1500]), ([1, 2, 1, 1], [90, 400, 2048, 5])]
     for call, (q_lens, k_lens) in enumerate(cases):                     # two calls in a row
         if nh // nkv * max(q_lens) > 16:
             q_lens = [1] * len(q_lens)
-        q, kv, bt, _, _ = paged_case(q_lens, k_lens, nh, nkv, d, ps, torch.bfloat16, seed=40 + call)
-        ctx = make_ctx(ops, q_lens, k_lens, nh, nkv, None, d)
-        plan = ctx.attention_plans[(nh // nkv, nkv, None, d)]
-        assert plan.n_small and not plan.n_large and plan.max_splits > 1
+        q, kv, bt, keys, vals = paged_case(q_lens, k_lens, nh, nkv, d, ps, torch.bfloat16, seed=40 + call)
+        ctx = make_ctx(ops, q_lens, k_lens, nh, nkv, window, d)
+        plan = ctx.attention_plans[(nh // nkv, nkv, window, d)]
+        assert plan.n_small and not plan.n_large and (plan.max_splits > 1 or window)
         qkv = torch.cat([q.reshape(-1, nh * d), torch.zeros(q.shape[0], 2 * nkv * d, dtype=torch.bfloat16)], 1).cuda().contiguous()
         kv, bt = kv.cuda(), bt.cuda()
-        want = ops.paged_attention(qkv, nh, nkv, d, kv, bt, ctx, d ** -0.5, None)
+        want = ops.paged_attention(qkv, nh, nkv, d, kv, bt, ctx, d ** -0.5, window)
         out = torch.full_like(want, float("nan"))
         torch.cuda.synchronize()
-        before = torch.cuda.memory_allocated()
-        rc = _call(lib, qkv, kv, out, bt, ctx, plan, nh, nkv, d, None, d ** -0.5)
+        # the driver's own count of free device memory: an allocation by any route would move it
+        free_before, _ = torch.cuda.mem_get_info()
+        with torch.cuda.stream(side):
+            rc = _call(lib, qkv, kv, out, bt, ctx, plan, nh, nkv, d, window, d ** -0.5)
         torch.cuda.synchronize()
         assert rc == 0, lib.pl_last_error().decode()
-        assert torch.cuda.memory_allocated() == before
+        if call > 0:                                 # the first call on a device sets the entry point up
+            assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the device's free memory"
         torch.testing.assert_close(out.float(), want.float(), atol=1.6e-2, rtol=1.6e-2, msg=f"call {call}")
+        plain = _plain_attention(q, keys, vals, q_lens, k_lens, nh, nkv, d, window)
+        torch.testing.assert_close(out.float().cpu(), plain, atol=1.6e-2, rtol=1.6e-2, msg=f"call {call} against plain")
+
+
+def test_static_scratch_entry_point_takes_the_last_row_that_fits():
+    """A work list whose request sits on the last scratch row the caller declared, with as many
+    rows declared as the array holds for this shape: partials go to the very end of the array."""
+    from paged_llm_b200.kernels.ops import CudaOps
+    from tests.test_kernels_gpu import make_ctx, paged_case
+
+    nh, nkv, d, ps = 32, 4, 64, 16
+    ops = CudaOps("cuda")
+    ops.set_compute_dtype(torch.bfloat16)
+    lib = _load()
+    q_lens, k_lens = [1, 1], [900, 300]
+    q, kv, bt, keys, vals = paged_case(q_lens, k_lens, nh, nkv, d, ps, torch.bfloat16, seed=7)
+    ctx = make_ctx(ops, q_lens, k_lens, nh, nkv, None, d)
+    plan = ctx.attention_plans[(nh // nkv, nkv, None, d)]
+    assert plan.max_splits > 1
+    rows = (8 << 20) // (4 * nh * plan.max_splits * (d + 2))            # scratch rows that fit the array
+    work = plan.small.cpu().clone()
+    work[work[:, 0] == 1, 1] = rows - 1                                  # request 1 on the last row
+    plan.small = work.cuda()
+    plan.small_tokens = rows
+    qkv = torch.cat([q.reshape(-1, nh * d), torch.zeros(q.shape[0], 2 * nkv * d, dtype=torch.bfloat16)], 1).cuda().contiguous()
+    kv, bt = kv.cuda(), bt.cuda()
+    out = torch.full((2, nh * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    rc = _call(lib, qkv, kv, out, bt, ctx, plan, nh, nkv, d, None, d ** -0.5)
+    torch.cuda.synchronize()
+    assert rc == 0, lib.pl_last_error().decode()
+    plain = _plain_attention(q, keys, vals, q_lens, k_lens, nh, nkv, d, None)
+    torch.testing.assert_close(out.float().cpu(), plain, atol=1.6e-2, rtol=1.6e-2)
 
 
 def test_static_scratch_entry_point_rejects_what_does_not_fit():
