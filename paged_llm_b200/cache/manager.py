@@ -126,6 +126,7 @@ class CacheManager:
         self.enable_prefix_caching = bool(enable_prefix_caching and all_keys and num_state_slots == 0)
         self.pools = [PagePool(g.num_pages, self.enable_prefix_caching) for g in groups]
         self._pending_copies: list[PageCopy] = []
+        self._pending_state_copies: list[tuple[int, int]] = []
         self._free_state_slots = list(range(num_state_slots - 1, -1, -1))
         self.num_state_slots = num_state_slots
         self.num_cache_queries = 0
@@ -346,10 +347,14 @@ class CacheManager:
         self.release_state_slot(seq)
 
     def fork(self, parent: Sequence, child: Sequence) -> None:
-        """`child` shares every page of `parent` (block_manager.py:225-231)."""
-        if self.num_state_slots:
-            raise NotImplementedError("fork needs a copy of the per-request state, which is not implemented")
+        """`child` shares every page of `parent` (block_manager.py:225-231).  State of fixed
+        size cannot be shared (a step overwrites it): the child gets a slot of its own and a copy
+        of the parent's state is queued for the next step (`take_pending_state_copies`)."""
         assert not any(self._tables(child)), "child already owns pages"
+        if self.num_state_slots and parent.state_slot is not None:
+            if not self.acquire_state_slot(child):
+                raise RuntimeError("fork: no state slot is free for the child")
+            self._pending_state_copies.append((parent.state_slot, child.state_slot))
         for g, table in enumerate(self._tables(parent)):
             for b in table:
                 if b != NO_PAGE:
@@ -361,6 +366,11 @@ class CacheManager:
 
     def take_pending_copies(self) -> list[PageCopy]:
         ops, self._pending_copies = self._pending_copies, []
+        return ops
+
+    def take_pending_state_copies(self) -> list[tuple[int, int]]:
+        """(source slot, destination slot) pairs that forks have queued, in order."""
+        ops, self._pending_state_copies = self._pending_state_copies, []
         return ops
 
     def slot_mapping(self, seq: Sequence, start_token: int, num_tokens: int, group: int = 0) -> list[int]:

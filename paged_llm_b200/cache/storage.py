@@ -107,7 +107,25 @@ class CacheStorage:
             if pairs:
                 ops.copy_pages(self.pools[g], pairs)
 
-    def zero_state(self, slot: int) -> None:
-        for lc in self.layer_caches:
-            if lc is not None and lc.kind == "fixed_state" and lc.owner:
-                lc.state[slot].zero_()
+    def _state_tensors(self):
+        return [lc.state for lc in self.layer_caches if lc is not None and lc.kind == "fixed_state" and lc.owner]
+
+    def zero_state(self, slots) -> None:
+        """Zero the state of the given slots (an int or a list of them) in every stateful run:
+        one indexed fill per state tensor, whatever the number of slots."""
+        slots = [slots] if isinstance(slots, int) else list(slots)
+        if not slots:
+            return
+        states = self._state_tensors()
+        if not states:
+            return
+        idx = torch.tensor(slots, dtype=torch.long).to(self.device, non_blocking=True)
+        for state in states:
+            state.index_fill_(0, idx, 0)
+
+    def copy_state(self, pairs) -> None:
+        """state[dst] = state[src] for each (src, dst), in order (a forked request starts from
+        its parent's state)."""
+        for src, dst in pairs:
+            for state in self._state_tensors():
+                state[dst].copy_(state[src])

@@ -137,10 +137,13 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
 
     const int g = lane >> 2, t4 = lane & 3;
     int pos[2];
+    float slope[2];
+    const bool modified = p.softcap > 0.f || p.slopes != nullptr;     // score modifiers (off for the Llama decoder)
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int R = it.row_base + wm * 16 + g + 8 * h;
         pos[h] = R < it.rows_total ? it.lk - it.nq + R / G : -1;
+        slope[h] = p.slopes != nullptr && R < it.rows_total ? p.slopes[kvh * G + R % G] : 0.f;
     }
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     float oacc[DPAD / 8][4];
@@ -215,7 +218,7 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
             // scale, mask, running maximum.  A tile whose keys all lie at or before the first
             // row's position (and inside the window and the range) needs no mask.
             const int pos_min_warp = __reduce_min_sync(0xffffffffu, min(pos[0], pos[1]));    // -1 if a row is padding
-            const bool full_tile = p.window <= 0 && kbase + KPW <= it.key_hi && kbase + KPW - 1 <= pos_min_warp;
+            const bool full_tile = !modified && p.window <= 0 && kbase + KPW <= it.key_hi && kbase + KPW - 1 <= pos_min_warp;
             float mx[2] = {-INFINITY, -INFINITY};
             if (full_tile) {
 #pragma unroll
@@ -234,7 +237,9 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
                         const int n = kbase + 8 * j + 2 * t4 + (e & 1);
                         const int pr = pos[e >> 1];
                         const bool vis = n < it.key_hi && n <= pr && (p.window <= 0 || n > pr - p.window);
-                        const float s = vis ? sacc[j][e] * scale_log2 : -INFINITY;
+                        const float s = !vis ? -INFINITY
+                                        : modified ? attn_score(p, sacc[j][e], slope[e >> 1], n, pr) * LOG2E
+                                                   : sacc[j][e] * scale_log2;
                         sacc[j][e] = s;
                         mx[e >> 1] = fmaxf(mx[e >> 1], s);
                     }
@@ -526,12 +531,15 @@ PL_EXPORT int PL_CAT(pl_attention_bf16_d, PL_DPAD)(const AttnParams* params, cud
                p.d, PL_DPAD);
     PL_REQUIRE(p.q_stride % 8 == 0 && p.out_stride % 2 == 0, "attention_bf16: row strides must keep 16-byte alignment");
     PL_REQUIRE(((uintptr_t)p.q & 15) == 0 && ((uintptr_t)p.kv & 15) == 0, "attention_bf16: q and kv must be 16-byte aligned");
+    PL_REQUIRE(p.softcap >= 0.f, "attention_bf16: softcap=%f must not be negative", (double)p.softcap);
     constexpr int KPW_SMALL = PL_DPAD <= 128 ? 32 : 16;
     if (p.cluster > 0) return launch_attn_cluster<PL_DPAD, KPW_SMALL>(p, stream);
     if (p.is_small) return launch_attn_bf16<PL_DPAD, 1, 4, KPW_SMALL>(p, stream);
 #if PL_DPAD == 64 || PL_DPAD == 128
     // prefill tiles of head sizes 64 and 128 run on tcgen05 with tensor-memory accumulators
-    static const bool no_tc = getenv("PAGED_LLM_B200_NO_TCGEN05") != nullptr;
+    // (the score modifiers live in the mma.sync kernel only; the tcgen05 kernels step aside for them)
+    static const bool no_tc_env = getenv("PAGED_LLM_B200_NO_TCGEN05") != nullptr;
+    const bool no_tc = no_tc_env || p.softcap > 0.f || p.slopes != nullptr;
 #if PL_DPAD == 64
     static const bool serial_tc = getenv("PAGED_LLM_B200_TC_SERIAL") != nullptr;     // the block-synchronous variant
     if (p.d == 64 && !no_tc) return serial_tc || !tc2::takes(p) ? tc::launch(p, stream) : tc2::launch<64>(p, stream);

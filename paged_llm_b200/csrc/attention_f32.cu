@@ -30,11 +30,12 @@ __global__ void __launch_bounds__(128) attn_f32_kernel(AttnParams p) {
         Qs[e] = v;
     }
     int pos[4];
-    float m[4], l[4], acc[4][F32_MAXD / 32];
+    float m[4], l[4], acc[4][F32_MAXD / 32], slope[4];
 #pragma unroll
     for (int rr = 0; rr < 4; ++rr) {
         const int R = it.row_base + warp * 4 + rr;
         pos[rr] = R < it.rows_total ? it.lk - it.nq + R / G : -1;
+        slope[rr] = p.slopes != nullptr && R < it.rows_total ? p.slopes[kvh * G + R % G] : 0.f;
         m[rr] = -INFINITY;
         l[rr] = 0.f;
 #pragma unroll
@@ -68,7 +69,7 @@ __global__ void __launch_bounds__(128) attn_f32_kernel(AttnParams p) {
             const float* kr = Ks + lane * (d + 1);
             float s = 0.f;
             for (int c = 0; c < d; ++c) s = fmaf(qr[c], kr[c], s);
-            s *= p.scale;
+            s = attn_score(p, s, slope[rr], n, pos[rr]);
             const bool vis = n < it.key_hi && n <= pos[rr] && (p.window <= 0 || n > pos[rr] - p.window);
             const float m_new = fmaxf(m[rr], warp_max(vis ? s : -INFINITY));
             if (m_new == -INFINITY) continue;
@@ -157,6 +158,7 @@ int pl_attn_check(const AttnParams& p, const char* who) {
     PL_REQUIRE(p.ps > 0, "%s: page_size=%d", who, p.ps);
     PL_REQUIRE(p.window >= 0, "%s: window=%d", who, p.window);
     PL_REQUIRE(p.max_splits >= 1, "%s: max_splits=%d", who, p.max_splits);
+    PL_REQUIRE(p.softcap >= 0.f, "%s: softcap=%f must not be negative", who, (double)p.softcap);
     return 0;
 }
 

@@ -116,4 +116,15 @@ struct AttnParams {
     int num_pages;          // pages in `kv` (0: unknown; kernels that need it step aside)
     int cluster;            // > 0: no work list; n_work requests of at most 16 rows each, every (request, kv head)
                             // is a thread-block cluster of this many blocks that split the keys between them
+    // Score modifiers, both off by default (the Llama decoder uses neither).  With s = scale * q.k:
+    float softcap;          // > 0: s = softcap * tanh(s / softcap)
+    const float* slopes;    // [nh] or null: s += slopes[head] * (key position - query position), a bias that grows
+                            // with the distance to the key; applied after the cap
 };
+
+// The score of one (query row, key) pair from the raw dot product, in natural-log units.
+__device__ __forceinline__ float attn_score(const AttnParams& p, float dot, float slope, int key_pos, int query_pos) {
+    float s = dot * p.scale;
+    if (p.softcap > 0.f) s = p.softcap * tanhf(s / p.softcap);
+    return s + slope * (float)(key_pos - query_pos);
+}

@@ -275,8 +275,7 @@ class LLMEngine:
         if not cfg.overlap_decode or flight.ids is None or sch.waiting:
             return False
         out = flight.out
-        if out.num_prefill_tokens or out.preempted or len(out.scheduled) != len(sch.running) \
-                or self.block_manager.num_state_slots:
+        if out.num_prefill_tokens or out.preempted or len(out.scheduled) != len(sch.running):
             return False
         for item, seq in zip(out.scheduled, sch.running):
             if item.seq is not seq or not item.needs_sampling or seq.num_unresolved != 1:

@@ -14,6 +14,7 @@ replayed from CUDA graphs, one per batch-size bucket, unless `enforce_eager`.
 
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass
 
 import numpy as np
@@ -266,9 +267,12 @@ class ModelRunner:
         if not items:
             return None
         self.storage.apply_copies(self.cm.take_pending_copies(), self.ops)
-        for it in items:
-            if it.seq.state_slot is not None and it.seq.num_computed_tokens == 0:
-                self.storage.zero_state(it.seq.state_slot)
+        if self.cm.num_state_slots:
+            # state of fixed size: a request that starts (again) begins from zeros, a forked one from its
+            # parent's state; both happen on the stream in front of the step, outside any captured graph
+            self.storage.zero_state([it.seq.state_slot for it in items
+                                     if it.seq.state_slot is not None and it.seq.num_computed_tokens == 0])
+            self.storage.copy_state(self.cm.take_pending_state_copies())
         override, self.next_ids_override = self.next_ids_override, None
         key = self._graph_key(items)
         if key is not None:
@@ -289,7 +293,7 @@ class ModelRunner:
         one request replays a graph per portion length, captured when that length is the token
         budget or comes a second time (a prompt cut by the budget brings the same length again
         and again)."""
-        if not self.use_graphs or self.cm.num_state_slots:
+        if not self.use_graphs:          # (off too when a part of the model is not capturable)
             return None
         if all(it.num_new_tokens == 1 and it.want == (0,) for it in items):
             if len(items) > self.GRAPH_BUCKETS[-1]:
@@ -442,8 +446,17 @@ class ModelRunner:
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         before = getattr(self.ops, "launches", 0)
-        with torch.cuda.graph(graph):
-            logits = self.model.forward(ctx)
+        # No garbage collection while the stream captures: collecting an older engine's graphs then
+        # (their destructors free device memory) is not permitted during a capture and would invalidate it.
+        gc.collect()
+        gc_was_on = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(ctx)
+        finally:
+            if gc_was_on:
+                gc.enable()
         launches = getattr(self.ops, "launches", 0) - before
         if hasattr(self.ops, "launches"):
             self.ops.launches = before        # capturing launches nothing; replays are counted in graph_launches

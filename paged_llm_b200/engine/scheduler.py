@@ -46,6 +46,14 @@ class SchedulerOutput:
     num_prefill_tokens: int = 0
     num_decode_tokens: int = 0
 
+    def grant(self, seq: Sequence, num_tokens: int) -> None:
+        """`seq` brings `num_tokens` tokens in this step; they count as decoding once its prompt is through."""
+        if seq.is_prefill_done:
+            self.num_decode_tokens += num_tokens
+        else:
+            self.num_prefill_tokens += num_tokens
+        self.scheduled.append(ScheduledSequence(seq, num_tokens))
+
     @property
     def is_empty(self) -> bool:
         return not self.scheduled
@@ -60,8 +68,8 @@ class Scheduler:
         self.config = config
         self.bm = block_manager
         self.eos_token_id = eos_token_id
-        self.waiting: deque[Sequence] = deque()
-        self.running: list[Sequence] = []
+        self.waiting: deque[Sequence] = deque()     # admission order; a preempted request goes to the front
+        self.running: list[Sequence] = []           # admission order: the last one is the first to be preempted
         self.finished: list[Sequence] = []
         self.num_preemptions = 0
 
@@ -93,88 +101,90 @@ class Scheduler:
         seq.status = SequenceStatus.WAITING
         self.waiting.append(seq)
 
+    def _retire(self, seq: Sequence, status: SequenceStatus) -> None:
+        """The request leaves for good: what it holds in the cache goes back."""
+        self.bm.free(seq)
+        seq.status = status
+        self.finished.append(seq)
+
     def abort(self, seq_id: int) -> None:
-        for queue in (self.waiting, self.running):
-            for seq in list(queue):
-                if seq.seq_id == seq_id:
-                    queue.remove(seq)
-                    self.bm.free(seq)
-                    seq.status = SequenceStatus.FINISHED_ABORTED
-                    self.finished.append(seq)
-                    return
+        seq = next((s for s in (*self.waiting, *self.running) if s.seq_id == seq_id), None)
+        if seq is None:
+            return
+        (self.waiting if seq.status is SequenceStatus.WAITING else self.running).remove(seq)
+        self._retire(seq, SequenceStatus.FINISHED_ABORTED)
 
     @property
     def has_unfinished(self) -> bool:
-        return bool(self.waiting or self.running)
+        return len(self.waiting) + len(self.running) > 0
 
     @property
     def num_unfinished(self) -> int:
         return len(self.waiting) + len(self.running)
 
     # ---- one step's decisions ----------------------------------------------------
-    def _preempt(self, seq: Sequence, out: SchedulerOutput) -> None:
-        self.running.remove(seq)
-        self.bm.free(seq)
-        seq.reset_for_recompute()
-        self.waiting.appendleft(seq)
-        out.preempted.append(seq)
+    def _portion(self, need: int, left: int) -> int:
+        """Tokens a request that still has `need` to compute may bring when `left` remain of the
+        step's budget: all of them, a cut prompt if chunking is on, else none this step."""
+        if need <= left:
+            return need
+        return left if self.config.enable_chunked_prefill else 0
+
+    def _evict_last(self, out: SchedulerOutput) -> Sequence:
+        """Preemption by recompute of the most recently admitted running request."""
+        victim = self.running.pop()
+        self.bm.free(victim)
+        victim.reset_for_recompute()
+        self.waiting.appendleft(victim)
+        out.preempted.append(victim)
         self.num_preemptions += 1
+        return victim
+
+    def _make_room(self, seq: Sequence, num_tokens: int, out: SchedulerOutput) -> bool:
+        """Pages for `num_tokens` more tokens of a running request, evicting from the end of
+        `running` while the pool is short.  False if `seq` itself had to go."""
+        while self.bm.allocate_slots(seq, num_tokens) is None:
+            if self._evict_last(out) is seq:
+                return False
+        return True
+
+    def _serve_running(self, out: SchedulerOutput, left: int) -> int:
+        """Running requests in admission order.  Evictions only ever shorten `running` from its
+        end, so walking it by index never meets a request that was preempted in this pass."""
+        i = 0
+        while i < len(self.running) and left > 0:
+            seq = self.running[i]
+            n = self._portion(seq.num_uncomputed_tokens, left)
+            if n > 0 and self._make_room(seq, n, out):
+                out.grant(seq, n)
+                left -= n
+            i += 1
+        return left
+
+    def _admit_waiting(self, out: SchedulerOutput, left: int) -> int:
+        """Waiting requests strictly in order, until one does not fit (budget, request limit,
+        state slot or pages): it keeps its place and is tried again next step."""
+        while self.waiting and left > 0 and len(self.running) < self.config.max_num_seqs:
+            seq = self.waiting[0]
+            hits, num_cached = self.bm.get_computed_blocks(seq)
+            n = self._portion(seq.num_tokens - num_cached, left)
+            if n == 0 or not self.bm.acquire_state_slot(seq):
+                break
+            if self.bm.allocate_slots(seq, n, hits) is None:
+                self.bm.release_state_slot(seq)
+                break
+            self.waiting.popleft()
+            seq.num_computed_tokens = seq.num_cached_tokens = num_cached
+            seq.status = SequenceStatus.RUNNING
+            self.running.append(seq)
+            out.grant(seq, n)
+            left -= n
+        return left
 
     def schedule(self) -> SchedulerOutput:
         out = SchedulerOutput()
-        budget = self.config.max_num_batched_tokens
-        chunked = self.config.enable_chunked_prefill
-
-        # running requests first, in admission order
-        for seq in list(self.running):
-            if budget == 0:
-                break
-            if seq.status is not SequenceStatus.RUNNING:
-                continue                              # preempted earlier in this loop
-            want = seq.num_uncomputed_tokens
-            assert want >= 1
-            if want > budget:
-                if not chunked:
-                    continue
-                want = budget
-            while self.bm.allocate_slots(seq, want) is None:
-                victim = self.running[-1]
-                self._preempt(victim, out)
-                if victim is seq:
-                    break
-            if seq.status is not SequenceStatus.RUNNING:
-                continue
-            budget -= want
-            decoding = seq.is_prefill_done
-            out.scheduled.append(ScheduledSequence(seq, want))
-            if decoding:
-                out.num_decode_tokens += want
-            else:
-                out.num_prefill_tokens += want
-
-        # then admit from the waiting queue, strictly in order
-        while self.waiting and budget > 0 and len(self.running) < self.config.max_num_seqs:
-            seq = self.waiting[0]
-            hits, num_cached = self.bm.get_computed_blocks(seq)
-            want = seq.num_tokens - num_cached
-            assert want >= 1
-            if want > budget:
-                if not chunked:
-                    break
-                want = budget
-            if not self.bm.acquire_state_slot(seq):
-                break
-            if self.bm.allocate_slots(seq, want, hits) is None:
-                self.bm.release_state_slot(seq)
-                break                                  # pool full: keep the order, try next step
-            self.waiting.popleft()
-            seq.num_computed_tokens = num_cached
-            seq.num_cached_tokens = num_cached
-            seq.status = SequenceStatus.RUNNING
-            self.running.append(seq)
-            budget -= want
-            out.scheduled.append(ScheduledSequence(seq, want))
-            out.num_prefill_tokens += want
+        left = self._serve_running(out, self.config.max_num_batched_tokens)
+        self._admit_waiting(out, left)
         return out
 
     # ---- after the step ----------------------------------------------------------
@@ -227,7 +237,6 @@ class Scheduler:
                     del seq.token_ids[known:]
                     seq.num_unresolved = 0
                 self.running.remove(seq)
-                self.bm.free(seq)
+                self._retire(seq, seq.status)
                 done.append(seq)
-        self.finished.extend(done)
         return done

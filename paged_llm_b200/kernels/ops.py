@@ -44,6 +44,7 @@ class AttnParams(ctypes.Structure):
         ("q_stride", c_int), ("out_stride", c_int), ("bt_stride", c_int), ("n_work", c_int), ("max_splits", c_int),
         ("nh", c_int), ("nkv", c_int), ("d", c_int), ("ps", c_int), ("window", c_int), ("is_small", c_int),
         ("scale", c_float), ("ps_shift", c_int), ("counters", c_void_p), ("num_pages", c_int), ("cluster", c_int),
+        ("softcap", c_float), ("slopes", c_void_p),
     ]
 
 
@@ -439,7 +440,11 @@ class CudaOps:
         lib = load_module(f"attn_bf16_d{b}")
         return lib, getattr(lib, f"pl_attention_bf16_d{b}")
 
-    def paged_attention(self, qkv, nh, nkv, d, kv, block_table, ctx, scale, window):
+    def paged_attention(self, qkv, nh, nkv, d, kv, block_table, ctx, scale, window, softcap=None, slopes=None):
+        """Attention of the step's tokens over the paged cache.  `softcap` (scores become
+        softcap * tanh(score / softcap)) and `slopes` (a float32 tensor [nh]: head h adds
+        slopes[h] * (key position - query position) to its scores) modify the scores; both off
+        by default."""
         T = ctx.num_tokens
         plan = ctx.attention_plans[(nh // nkv, nkv, window, d)]
         out = torch.empty((T, nh * d), dtype=qkv.dtype, device=self.device)
@@ -451,6 +456,10 @@ class CudaOps:
         p.q_stride, p.out_stride, p.bt_stride = qkv.shape[1], nh * d, block_table.shape[1]
         p.nh, p.nkv, p.d, p.ps, p.num_pages = nh, nkv, d, kv.shape[3], kv.shape[0]
         p.window, p.scale, p.max_splits = int(window or 0), float(scale), plan.max_splits
+        p.softcap = float(softcap or 0.0)
+        if slopes is not None:
+            assert slopes.dtype == torch.float32 and slopes.numel() == nh and slopes.is_contiguous() and slopes.is_cuda
+            p.slopes = slopes.data_ptr()
         ps = kv.shape[3]
         p.ps_shift = ps.bit_length() - 1 if ps & (ps - 1) == 0 else -1
         p.counters = 0

@@ -9,7 +9,11 @@ one matrix when the weights are taken, so a step runs one product for them.
 
 `scale` and `window` are parameters: the reference fixes scale = head_dim^-0.5
 (llama.py:138) and has no window; a window w keeps, for the query at position p,
-the keys at positions p-w+1 .. p.
+the keys at positions p-w+1 .. p.  Two score modifiers, off unless a spec asks
+for them (the reference has neither): `score_cap` c turns a scaled score s into
+c * tanh(s / c), and `position_slopes` (one number per query head) adds
+slope * (key position - query position) to it, a bias by distance that needs no
+rotation of q and k.
 """
 
 from __future__ import annotations
@@ -24,13 +28,21 @@ class PagedAttention(Mixer):
     accepts_lazy_input = True
 
     def __init__(self, weights: dict[str, str], hidden_size: int, num_heads: int, num_kv_heads: int,
-                 head_dim: int, scale: float | None = None, window: int | None = None, position=None):
+                 head_dim: int, scale: float | None = None, window: int | None = None, position=None,
+                 score_cap: float | None = None, position_slopes=None):
         if num_heads % num_kv_heads:
             raise ValueError(f"num_heads={num_heads} is not a multiple of num_kv_heads={num_kv_heads}")
         self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = hidden_size, num_heads, num_kv_heads, head_dim
         self.scale = float(scale) if scale is not None else head_dim ** -0.5
         self.window = window
         self.position = position
+        if score_cap is not None and not score_cap > 0:
+            raise ValueError(f"score_cap={score_cap} must be positive")
+        if position_slopes is not None and len(position_slopes) != num_heads:
+            raise ValueError(f"position_slopes has {len(position_slopes)} entries for {num_heads} heads")
+        self.score_cap = score_cap
+        self.position_slopes = [float(x) for x in position_slopes] if position_slopes is not None else None
+        self._slopes = None              # the same on the device, made at the first step
         self.names = weights
         self.w_qkv = None
         self.w_o = None
@@ -63,6 +75,11 @@ class PagedAttention(Mixer):
         block_table = ctx.block_tables[cache.group]
         qkv = ops.qkv_rope_write(h, self.w_qkv, self.num_heads, self.num_kv_heads, self.head_dim, self.position,
                                  ctx, cache.kv, block_table, write=cache.owner)
+        if self.position_slopes is not None and self._slopes is None:
+            self._slopes = torch.tensor(self.position_slopes, dtype=torch.float32, device=qkv.device)
+        extra = {}
+        if self.score_cap is not None or self._slopes is not None:
+            extra = dict(softcap=self.score_cap, slopes=self._slopes)
         o = ops.paged_attention(qkv, self.num_heads, self.num_kv_heads, self.head_dim, cache.kv,
-                                block_table, ctx, self.scale, self.window)
+                                block_table, ctx, self.scale, self.window, **extra)
         return LazyLinear(o, self.w_o)

@@ -5,7 +5,8 @@ parameter of the same name, ignores names ending in `rotary_emb.inv_freq`, and
 raises on an unexpected name or on missing ones (pagedllm/model/loader.py:39-69).
 Here the model says which tensors it expects (`tensor_specs`) and the loader
 checks all of them at once: ONE error lists every missing tensor, every
-unexpected tensor and every wrong shape.
+unexpected tensor, every wrong shape and every tensor stored in a type that its
+role cannot take (an integer or 8-bit tensor where a matrix is expected).
 
 Storage: matrices are kept in the compute dtype (bfloat16 or float32); vectors
 (norm weights) that the file stores in 32-bit stay 32-bit; integer tables become
@@ -27,12 +28,13 @@ _DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 
 
 class WeightError(KeyError):
-    """The checkpoint does not match the model.  `missing`, `unexpected` and
-    `wrong_shape` hold the offending names."""
+    """The checkpoint does not match the model.  `missing`, `unexpected`,
+    `wrong_shape`, `wrong_dtype` and `duplicates` hold the offending names."""
 
-    def __init__(self, missing, unexpected, wrong_shape, duplicates=()):
+    def __init__(self, missing, unexpected, wrong_shape, duplicates=(), wrong_dtype=()):
         self.missing, self.unexpected = list(missing), list(unexpected)
         self.wrong_shape, self.duplicates = list(wrong_shape), list(duplicates)
+        self.wrong_dtype = list(wrong_dtype)
         lines = ["checkpoint does not match the model:"]
         if self.missing:
             lines.append(f"  missing tensors ({len(self.missing)}): " + ", ".join(self.missing))
@@ -41,6 +43,9 @@ class WeightError(KeyError):
         if self.wrong_shape:
             lines.append(f"  wrong shapes ({len(self.wrong_shape)}): " + ", ".join(
                 f"{n}: file {tuple(got)} != expected {tuple(want)}" for n, got, want in self.wrong_shape))
+        if self.wrong_dtype:
+            lines.append(f"  wrong dtypes ({len(self.wrong_dtype)}): " + ", ".join(
+                f"{n}: file stores {got}, a {role} needs {want}" for n, got, role, want in self.wrong_dtype))
         if self.duplicates:
             lines.append(f"  stored in more than one file ({len(self.duplicates)}): " + ", ".join(self.duplicates))
         super().__init__("\n".join(lines))
@@ -80,6 +85,17 @@ def storage_dtype(spec: TensorSpec, stored: torch.dtype, compute: torch.dtype) -
     return compute
 
 
+_FLOATS = (torch.float32, torch.bfloat16, torch.float16, torch.float64)
+_INTS = (torch.int32, torch.int64, torch.int16, torch.int8, torch.uint8)
+
+
+def stored_dtype_ok(spec: TensorSpec, stored: torch.dtype) -> bool:
+    """Matrices and vectors must be stored as floating point of 16 bits or more (an 8-bit or
+    integer tensor would be a quantized checkpoint, which this engine does not run, and casting
+    it would give numbers that mean nothing); integer tables as integers."""
+    return stored in (_INTS if spec.role == "table_int" else _FLOATS)
+
+
 def read_safetensors(path: str) -> tuple[dict[str, torch.Tensor], list[str]]:
     """All tensors of all *.safetensors files of a folder, on the CPU, and the
     names that occur in more than one file."""
@@ -103,18 +119,22 @@ def check_and_cast(expected: dict[str, TensorSpec], tensors: dict[str, torch.Ten
                    device, ignored_suffixes: tuple[str, ...] = (), duplicates=()) -> dict[str, torch.Tensor]:
     """Validate names and shapes against the model's expectations, then cast and
     move.  Raises one `WeightError` that lists everything that is wrong."""
-    missing, unexpected, wrong_shape = [], [], []
+    missing, unexpected, wrong_shape, wrong_dtype = [], [], [], []
     for name, spec in expected.items():
         if name not in tensors:
             if not spec.optional:
                 missing.append(name)
-        elif tuple(tensors[name].shape) != tuple(spec.shape):
+            continue
+        if tuple(tensors[name].shape) != tuple(spec.shape):
             wrong_shape.append((name, tuple(tensors[name].shape), tuple(spec.shape)))
+        if not stored_dtype_ok(spec, tensors[name].dtype):
+            wrong_dtype.append((name, str(tensors[name].dtype).replace("torch.", ""), spec.role,
+                                "an integer type" if spec.role == "table_int" else "float32, bfloat16 or float16"))
     for name in tensors:
         if name not in expected and not any(name.endswith(s) for s in ignored_suffixes):
             unexpected.append(name)
-    if missing or unexpected or wrong_shape or duplicates:
-        raise WeightError(sorted(missing), sorted(unexpected), sorted(wrong_shape), sorted(duplicates))
+    if missing or unexpected or wrong_shape or duplicates or wrong_dtype:
+        raise WeightError(sorted(missing), sorted(unexpected), sorted(wrong_shape), sorted(duplicates), sorted(wrong_dtype))
     out = {}
     for name, spec in expected.items():
         if name not in tensors:

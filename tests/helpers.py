@@ -16,7 +16,9 @@ from tests.tiny import TINIES, make_folder, random_tokens, read_folder
 #  activations is left, which is what a misplaced key or a stale page would have to hide in.
 F32_TOL = 2e-5
 BF16_REL_TOL = 3e-2
-BF16_VS_F32_TOL = 1e-2
+#  Measured on a B200 over every schedule of the tiny and the wide models: at most 1.5e-2 of the largest
+#  logit (the far tail of some 10^5 logits per comparison).
+BF16_VS_F32_TOL = 2e-2
 
 
 def model_folder(tmp_path_factory, name: str, dtype: str = "float32"):

@@ -93,13 +93,15 @@ def apply_rotary(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch
 
 
 def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
-                     window: int | None = None) -> torch.Tensor:
+                     window: int | None = None, softcap: float | None = None, slopes=None) -> torch.Tensor:
     """q: [T, heads, d], k/v: [T, kv_heads, d], one whole sequence.
 
     Query head h reads kv head h // (heads // kv_heads); scores scaled, keys after
     the query's position masked out, softmax over keys, weighted sum of values
     (pagedllm/attention/reference.py:23-55).  `window`, which the reference does
-    not have, keeps only the last `window` keys (the query's own included).
+    not have, keeps only the last `window` keys (the query's own included); `softcap` c turns a scaled score s into c * tanh(s / c) and
+    `slopes` (one number per query head) adds slope * (key position - query position): two
+    score modifiers of this engine's attention part, neither of which the reference has.
     """
     T, heads, _ = q.shape
     group = heads // k.shape[1]
@@ -107,6 +109,10 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: f
     v = v.repeat_interleave(group, dim=1)
     scores = torch.einsum("qhd,khd->hqk", q, k) * scale
     pos = torch.arange(T)
+    if softcap:
+        scores = softcap * torch.tanh(scores / softcap)
+    if slopes is not None:
+        scores = scores + torch.as_tensor(slopes, dtype=scores.dtype)[:, None, None] * (pos[None, None, :] - pos[None, :, None])
     hidden = pos[None, :] > pos[:, None]
     if window is not None:
         hidden = hidden | (pos[None, :] <= pos[:, None] - window)

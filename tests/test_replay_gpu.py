@@ -10,7 +10,7 @@ import numpy as np
 import pytest
 
 from tests import schedules
-from tests.helpers import assert_logits_close, model_folder, plain_logits, requests_for
+from tests.helpers import assert_bf16_close_to_f32, assert_logits_close, model_folder, plain_logits, requests_for
 from tests.tiny import TINIES
 
 pytestmark = pytest.mark.gpu
@@ -53,6 +53,23 @@ def test_schedule_matches_plain(folders, name, dtype, schedule):
     if schedule == "mixed":
         total = sum(-(-len(t) // rp.cm.block_size) for t in reqs.values())
         assert total > rp.cm.num_blocks, "the mixed trace must need more pages than the pool has, so that they are reused"
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("schedule", ["whole", "tail", "portions", "mixed"])
+def test_bfloat16_against_the_float32_engine(tmp_path_factory, name, schedule):
+    """Both engines on a folder of bfloat16 values: the weights are the same numbers, so the
+    logits differ by the rounding of activations only, which is held much tighter than the
+    distance to the plain float32 model."""
+    folder = model_folder(tmp_path_factory, name, dtype="bfloat16")
+    hf, _ = TINIES[name]
+    reqs = requests_for(hf["vocab_size"], LENGTHS[name], seed=ord(name))
+    steps, max_tokens = getattr(schedules, schedule)(reqs)
+    block = 8 if name == "B" else 16
+    a, _ = replay(folder, "float32", steps, max_tokens, block_size=block)
+    b, _ = replay(folder, "bfloat16", steps, max_tokens, block_size=block)
+    for k in a:
+        assert_bf16_close_to_f32(b[k], a[k], f"{schedule}/{name}/step {k}")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -76,6 +76,8 @@ def test_one_error_lists_everything(tmp_path):
     del t["model.norm.weight"]
     t["model.layers.0.self_attn.q_proj.bias"] = torch.zeros(64)
     t["model.layers.0.mlp.down_proj.weight"] = torch.zeros(64, 171)
+    t["model.layers.1.self_attn.o_proj.weight"] = torch.zeros(64, 64, dtype=torch.int8)     # a quantized matrix
+    t["model.layers.1.input_layernorm.weight"] = torch.ones(64, dtype=torch.int32)
     save_file(t, path)
     with pytest.raises(WeightError) as info:
         load_model(d, "float32", "cpu")
@@ -83,8 +85,11 @@ def test_one_error_lists_everything(tmp_path):
     assert e.missing == ["model.layers.1.mlp.up_proj.weight", "model.norm.weight"]
     assert e.unexpected == ["model.layers.0.self_attn.q_proj.bias"]
     assert [w[0] for w in e.wrong_shape] == ["model.layers.0.mlp.down_proj.weight"]
+    assert [w[0] for w in e.wrong_dtype] == ["model.layers.1.input_layernorm.weight",
+                                             "model.layers.1.self_attn.o_proj.weight"]
     msg = str(e)
-    for needle in ("missing tensors (2)", "unexpected tensors (1)", "wrong shapes (1)", "(64, 171)", "(64, 172)"):
+    for needle in ("missing tensors (2)", "unexpected tensors (1)", "wrong shapes (1)", "(64, 171)", "(64, 172)",
+                   "wrong dtypes (2)", "file stores int8"):
         assert needle in msg, msg
 
 

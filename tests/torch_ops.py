@@ -114,7 +114,7 @@ class TorchOps:
         return plan_attention(q_lens, k_lens, group_size, num_kv_heads, window, small_rows=16, large_rows=64,
                               min_split_keys=128, num_sms=4, pad_requests=pad_requests, fixed_capacity=fixed_capacity)
 
-    def paged_attention(self, qkv, nh, nkv, d, kv, block_table, ctx, scale, window):
+    def paged_attention(self, qkv, nh, nkv, d, kv, block_table, ctx, scale, window, softcap=None, slopes=None):
         self._count("paged_attention")
         T = ctx.num_tokens
         q = qkv[:, :nh * d].view(T, nh, d).float()
@@ -135,6 +135,10 @@ class TorchOps:
             qs = q[cu[s]:cu[s + 1]]
             scores = torch.einsum("qhd,khd->hqk", qs, k) * scale
             qpos = torch.arange(first, lk)
+            if softcap:
+                scores = softcap * torch.tanh(scores / softcap)
+            if slopes is not None:
+                scores = scores + slopes.float().cpu()[:, None, None] * (idx[None, None, :] - qpos[None, :, None])
             hidden = idx[None, :] > qpos[:, None]
             if window:
                 hidden |= idx[None, :] <= qpos[:, None] - window
