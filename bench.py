@@ -165,16 +165,28 @@ def write_tokenizer(folder: str, vocab: int) -> None:
         json.dump({"tokenizer_class": "PreTrainedTokenizerFast", "unk_token": "t0", "eos_token": "t1"}, f)
 
 
-def make_model(folder: str, size: str, layers: int | None, with_tokenizer: bool = False):
-    from paged_llm_b200.config import LlamaConfig
-    from paged_llm_b200.weights import write_model_folder
+STUB_ABOVE_PARAMS = 2_000_000_000      # larger models get their random weights drawn on the device
+
+
+def make_model(folder: str, size: str, layers: int | None, with_tokenizer: bool = False, on_device: bool | None = None):
+    """Writes a model folder of the named layer sizes with random weights N(0, 0.02), seed 0.  Models of
+    more than two billion parameters (or `on_device`) get a folder without tensors whose weights the
+    engine draws on the device (weights/random_init.py: write_random_stub); the reference arm always
+    gets tensors."""
+    from paged_llm_b200.config.registry import parse_model_config
+    from paged_llm_b200.weights import write_model_folder, write_random_stub
 
     hf = {"architectures": ["LlamaForCausalLM"], **SIZES[size]}
     full_layers = hf["num_hidden_layers"]
     if layers:
         hf["num_hidden_layers"] = layers
-    cfg = LlamaConfig.from_hf_dict(hf)
-    write_model_folder(folder, cfg, seed=0, std=0.02, dtype="bfloat16")
+    _, cfg = parse_model_config(hf)          # the architecture named in the configuration decides the config class
+    if on_device is None:
+        on_device = cfg.num_parameters > STUB_ABOVE_PARAMS and not with_tokenizer
+    if on_device:
+        write_random_stub(folder, cfg, seed=0, std=0.02, dtype="bfloat16")
+    else:
+        write_model_folder(folder, cfg, seed=0, std=0.02, dtype="bfloat16")
     if with_tokenizer:
         write_tokenizer(folder, cfg.vocab_size)
     return cfg, full_layers
@@ -216,7 +228,8 @@ def device_decode_loop(engine, batch: int, steps: int, warmup: int, prompt_len: 
     for i in range(0, batch, chunk):
         group = seqs[i:i + chunk]
         for s in group:
-            assert cm.allocate_slots(s, prompt_len) is not None, "pool too small for the benchmark"
+            ok = cm.allocate_slots(s, prompt_len)
+            assert ok is not None, "pool too small for the benchmark"
         logits = runner.step([StepItem(s, prompt_len, (prompt_len - 1,)) for s in group])
         toks = ops.argmax(logits).tolist()
         for s, t in zip(group, toks):
@@ -226,7 +239,8 @@ def device_decode_loop(engine, batch: int, steps: int, warmup: int, prompt_len: 
 
     def one_step(first: bool):
         for s in seqs:
-            assert cm.allocate_slots(s, 1) is not None
+            ok = cm.allocate_slots(s, 1)
+            assert ok is not None, "pool too small for the benchmark"
         logits = runner.step(items)
         nxt = ops.argmax(logits)
         for s in seqs:
@@ -329,7 +343,8 @@ def prefill_once(engine, tokens: int, iters: int = 5, warmup: int = 3):
     times = []
     for i in range(warmup + iters):
         seq = Sequence(prompts_for(vocab, 1, tokens, seed=7 + i)[0], SamplingParams())
-        assert cm.allocate_slots(seq, tokens) is not None
+        ok = cm.allocate_slots(seq, tokens)
+        assert ok is not None, "pool too small for the benchmark"
         torch.cuda.synchronize()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
@@ -342,19 +357,116 @@ def prefill_once(engine, tokens: int, iters: int = 5, warmup: int = 3):
     return statistics.median(times)
 
 
+def mixed_step(engine, batch: int, portion: int, context: int, iters: int = 5, warmup: int = 3):
+    """One step that carries `batch` decoding requests (context `context`) beside one prompt portion of
+    `portion` tokens of a new request: the step a serving engine runs while a long prompt arrives.
+    Returns the median milliseconds of the step (CUDA events)."""
+    import torch
+    from paged_llm_b200.config import SamplingParams
+    from paged_llm_b200.engine.runner import StepItem
+    from paged_llm_b200.engine.sequence import Sequence
+
+    cm, runner, ops = engine.block_manager, engine.runner, engine.ops
+    vocab = engine.model_config.vocab_size
+    seqs = [Sequence(p, SamplingParams()) for p in prompts_for(vocab, batch, context, seed=3)]
+    chunk = max(1, engine.config.max_num_batched_tokens // context)
+    for i in range(0, batch, chunk):
+        group = seqs[i:i + chunk]
+        for s in group:
+            ok = cm.allocate_slots(s, context)
+            assert ok is not None, "pool too small for the benchmark"
+        runner.step([StepItem(s, context, ()) for s in group])
+        for s in group:
+            s.num_computed_tokens = context
+            s.append_token(1)
+    times = []
+    for i in range(warmup + iters):
+        new = Sequence(prompts_for(vocab, 1, portion, seed=50 + i)[0], SamplingParams())
+        ok = cm.allocate_slots(new, portion)
+        assert ok is not None
+        for s in seqs:
+            ok = cm.allocate_slots(s, 1)
+            assert ok is not None
+        items = [StepItem(s, 1, (0,)) for s in seqs] + [StepItem(new, portion, (portion - 1,))]
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        ops.argmax(runner.step(items))
+        end.record()
+        torch.cuda.synchronize()
+        if i >= warmup:
+            times.append(start.elapsed_time(end))
+        for s in seqs:
+            s.num_computed_tokens += 1
+            s.append_token(1)
+        cm.free(new)
+    for s in seqs:
+        cm.free(s)
+    return statistics.median(times)
+
+
+def validate(args) -> dict:
+    """The float32 validation run at the benchmark's layer sizes: the same trace (a 2,048-token
+    portion, 32 decoded tokens, portions of changing size, a mixed batch) through the bfloat16 engine
+    and the true-float32 engine on the same weight values, and the float32 engine against the plain
+    implementation of tests/plain_llama.py on a shorter request.  Reports the largest differences
+    relative to the largest logit."""
+    import numpy as np
+    from paged_llm_b200.engine.replay import TraceReplayer
+    from tests import plain_llama, schedules
+    from tests.tiny import random_tokens, read_folder
+
+    with tempfile.TemporaryDirectory() as folder:
+        cfg, full_layers = make_model(folder, args.size, args.layers, on_device=False)
+        V = cfg.vocab_size
+        long_req = random_tokens(V, 2048 + 32, 1)
+        reqs = {"w": long_req, "p": random_tokens(V, 700, 2), "q": random_tokens(V, 333, 3), "r": random_tokens(V, 90, 4)}
+        # whole + tail for the long request, portions and a mixed batch for the others
+        steps = [{"step": 0, "entries": [{"id": "w", "tokens": long_req[:2048], "want": [0, 1, 511, 1024, 2047]}], "end": []}]
+        for i in range(2048, len(long_req)):
+            steps.append({"step": len(steps), "entries": [{"id": "w", "tokens": [long_req[i]], "want": [0]}],
+                          "end": ["w"] if i == len(long_req) - 1 else []})
+        more, _ = schedules.mixed({k: reqs[k] for k in "pqr"}, live=3, seed=1, choices=(2, 5, 16, 40, 64, 130, 257))
+        more = schedules.keep_wanted(more, lambda rid, p: p % 16 == 0 or p >= len(reqs[rid]) - 4)
+        for rec in more:
+            steps.append({**rec, "step": len(steps)})
+        max_tokens = 2112 + sum(schedules._round64(len(reqs[k])) for k in "pqr")
+        out = {}
+        for dtype in ("float32", "bfloat16"):
+            rp = TraceReplayer(folder, dtype, max_tokens)
+            res = {rec["step"]: o for rec in steps if (o := rp.step(rec)) is not None}
+            out[dtype] = schedules.collect(steps, res)
+            del rp
+        worst16 = max(float(np.abs(out["bfloat16"][k] - out["float32"][k]).max() / np.abs(out["float32"][k]).max())
+                      for k in out["float32"])
+        hf, w = read_folder(folder)
+        rows = schedules.wanted_positions(steps)["q"]
+        want = plain_llama.forward_logits(hf, w, reqs["q"], rows=rows).numpy()
+        worst32 = float(np.abs(out["float32"]["q"] - want).max() / max(1.0, np.abs(want).max()))
+    return {"only": "validate", "size": args.size, "layers": cfg.num_hidden_layers, "layers_full": full_layers,
+            "positions_compared": int(sum(len(v) for v in out["float32"].values())),
+            "bf16_vs_f32_engine_rel": round(worst16, 6), "f32_engine_vs_plain_rel": round(worst32, 8),
+            "trace": "2,048-token portion + 32 decoded tokens; three requests of 700/333/90 tokens mixed, portions of 2 to 257 tokens"}
+
+
 def run_ours(args) -> dict:
     import torch
     from paged_llm_b200 import EngineConfig, LLMEngine
 
     peaks = load_peaks()
+    if args.only == "validate":
+        return validate(args)
     with tempfile.TemporaryDirectory() as folder:
         cfg, full_layers = make_model(folder, args.size, args.layers)
-        prompt_len = args.context if args.only == "decode" and args.context else PROMPT_LEN
-        pre_tokens = args.prefill_tokens if args.only == "prefill" and args.prefill_tokens else PREFILL_TOKENS
+        prompt_len = args.context if args.only in ("decode", "mixed") and args.context else PROMPT_LEN
+        pre_tokens = args.prefill_tokens if args.only in ("prefill", "mixed") and args.prefill_tokens else PREFILL_TOKENS
         max_len = max(prompt_len + args.steps + args.warmup + DECODE_LEN, pre_tokens) + 64
         if args.only == "ragged":
             max_len = RAGGED_PROMPTS[1] + RAGGED_OUTPUTS[1] + 64
         seqs = max(args.batch, 64) if prompt_len == PROMPT_LEN else args.batch
+        if args.only == "mixed":
+            max_len = max(max_len, prompt_len + 64, pre_tokens + 64)
+            seqs = args.batch + 2
         engine = LLMEngine(folder, EngineConfig(
             dtype="bfloat16", block_size=BLOCK_SIZE, max_model_len=max_len, max_num_seqs=max(seqs, 64),
             max_num_batched_tokens=max(2048, pre_tokens), enable_prefix_caching=False,
@@ -368,9 +480,20 @@ def run_ours(args) -> dict:
     if args.only == "decode":            # a short run of one part, for profilers and other context lengths
         ms, launches, ctx_mid = device_decode_loop(engine, B, args.steps, args.warmup, prompt_len)
         step_bytes = engine.model.weight_bytes_per_step() + B * ctx_mid * (engine.kv_cache.page_bytes() // BLOCK_SIZE)
-        return {"only": "decode", "batch": B, "context": ctx_mid, "ms_per_step": round(ms, 4),
-                "launches_per_step": launches, "layers": cfg.num_hidden_layers,
-                "gb_per_s": round(step_bytes / (ms * 1e-3) / 1e9, 1)}
+        gbs = step_bytes / (ms * 1e-3) / 1e9
+        return {"only": "decode", "size": args.size, "batch": B, "context": ctx_mid, "ms_per_step": round(ms, 4),
+                "tokens_per_s": round(B * 1000.0 / ms, 1), "launches_per_step": launches,
+                "layers": cfg.num_hidden_layers, "layers_full": full_layers, "gb_per_s": round(gbs, 1),
+                "frac": round(gbs / peaks["hbm_gbs"], 4), "peaks_source": peaks["source"]}
+    if args.only == "mixed":             # B decoding requests beside one prompt portion, in one step
+        portion = args.prefill_tokens or PREFILL_TOKENS
+        ms = mixed_step(engine, B, portion, prompt_len, iters=max(3, min(args.steps, 10)), warmup=args.warmup)
+        flops = step_flops(cfg, portion) + B * step_flops(cfg, 1, prompt_len)
+        return {"only": "mixed", "size": args.size, "layers": cfg.num_hidden_layers, "layers_full": full_layers,
+                "decoding_requests": B, "context": prompt_len, "portion": portion, "ms": round(ms, 3),
+                "tokens_per_s": round((portion + B) * 1000.0 / ms, 1),
+                "tflops": round(flops / (ms * 1e-3) / 1e12, 1),
+                "frac": round(flops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"], 4), "peaks_source": peaks["source"]}
     if args.only == "prefill":
         pre_ms = prefill_once(engine, pre_tokens, iters=max(1, args.steps), warmup=args.warmup)
         tflops = step_flops(cfg, pre_tokens) / (pre_ms * 1e-3) / 1e12
@@ -488,14 +611,16 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--context", type=int, default=None, help="with --only decode: prompt length instead of 512")
+    ap.add_argument("--context", type=int, default=None,
+                    help="with --only decode or mixed: prompt length of the decoding requests instead of 512")
     ap.add_argument("--prefill-tokens", type=int, default=None,
                     help="with --only prefill: length of the prompt (one step) instead of 2,048")
     ap.add_argument("--size", choices=sorted(SIZES), default="tinyllama-1.1b")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the named size (reported in config)")
-    ap.add_argument("--only", choices=["decode", "prefill", "ragged"], default=None,
-                    help="run only the decode loop, only the prefill step, or the ragged serving workload through "
-                         "LLMEngine.generate, and print a short line")
+    ap.add_argument("--only", choices=["decode", "prefill", "ragged", "mixed", "validate"], default=None,
+                    help="run only the decode loop, only the prefill step, the ragged serving workload through "
+                         "LLMEngine.generate, one mixed step (--batch decoding requests of --context tokens beside one "
+                         "portion of --prefill-tokens), or the float32 validation run, and print a short line")
     args = ap.parse_args()
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
         if int(os.environ.get("RANK", "0")) == 0:

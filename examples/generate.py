@@ -54,10 +54,11 @@ def main() -> None:
     tmp = None
     model = args.model
     if args.random_weights:
-        from paged_llm_b200.config import LlamaConfig
+        from paged_llm_b200.config.registry import parse_model_config
         from paged_llm_b200.weights import write_model_folder
         tmp = tempfile.TemporaryDirectory()
-        cfg = LlamaConfig.from_hf_dict({"architectures": ["LlamaForCausalLM"], **NAMED_SIZES[args.random_weights]})
+        # the architecture named in the configuration decides the config class, as for a checkpoint
+        _, cfg = parse_model_config({"architectures": ["LlamaForCausalLM"], **NAMED_SIZES[args.random_weights]})
         model = write_model_folder(tmp.name, cfg, seed=args.seed, dtype="bfloat16" if args.dtype == "auto" else args.dtype)
     if model is None:
         ap.error("--model or --random-weights is required")

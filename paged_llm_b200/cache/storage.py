@@ -123,6 +123,15 @@ class CacheStorage:
         for state in states:
             state.index_fill_(0, idx, 0)
 
+    def save_state(self) -> list[torch.Tensor]:
+        """Copies of all state tensors (the runner takes them around the trial runs of a graph
+        capture, which must leave no trace: a stateful mixer's step is not idempotent)."""
+        return [state.clone() for state in self._state_tensors()]
+
+    def restore_state(self, saved: list[torch.Tensor]) -> None:
+        for state, old in zip(self._state_tensors(), saved):
+            state.copy_(old)
+
     def copy_state(self, pairs) -> None:
         """state[dst] = state[src] for each (src, dst), in order (a forked request starts from
         its parent's state)."""

@@ -1,5 +1,6 @@
 from .engine import EngineConfig
-from .model import ConfigError, LlamaConfig, ModelConfig, RopeScaling
+from .llama import LlamaConfig, RopeScaling
+from .model import ConfigError, ModelConfig
 from .registry import ARCHITECTURES, Architecture, parse_model_config, register_architecture, resolve_architecture
 from .sampling import SamplingParams
 

@@ -48,7 +48,7 @@ def parse_model_config(hf_config: dict) -> tuple[Architecture, ModelConfig]:
 
 def _register_builtin() -> None:
     from ..models.llama import llama_spec
-    from .model import LlamaConfig
+    from .llama import LlamaConfig
     if "LlamaForCausalLM" not in ARCHITECTURES:
         register_architecture("LlamaForCausalLM", LlamaConfig, llama_spec)
 

@@ -61,18 +61,22 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int DPAD, int MW, int NW, int KPW>
+template <int DPAD, int MW, int NW, int KPW, int STAGES = 2>
 struct AttnShape {
     static constexpr int BM = 16 * MW, BN = KPW * NW, PITCH = DPAD + 8, THREADS = 32 * MW * NW;
-    static constexpr int SMEM_BYTES = (BM + 4 * BN) * PITCH * 2;
+    static constexpr int Q_BYTES = BM * PITCH * 2;                                // Q tile
+    static constexpr int SMEM_BYTES = Q_BYTES + 2 * STAGES * BN * PITCH * 2;      // then K and V stages
 };
 
 // CLUSTER: the blocks of a thread-block cluster take the splits of one (request, kv head) and
 // merge their partial results through distributed shared memory: no partials in global memory,
 // no counter, no work list.
-template <int DPAD, int MW, int NW, int KPW, bool CLUSTER = false>
+// MOD: the score modifiers of AttnParams (cap, bias by distance) are applied; the kernel without
+// them is the one the Llama decoder runs and carries none of their code.
+// STAGES: key tiles in flight (a ring of that many K and V stages).
+template <int DPAD, int MW, int NW, int KPW, bool CLUSTER = false, bool MOD = false, int STAGES = 2>
 __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
-    using Shape = AttnShape<DPAD, MW, NW, KPW>;
+    using Shape = AttnShape<DPAD, MW, NW, KPW, STAGES>;
     constexpr int BM = Shape::BM, BN = Shape::BN, PITCH = Shape::PITCH, THREADS = Shape::THREADS;
     constexpr int CH = DPAD / 8;                          // 16-byte chunks per row
     constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
@@ -90,8 +94,8 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
 
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-    __nv_bfloat16* Ks = Qs + BM * PITCH;                   // [2][BN][PITCH]
-    __nv_bfloat16* Vs = Ks + 2 * BN * PITCH;               // [2][BN][PITCH]
+    __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_raw + Shape::Q_BYTES);     // [STAGES][BN][PITCH]
+    __nv_bfloat16* Vs = Ks + STAGES * BN * PITCH;                                          // [STAGES][BN][PITCH]
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wm = warp % MW, wn = warp / MW;
@@ -138,12 +142,12 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
     const int g = lane >> 2, t4 = lane & 3;
     int pos[2];
     float slope[2];
-    const bool modified = p.softcap > 0.f || p.slopes != nullptr;     // score modifiers (off for the Llama decoder)
+    constexpr bool modified = MOD;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int R = it.row_base + wm * 16 + g + 8 * h;
         pos[h] = R < it.rows_total ? it.lk - it.nq + R / G : -1;
-        slope[h] = p.slopes != nullptr && R < it.rows_total ? p.slopes[kvh * G + R % G] : 0.f;
+        slope[h] = MOD && p.slopes != nullptr && R < it.rows_total ? p.slopes[kvh * G + R % G] : 0.f;
     }
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     float oacc[DPAD / 8][4];
@@ -160,6 +164,7 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
     // that the loop waits for together with the tile.
     const int own_lo = CLUSTER ? it.lk - it.nq : 0x7fffffff;
     if (n_tiles > 0) load_tile(0, it.key_lo, own_lo);
+    else cp_async_commit();
     if (CLUSTER) {
         pdl_wait();
         const int new_lo = max(own_lo, it.key_lo), new_hi = min(it.key_hi, it.key_lo + BN);
@@ -178,6 +183,13 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
         }
         cp_async_commit();
     }
+    // the tiles behind the first, up to the depth of the ring; every position of the sequence of
+    // copy groups is committed (empty if there is no such tile), so that the waits below can count
+#pragma unroll
+    for (int t = 1; t < STAGES - 1; ++t) {
+        if (t < n_tiles) load_tile(t, it.key_lo + t * BN);
+        else cp_async_commit();
+    }
     for (int e = tid; e < BM * CH; e += THREADS) {
         const int r = e / CH, c8 = e - r * CH;
         const int R = it.row_base + r;
@@ -187,15 +199,15 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
         *reinterpret_cast<uint4*>(Qs + r * PITCH + c8 * 8) = v;
     }
     for (int t = 0; t < n_tiles; ++t) {
-        if (t + 1 < n_tiles) {
-            load_tile((t + 1) & 1, it.key_lo + (t + 1) * BN);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
+        // tile t + STAGES - 1 goes into the stage that tile t - 1 left (all warps are past it: the
+        // barrier at the end of the iteration before); then all copies but those of the STAGES - 1
+        // newest groups are awaited, which completes tile t (and the step's own keys)
+        if (t + STAGES - 1 < n_tiles) load_tile((t + STAGES - 1) % STAGES, it.key_lo + (t + STAGES - 1) * BN);
+        else cp_async_commit();
+        cp_async_wait<STAGES - 1>();
         __syncthreads();
-        const __nv_bfloat16* kst = Ks + (t & 1) * BN * PITCH + wn * KPW * PITCH;
-        const __nv_bfloat16* vst = Vs + (t & 1) * BN * PITCH + wn * KPW * PITCH;
+        const __nv_bfloat16* kst = Ks + (t % STAGES) * BN * PITCH + wn * KPW * PITCH;
+        const __nv_bfloat16* vst = Vs + (t % STAGES) * BN * PITCH + wn * KPW * PITCH;
         const int kbase = it.key_lo + t * BN + wn * KPW;
         if (kbase < it.key_hi) {                               // uniform per warp
             float sacc[KPW / 8][4];
@@ -296,7 +308,7 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
         l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
     }
     float* red_ml = reinterpret_cast<float*>(smem_raw);                     // [NW][BM][2] in the Q region
-    float* red_o = reinterpret_cast<float*>(smem_raw + BM * PITCH * 2);     // [NW][BM][DPAD] in the K/V region
+    float* red_o = reinterpret_cast<float*>(smem_raw + Shape::Q_BYTES);     // [NW][BM][DPAD] in the K/V region
     float* cpart = red_o + (size_t)NW * BM * DPAD;                          // [BM][DPAD + 2]: this block's partial (CLUSTER)
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -450,31 +462,30 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
     if (tid == 0) p.counters[(size_t)it.seq * p.nkv + kvh] = 0u;      // ready for the next launch
 }
 
-template <int DPAD, int MW, int NW, int KPW>
+template <int DPAD, int MW, int NW, int KPW, bool MOD = false, int STAGES = 2>
 int launch_attn_bf16(const AttnParams& p, cudaStream_t stream) {
-    using Shape = AttnShape<DPAD, MW, NW, KPW>;
+    using Shape = AttnShape<DPAD, MW, NW, KPW, STAGES>;
+    auto kernel = attn_bf16_kernel<DPAD, MW, NW, KPW, false, MOD, STAGES>;
     static bool attr_set[kAttnMaxDevices] = {};         // function attributes are per device
     int dev = 0;
     PL_CUDA(cudaGetDevice(&dev));
     PL_REQUIRE(dev >= 0 && dev < kAttnMaxDevices, "attention_bf16: device index %d is out of range", dev);
     if (!attr_set[dev]) {
-        PL_CUDA(cudaFuncSetAttribute(attn_bf16_kernel<DPAD, MW, NW, KPW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     Shape::SMEM_BYTES));
+        PL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape::SMEM_BYTES));
         attr_set[dev] = true;
     }
-    PL_CUDA(launch_pdl(attn_bf16_kernel<DPAD, MW, NW, KPW>, dim3(p.n_work * p.nkv), dim3(Shape::THREADS),
-                       (size_t)Shape::SMEM_BYTES, stream, p));
+    PL_CUDA(launch_pdl(kernel, dim3(p.n_work * p.nkv), dim3(Shape::THREADS), (size_t)Shape::SMEM_BYTES, stream, p));
     return 0;
 }
 
 // The cluster form of the small shape: p.n_work requests, p.cluster blocks per (request, kv head).
-template <int DPAD, int KPW>
+template <int DPAD, int KPW, bool MOD = false, int STAGES = 2>
 int launch_attn_cluster(const AttnParams& p, cudaStream_t stream) {
-    using Shape = AttnShape<DPAD, 1, 4, KPW>;
-    constexpr size_t smem = Shape::SMEM_BYTES > (Shape::BM * Shape::PITCH * 2 + 4 * Shape::BM * DPAD * 4)
-                                ? Shape::SMEM_BYTES + Shape::BM * (DPAD + 2) * 4
-                                : Shape::BM * Shape::PITCH * 2 + 4 * Shape::BM * DPAD * 4 + Shape::BM * (DPAD + 2) * 4;
-    auto kernel = attn_bf16_kernel<DPAD, 1, 4, KPW, true>;
+    using Shape = AttnShape<DPAD, 1, 4, KPW, STAGES>;
+    // the merge of the warps reuses the K/V stages ([4][BM][DPAD] float32); behind it, this block's partial
+    constexpr size_t merge = (size_t)Shape::Q_BYTES + 4 * Shape::BM * DPAD * 4;
+    constexpr size_t smem = (Shape::SMEM_BYTES > merge ? Shape::SMEM_BYTES : merge) + Shape::BM * (DPAD + 2) * 4;
+    auto kernel = attn_bf16_kernel<DPAD, 1, 4, KPW, true, MOD, STAGES>;
     static bool attr_set[kAttnMaxDevices] = {};
     int dev = 0;
     PL_CUDA(cudaGetDevice(&dev));
@@ -532,14 +543,28 @@ PL_EXPORT int PL_CAT(pl_attention_bf16_d, PL_DPAD)(const AttnParams* params, cud
     PL_REQUIRE(p.q_stride % 8 == 0 && p.out_stride % 2 == 0, "attention_bf16: row strides must keep 16-byte alignment");
     PL_REQUIRE(((uintptr_t)p.q & 15) == 0 && ((uintptr_t)p.kv & 15) == 0, "attention_bf16: q and kv must be 16-byte aligned");
     PL_REQUIRE(p.softcap >= 0.f, "attention_bf16: softcap=%f must not be negative", (double)p.softcap);
-    constexpr int KPW_SMALL = PL_DPAD <= 128 ? 32 : 16;
-    if (p.cluster > 0) return launch_attn_cluster<PL_DPAD, KPW_SMALL>(p, stream);
-    if (p.is_small) return launch_attn_bf16<PL_DPAD, 1, 4, KPW_SMALL>(p, stream);
+    // Shapes of the decode kernel, by measurement (B200; bytes in flight per SM are what counts, so the
+    // shared memory a block takes decides): head sizes up to 64 walk 128 keys per tile, but 64 keys in
+    // a ring of three tiles where the work list says that the ranges are long (is_small == 2: three
+    // blocks per SM, 18 against 26 us at 8 requests x 4,096 keys); head size 128 walks 64 keys per tile
+    // in all forms (three blocks per SM instead of one: 1.7 times the speed); head size 256 keeps 64
+    // keys and two stages, which is what fits.
+    constexpr int KPW_CLUSTER = PL_DPAD <= 64 ? 32 : 16;
+    if (p.softcap > 0.f || p.slopes != nullptr) {
+        // the score modifiers live in instantiations of their own of the mma.sync kernel (the tcgen05
+        // kernels step aside for them)
+        if (p.cluster > 0) return launch_attn_cluster<PL_DPAD, KPW_CLUSTER, true>(p, stream);
+        if (p.is_small) return launch_attn_bf16<PL_DPAD, 1, 4, KPW_CLUSTER, true>(p, stream);
+        return launch_attn_bf16<PL_DPAD, PL_LARGE_MW, 1, 64, true>(p, stream);
+    }
+    if (p.cluster > 0) return launch_attn_cluster<PL_DPAD, KPW_CLUSTER>(p, stream);
+#if PL_DPAD <= 64
+    if (p.is_small == 2) return launch_attn_bf16<PL_DPAD, 1, 4, 16, false, 3>(p, stream);
+#endif
+    if (p.is_small) return launch_attn_bf16<PL_DPAD, 1, 4, KPW_CLUSTER>(p, stream);
 #if PL_DPAD == 64 || PL_DPAD == 128
     // prefill tiles of head sizes 64 and 128 run on tcgen05 with tensor-memory accumulators
-    // (the score modifiers live in the mma.sync kernel only; the tcgen05 kernels step aside for them)
-    static const bool no_tc_env = getenv("PAGED_LLM_B200_NO_TCGEN05") != nullptr;
-    const bool no_tc = no_tc_env || p.softcap > 0.f || p.slopes != nullptr;
+    static const bool no_tc = getenv("PAGED_LLM_B200_NO_TCGEN05") != nullptr;
 #if PL_DPAD == 64
     static const bool serial_tc = getenv("PAGED_LLM_B200_TC_SERIAL") != nullptr;     // the block-synchronous variant
     if (p.d == 64 && !no_tc) return serial_tc || !tc2::takes(p) ? tc::launch(p, stream) : tc2::launch<64>(p, stream);

@@ -28,10 +28,13 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",
 ]
 
+# extra nvcc flags for experiments (e.g. -DNAME): part of the hash, so such a build never replaces the regular one
+NVCC_FLAGS += os.environ.get("PAGED_LLM_B200_NVCC_FLAGS", "").split()
+
 HEAD_DIM_BUILDS = (16, 32, 64, 128, 256)
 
 MODULES: dict[str, list[str]] = {
-    "core": ["common.cu", "elementwise.cu", "gemm_f32.cu", "gemm_skinny.cu", "gemm_stream_tc.cu", "gemm_tc.cu", "attention_f32.cu",
+    "core": ["common.cu", "elementwise.cu", "gemm_f32.cu", "gemm_skinny.cu", "gemm_tc.cu", "attention_f32.cu",
              "sampling.cu"],
     **{f"attn_bf16_d{d}": ["common.cu", f"attention_bf16_d{d}.cu"] for d in HEAD_DIM_BUILDS},
     # the many-token tcgen05 product with blocks in pairs that share W tiles (optional: the package runs without

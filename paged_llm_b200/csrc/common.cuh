@@ -109,6 +109,7 @@ struct AttnParams {
     int nh, nkv, d, ps;
     int window;             // 0: none
     int is_small;           // items are (request, scratch base, split, splits), one tile per request
+                            // (2: the same, and the items' key ranges are long: see the dispatch of the kernels)
     float scale;
     int ps_shift;           // log2(ps) if ps is a power of two, else -1
     unsigned int* counters; // [requests * kv_heads] zeros, or null: the block of a request's kv head that

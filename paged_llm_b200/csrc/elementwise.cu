@@ -476,3 +476,49 @@ PL_EXPORT int pl_copy_page(void* pool, int layers, long long pages, long long pa
     PL_LAUNCHED("copy_page");
     return 0;
 }
+
+// ------------------------------------------------------------------ random weights on the device
+// out[i] = mean + std * z_i with z ~ N(0, 1) from a counter-based stream: the pair of elements
+// (2j, 2j + 1) comes from one 64-bit hash of (seed, tensor key, j) through the Box-Muller transform,
+// so a tensor's values depend only on (seed, key, its size), never on the launch shape.  For
+// benchmark models too large to draw on the host; the reference has no such mode.
+__device__ __forceinline__ uint64_t fill_hash(uint64_t seed, uint64_t key, uint64_t j) {
+    uint64_t x = seed + key * 0x9E3779B97F4A7C15ull + j * 0xBF58476D1CE4E5B9ull;
+    x ^= x >> 30;
+    x *= 0xBF58476D1CE4E5B9ull;
+    x ^= x >> 27;
+    x *= 0x94D049BB133111EBull;
+    x ^= x >> 31;
+    return x;
+}
+
+template <typename T>
+__global__ void fill_normal_kernel(T* __restrict__ out, long long n, uint64_t seed, uint64_t key, float mean, float std) {
+    const long long pairs = (n + 1) / 2;
+    for (long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x; j < pairs; j += (long long)gridDim.x * blockDim.x) {
+        const uint64_t x = fill_hash(seed, key, (uint64_t)j);
+        const float u1 = ((float)(x >> 40) + 0.5f) * (1.0f / 16777216.0f);            // (0, 1)
+        const float u2 = ((float)((x >> 16) & 0xFFFFFFull) + 0.5f) * (1.0f / 16777216.0f);
+        const float r = sqrtf(-2.0f * logf(u1));
+        float s, c;
+        sincosf(6.283185307179586f * u2, &s, &c);
+        out[2 * j] = from_float<T>(mean + std * r * c);
+        if (2 * j + 1 < n) out[2 * j + 1] = from_float<T>(mean + std * r * s);
+    }
+}
+
+PL_EXPORT int pl_fill_normal(void* out, int dtype, long long n, unsigned long long seed, unsigned long long key,
+                             float mean, float std, cudaStream_t stream) {
+    PL_REQUIRE(n >= 0 && std >= 0.f, "fill_normal: n=%lld std=%f", n, (double)std);
+    if (n == 0) return 0;
+    const long long pairs = (n + 1) / 2;
+    const int blocks = (int)((pairs + 255) / 256 < 148 * 16 ? (pairs + 255) / 256 : 148 * 16);
+    if (dtype == PL_F32)
+        fill_normal_kernel<float><<<blocks, 256, 0, stream>>>((float*)out, n, seed, key, mean, std);
+    else if (dtype == PL_BF16)
+        fill_normal_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)out, n, seed, key, mean, std);
+    else
+        return pl_fail("fill_normal: unknown dtype %d", dtype);
+    PL_LAUNCHED("fill_normal");
+    return 0;
+}

@@ -101,7 +101,7 @@ class LLMEngine:
         self.tokenizer = _load_tokenizer(model)
         hf_config = read_hf_config(model)
         t0 = time.perf_counter()
-        self.model, self.model_config, self.dtype = load_model(model, cfg.dtype, self.device)
+        self.model, self.model_config, self.dtype = load_model(model, cfg.dtype, self.device, ops=ops)
         ops.set_compute_dtype(self.dtype)
         self.model.prepare(cfg.max_model_len, self.device, ops)
         log.info("loaded %s in %.1fs (dtype=%s)", model, time.perf_counter() - t0, self.dtype)

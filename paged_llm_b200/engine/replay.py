@@ -48,7 +48,7 @@ class TraceReplayer:
             from ..kernels.ops import CudaOps
             ops = CudaOps(self.device)
         self.ops = ops
-        self.model, self.model_config, self.dtype = load_model(model_dir, dtype, self.device)
+        self.model, self.model_config, self.dtype = load_model(model_dir, dtype, self.device, ops=ops)
         ops.set_compute_dtype(self.dtype)
         num_pages = max(1, -(-int(max_tokens) // block_size))
         max_len = num_pages * block_size

@@ -437,18 +437,22 @@ class ModelRunner:
         dev = torch.empty(pk.size, dtype=torch.int32, device=self.device)
         self._upload(pk, dev)
         ctx = self._context(pk, dev, host, info)
+        # The trial runs write this step's keys and values (the replay writes the same again) but must
+        # leave state of fixed size as it was: a stateful mixer's step is not idempotent.
+        saved_state = self.storage.save_state() if self.cm.num_state_slots else None
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             for _ in range(2):                       # warm-up: library workspaces, lazy module loads
                 self.model.forward(ctx)
         torch.cuda.current_stream().wait_stream(side)
+        if saved_state is not None:
+            self.storage.restore_state(saved_state)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         before = getattr(self.ops, "launches", 0)
         # No garbage collection while the stream captures: collecting an older engine's graphs then
         # (their destructors free device memory) is not permitted during a capture and would invalidate it.
-        gc.collect()
         gc_was_on = gc.isenabled()
         gc.disable()
         try:

@@ -80,7 +80,8 @@ class Scheduler:
         if n >= cfg.max_model_len:
             raise ValueError(f"prompt has {n} tokens, max_model_len={cfg.max_model_len}")
         if not cfg.enable_chunked_prefill and n > cfg.max_num_batched_tokens:
-            raise ValueError("prompt longer than max_num_batched_tokens; enable chunked prefill")
+            raise ValueError(f"prompt of {n} tokens exceeds max_num_batched_tokens={cfg.max_num_batched_tokens} and "
+                             "chunked prefill is off")
         seq.max_tokens = seq.sampling_params.max_tokens
         if n + seq.max_tokens > cfg.max_model_len:
             seq.max_tokens = max(1, cfg.max_model_len - n)
@@ -209,6 +210,17 @@ class Scheduler:
                 seq.append_token(self.PLACEHOLDER)
                 seq.num_unresolved += 1
 
+    def _status_after(self, seq: Sequence, token: int, known: int) -> SequenceStatus | None:
+        """The finished status a request takes once `token` is its newest of `known` known tokens,
+        or None if it goes on: a stop token or (unless ignored) the end-of-sequence token stops it,
+        its own token limit or the model's length limit ends it."""
+        sp = seq.sampling_params
+        if token in sp.stop_token_ids or (token == self.eos_token_id and not sp.ignore_eos):
+            return SequenceStatus.FINISHED_STOPPED
+        if known - seq.num_prompt_tokens >= seq.max_tokens or known >= self.config.max_model_len:
+            return SequenceStatus.FINISHED_LENGTH
+        return None
+
     def resolve(self, out: SchedulerOutput, sampled: dict[int, int]) -> list[Sequence]:
         """The step's tokens are known: they take their places, pages that are full of
         known tokens get their hashes, finished requests are retired.  A request that
@@ -224,14 +236,8 @@ class Scheduler:
                 seq.num_unresolved -= 1
             known = seq.num_tokens - seq.num_unresolved
             self.bm.cache_full_blocks(seq, 0, min(seq.num_computed_tokens, known))
-            if not item.needs_sampling:
-                continue
-            sp = seq.sampling_params
-            generated = known - seq.num_prompt_tokens
-            if (not sp.ignore_eos and token == self.eos_token_id) or token in sp.stop_token_ids:
-                seq.status = SequenceStatus.FINISHED_STOPPED
-            elif generated >= seq.max_tokens or known >= self.config.max_model_len:
-                seq.status = SequenceStatus.FINISHED_LENGTH
+            if item.needs_sampling:
+                seq.status = self._status_after(seq, token, known) or seq.status
             if seq.is_finished:
                 if seq.num_unresolved:                     # places of a step that ran ahead in vain
                     del seq.token_ids[known:]

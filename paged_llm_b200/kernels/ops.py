@@ -104,9 +104,6 @@ class CudaOps:
         self._attn_fn = None
         self.launches = 0                 # kernels of this package launched so far
         self.use_skinny = True            # few-token products on this package's weight-streaming kernel
-        # 17..128 tokens: this package's tcgen05 kernel with cluster split-K.  Off unless asked for
-        # (PAGED_LLM_B200_STREAM_TC=1): measured at 1.5 to 2.5 times the library product's time.
-        self.use_stream_tc = os.environ.get("PAGED_LLM_B200_STREAM_TC") is not None
         # Many tokens: this package's tcgen05 kernel (128 x 256 tiles, fused epilogues) where it is at least
         # as fast as the library product followed by the elementwise kernel.  Measured: the gate/up product
         # with SiLU-mul from 2,048 tokens on (78 us against 80 us); the narrower products and fewer tokens are
@@ -175,6 +172,17 @@ class CudaOps:
         """Asynchronous copy of `nbytes` from pinned host memory to the device on the current stream."""
         _check(self.core, self.core.pl_copy_h2d(self._p(dst), self._p(src), c_longlong(nbytes), self._stream))
 
+    def fill_normal(self, out: torch.Tensor, seed: int, key: int, mean: float = 0.0, std: float = 1.0) -> torch.Tensor:
+        """out[...] = mean + std * N(0, 1) from the counter-based stream (seed, key): the values depend
+        on nothing else.  For random weights drawn on the device."""
+        assert out.is_contiguous() and out.is_cuda
+        _check(self.core, self.core.pl_fill_normal(self._p(out), self._code(out), c_longlong(out.numel()),
+                                                   ctypes.c_ulonglong(seed & (2 ** 64 - 1)),
+                                                   ctypes.c_ulonglong(key & (2 ** 64 - 1)), c_float(mean), c_float(std),
+                                                   self._stream))
+        self.launches += 1
+        return out
+
     # ---- embedding, norms, activation ------------------------------------------
     def embedding(self, table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
         T, (V, H) = ids.numel(), table.shape
@@ -238,13 +246,6 @@ class CudaOps:
         M, K = h.shape
         return self.use_skinny and h.dtype == torch.bfloat16 and 1 <= M <= 16 and K >= 32 and K % 32 == 0
 
-    def _stream_ok(self, h, w: torch.Tensor) -> bool:
-        """17 to 128 tokens in bfloat16: this package's tcgen05 weight-streaming kernel instead
-        of the library."""
-        M, K = h.shape
-        return (self.use_stream_tc and h.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 16 < M <= 128
-                and K >= 64 and K % 64 == 0 and w.is_contiguous())
-
     def _gemm_tc_ok(self, h, w: torch.Tensor, kind: str) -> bool:
         M, K = h.shape
         return (kind in self.gemm_tc_for and h.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
@@ -263,14 +264,6 @@ class CudaOps:
                        self._p(resid), M, N, K, epi, self._stream))
         self.launches += 1
 
-    def _stream_tc(self, h: torch.Tensor, w: torch.Tensor, out, resid, N: int, epi: int) -> None:
-        M, K = h.shape
-        assert h.stride(1) == 1 and h.stride(0) % 8 == 0
-        _check(self.core, self.core.pl_gemm_stream_tc(
-            self._p(h), h.stride(0), self._p(w), self._p(out), out.shape[1] if out is not None else 0,
-            self._p(resid), M, N, K, epi, self._stream))
-        self.launches += 1
-
     def linear(self, h, w: torch.Tensor, out_float32: bool = False) -> torch.Tensor:
         """h [M, K] @ w[N, K]^T.  float32: this package's CUDA-core kernel; bfloat16 with few
         tokens: this package's weight-streaming kernel; else the library product with
@@ -287,10 +280,6 @@ class CudaOps:
             return out
         h = self.materialize(h)
         assert h.is_contiguous()
-        if self._stream_ok(h, w):
-            out = torch.empty((M, N), dtype=torch.float32 if out_float32 else torch.bfloat16, device=self.device)
-            self._stream_tc(h, w, out, None, N, 1 if out_float32 else 0)
-            return out
         if self._gemm_tc_ok(h, w, "plain") and N % 8 == 0:
             out = torch.empty((M, N), dtype=torch.float32 if out_float32 else torch.bfloat16, device=self.device)
             self._gemm_tc(h, w, out, None, N, 1 if out_float32 else 0)
@@ -322,9 +311,6 @@ class CudaOps:
                                                            self._p(self._norm_part), self._stream))
             self.launches += 1
             return LazyNorm(x, self._norm_part, norm_w, eps)
-        if not isinstance(h, LazyNorm) and self._stream_ok(h, w) and x.dtype == torch.float32 and x.is_contiguous():
-            self._stream_tc(h, w, None, x, N, 3)                  # the product's epilogue adds to the stream
-            return self.rms_norm(x, norm_w, eps)
         if (not isinstance(h, LazyNorm) and self._gemm_tc_ok(h, w, "add") and x.dtype == torch.float32
                 and x.is_contiguous() and N % 4 == 0):
             self._gemm_tc(h, w, None, x, N, 3)
@@ -344,10 +330,6 @@ class CudaOps:
             self.launches += 1
             return out
         h = self.materialize(h)
-        if self._stream_ok(h, w_gate_up) and h.is_contiguous():
-            out = torch.empty((M, I), dtype=torch.bfloat16, device=self.device)
-            self._stream_tc(h, w_gate_up, out, None, I, 2)
-            return out
         if self._gemm_tc_ok(h, w_gate_up, "silu") and h.is_contiguous() and I % 8 == 0:
             out = torch.empty((M, I), dtype=torch.bfloat16, device=self.device)
             self._gemm_tc(h, w_gate_up, out, None, I, 2)
@@ -482,7 +464,7 @@ class CudaOps:
             floats = max(plan.small_tokens, 1) * nh * plan.max_splits * (d + 2)
             scratch = self._scratch_for(floats)
             p.scratch, p.scratch_floats = scratch.data_ptr(), scratch.numel()
-            p.work, p.n_work, p.is_small = plan.small.data_ptr(), plan.n_small, 1
+            p.work, p.n_work, p.is_small = plan.small.data_ptr(), plan.n_small, 2 if plan.long_context else 1
             fused_merge = bf16 and plan.max_splits > 1
             if fused_merge:
                 need = ctx.num_seqs * nkv

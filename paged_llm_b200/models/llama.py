@@ -8,7 +8,7 @@ the schedule runs the layers once each, in order.
 
 from __future__ import annotations
 
-from ..config.model import LlamaConfig
+from ..config.llama import LlamaConfig
 from ..parts.base import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 
 

@@ -146,15 +146,27 @@ def check_and_cast(expected: dict[str, TensorSpec], tensors: dict[str, torch.Ten
     return out
 
 
-def load_model(path: str, dtype: str = "auto", device="cuda"):
-    """Folder -> (model with weights on `device`, typed config, compute dtype)."""
+def load_model(path: str, dtype: str = "auto", device="cuda", ops=None):
+    """Folder -> (model with weights on `device`, typed config, compute dtype).  A folder that
+    holds `random_weights.json` instead of tensors (weights/random_init.py: `write_random_stub`)
+    gets its weights drawn on the device by `ops`, the kernel library."""
     from ..models.causal_lm import build_model
+    from .random_init import draw_on_device, read_random_stub
 
     hf_config = read_hf_config(path)
     arch, config = parse_model_config(hf_config)
     compute = resolve_dtype(dtype, hf_config)
     spec = arch.build_spec(config)
     model = build_model(spec)
+    stub = read_random_stub(path)
+    if stub is not None:
+        if glob.glob(os.path.join(path, "*.safetensors")):
+            raise ValueError(f"{path!r} holds both random_weights.json and *.safetensors files; remove one")
+        if ops is None or not hasattr(ops, "fill_normal"):
+            raise ValueError(f"{path!r} holds random_weights.json: its weights are drawn on the device, which needs "
+                             "the kernel library (pass ops)")
+        model.load(draw_on_device(model.tensor_specs(), stub, compute, device, ops))
+        return model, config, compute
     tensors, duplicates = read_safetensors(path)
     cast = check_and_cast(model.tensor_specs(), tensors, compute, device, spec.ignored_tensors, duplicates)
     model.load(cast)

@@ -387,3 +387,52 @@ def test_tiny_b_workload_preempts_and_hits_the_prefix_cache(folders):
             scores = gumbel_scores(plain_llama.forward_logits(cfg, w, seq)[-1].numpy(), 0.7, -1, 1.0, sp.seed, len(seq))
             assert scores.max() - scores[tok] < 1e-3
             seq.append(tok)
+
+
+def test_score_modifiers_reach_the_attention_part(tmp_path):
+    """The Llama with a bias by distance and a score cap (tests/toy_parts.py) on the host."""
+    from tests.toy_parts import biased_llama_case
+    hf, w, reqs, plain = biased_llama_case(tmp_path)
+    steps, max_tokens = schedules.mixed(reqs, live=3, seed=6)
+    rp = TraceReplayer(str(tmp_path), "float32", max_tokens, device="cpu", ops=TorchOps(), poison=float("nan"))
+    outputs = {rec["step"]: out for rec in steps if (out := rp.step(rec)) is not None}
+    got = schedules.collect(steps, outputs)
+    for rid, toks in reqs.items():
+        assert np.abs(got[rid] - plain(toks)).max() < 2e-5, rid
+    without = plain_llama.forward_logits(hf, w, reqs["a"]).numpy()
+    assert np.abs(without - plain(reqs["a"])).max() > 0.05 * np.abs(without).max(), "the modifiers must matter here"
+
+
+def test_fork_gives_the_child_a_copy_of_the_state(tmp_path):
+    """A model with state of fixed size: `fork` hands the child a slot of its own and queues a
+    copy of the parent's state, which the next step carries out before it runs."""
+    from paged_llm_b200.weights import write_model_folder
+    from tests.toy_parts import TOY, ToyConfig, plain_toy_logits
+    write_model_folder(str(tmp_path), ToyConfig.from_hf_dict(TOY), seed=4, std=0.1, norm_std=0.05)
+    cfg, w = read_folder(tmp_path)
+    eng = LLMEngine(str(tmp_path), ops=TorchOps(), dtype="float32", device="cpu", block_size=8, num_gpu_blocks=32,
+                    max_model_len=128, max_num_seqs=4)
+    sched, cm, runner = eng.scheduler, eng.block_manager, eng.runner
+    base = random_tokens(61, 21, 3)
+    root = Sequence(base, SamplingParams(temperature=0.0, max_tokens=50, ignore_eos=True))
+    sched.add(root)
+    out = sched.schedule(); sched.update(out, runner.run(out))
+    child = Sequence(base, SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True))
+    cm.fork(root, child)
+    assert child.state_slot is not None and child.state_slot != root.state_slot
+    child.token_ids = base + [7]
+    child.status = root.status
+    sched.running.append(child)
+    while sched.has_unfinished and not child.is_finished:
+        out = sched.schedule(); sched.update(out, runner.run(out))
+    toks = base + [7]
+    for tok in child.output_token_ids[1:]:
+        assert tok == int(plain_toy_logits(cfg, w, toks)[-1].argmax())
+        toks.append(tok)
+    # the parent went on from its own state, untouched by the child
+    toks = list(base)
+    for tok in root.output_token_ids[:5]:
+        assert tok == int(plain_toy_logits(cfg, w, toks)[-1].argmax())
+        toks.append(tok)
+    sched.abort(root.seq_id)
+    assert cm.num_free_state_slots == cm.num_state_slots and cm.num_free_blocks == 32

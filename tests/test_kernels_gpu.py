@@ -105,6 +105,47 @@ def test_rope_table_matches_float32_angles(ops):
     torch.testing.assert_close(table[..., 1], sin[:, :24], atol=2e-6, rtol=0)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_fill_normal_on_the_device(ops, dtype):
+    """Random weights drawn on the device: N(mean, std) from a counter-based stream that depends
+    on (seed, key) alone: the same again on a second call, a prefix of itself at another size,
+    other values for another key or seed."""
+    n = 1_000_003                                                   # odd: the last pair is half used
+    a = ops.fill_normal(torch.empty(n, dtype=dtype, device="cuda"), 7, 11, 0.5, 0.02).float()
+    assert abs(float(a.mean()) - 0.5) < 2e-4 and abs(float(a.std()) - 0.02) < 2e-4
+    z = (a - 0.5) / 0.02
+    assert abs(float((z ** 3).mean())) < 0.02 and abs(float((z ** 4).mean()) - 3.0) < 0.1      # skewness, kurtosis
+    assert float(z.abs().max()) < 6.0
+    again = ops.fill_normal(torch.empty(n, dtype=dtype, device="cuda"), 7, 11, 0.5, 0.02).float()
+    assert torch.equal(a, again)
+    shorter = ops.fill_normal(torch.empty(1000, dtype=dtype, device="cuda"), 7, 11, 0.5, 0.02).float()
+    assert torch.equal(shorter, a[:1000])
+    for seed, key in ((8, 11), (7, 12)):
+        other = ops.fill_normal(torch.empty(1000, dtype=dtype, device="cuda"), seed, key, 0.5, 0.02).float()
+        assert not torch.equal(other, a[:1000])
+        assert abs(float(torch.corrcoef(torch.stack([other, a[:1000]]))[0, 1])) < 0.15
+
+
+def test_model_from_a_random_stub(ops, tmp_path):
+    """A folder without tensors (config.json + random_weights.json): the engine draws the weights on
+    the device, the same for the same stub, and generates with them."""
+    from paged_llm_b200 import LLMEngine, SamplingParams
+    from paged_llm_b200.config import LlamaConfig
+    from paged_llm_b200.weights import write_random_stub
+    from tests.tiny import TINY_B
+    d = write_random_stub(str(tmp_path), LlamaConfig.from_hf_dict(TINY_B), seed=3, std=0.05, norm_std=0.1)
+    outs = []
+    for _ in range(2):
+        eng = LLMEngine(d, dtype="bfloat16", block_size=8, num_gpu_blocks=32, max_model_len=128)
+        w = eng.model.blocks[0].mixer.w_qkv.float()
+        assert w.dtype == torch.float32 and abs(float(w.std()) - 0.05) < 2e-3 and abs(float(w.mean())) < 2e-3
+        assert eng.model.head.weight is eng.model.embedding.weight            # tied, as the configuration says
+        nw = eng.model.final_norm.weight
+        assert nw.dtype == torch.float32 and abs(float(nw.mean()) - 1.0) < 0.05 and 0.05 < float(nw.std()) < 0.15
+        outs.append(eng.generate([[1, 2, 3, 4]], SamplingParams(temperature=0.0, max_tokens=6))[0].token_ids)
+    assert outs[0] == outs[1] and len(outs[0]) == 6
+
+
 # ---------------------------------------------------------------------------- paged pieces
 
 def paged_case(q_lens, k_lens, nh, nkv, d, ps, dtype, seed=0, spare=3):
@@ -251,6 +292,43 @@ def test_paged_attention_window(ops, dtype, window, nh, nkv, d):
         qs[L - nq:] = q[cu[s]:cu[s + 1]].float()
         want = plain_llama.causal_attention(qs, keys[s], vals[s], 0.3, window=window)[L - nq:].reshape(nq, nh * d)
         torch.testing.assert_close(out[cu[s]:cu[s + 1]], want, atol=tol(dtype), rtol=tol(dtype), msg=f"request {s}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,d", [(32, 4, 64), (6, 3, 128), (4, 2, 16)])
+@pytest.mark.parametrize("softcap,sloped", [(None, True), (1.5, False), (0.7, True)])
+def test_paged_attention_with_score_modifiers(ops, dtype, nh, nkv, d, softcap, sloped):
+    """The two score modifiers of the attention part (a cap c * tanh(s / c) and a per-head bias
+    slope * (key position - query position)) against the plain formulation, for prompt portions
+    (head sizes 64 and 128 leave the tcgen05 kernel for them), decode clusters and work-list splits."""
+    ops.set_compute_dtype(dtype)
+    ps = 16
+    q_lens, k_lens = [150, 1, 2, 1, 40], [400, 700, 19, 3000, 40]
+    if max(q for q in q_lens if q <= 2) * (nh // nkv) > 16:
+        q_lens[2] = 1
+    q, kv, bt, keys, vals = paged_case(q_lens, k_lens, nh, nkv, d, ps, dtype, seed=11)
+    slopes = [2.0 ** -(1 + 8.0 * h / nh) for h in range(nh)] if sloped else None
+    dev_slopes = torch.tensor(slopes, dtype=torch.float32, device="cuda") if sloped else None
+    cu = [0]
+    for n in q_lens:
+        cu.append(cu[-1] + n)
+    qkv = torch.cat([q.reshape(-1, nh * d), torch.zeros(q.shape[0], 2 * nkv * d, dtype=dtype)], dim=1).cuda().contiguous()
+    # the whole mixed batch, then the decoding requests alone (so that they run as clusters in bfloat16)
+    for pick in (list(range(len(q_lens))), [1, 3]):
+        ql, kl = [q_lens[s] for s in pick], [k_lens[s] for s in pick]
+        ctx = make_ctx(ops, ql, kl, nh, nkv, None, d)
+        rows = torch.cat([torch.arange(cu[s], cu[s + 1]) for s in pick])
+        out = ops.paged_attention(qkv[rows.cuda()].contiguous(), nh, nkv, d, kv.cuda(), bt[pick].contiguous().cuda(), ctx,
+                                  d ** -0.5, None, softcap=softcap, slopes=dev_slopes).float().cpu()
+        o = 0
+        for s in pick:
+            nq, L = q_lens[s], k_lens[s]
+            qs = torch.zeros(L, nh, d)
+            qs[L - nq:] = q[cu[s]:cu[s + 1]].float()
+            want = plain_llama.causal_attention(qs, keys[s], vals[s], d ** -0.5, softcap=softcap,
+                                                slopes=slopes)[L - nq:].reshape(nq, nh * d)
+            torch.testing.assert_close(out[o:o + nq], want, atol=tol(dtype), rtol=tol(dtype), msg=f"request {s}")
+            o += nq
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -442,51 +520,6 @@ def test_skinny_gated_silu(ops, M, I, K):
     torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=2e-2)
 
 
-@pytest.mark.parametrize("M", [17, 32, 33, 64, 100, 128])
-@pytest.mark.parametrize("N,K", [(2048, 2048), (2560, 2048), (300, 128), (2048, 5632), (1000, 64), (129, 320)])
-def test_stream_tc_product(ops, M, N, K):
-    """17 to 128 tokens: the tcgen05 weight-streaming product with its epilogues (plain in both
-    output types, residual add, SiLU-gated) against float32 arithmetic on the same bfloat16 inputs."""
-    ops.set_compute_dtype(torch.bfloat16)
-    h = randn(M, K, seed=40 + M, dtype=torch.bfloat16)
-    w = randn(N, K, seed=41 + N, dtype=torch.bfloat16, std=K ** -0.5)
-    want = h.float() @ w.float().T
-    before = ops.launches
-    was, ops.use_stream_tc = ops.use_stream_tc, True         # the library product is the default at these sizes
-    try:
-        _stream_tc_checks(ops, h, w, want, before, M, N, K)
-    finally:
-        ops.use_stream_tc = was
-
-
-def _stream_tc_checks(ops, h, w, want, before, M, N, K):
-    got = ops.linear(h, w)
-    assert ops.launches == before + 1, "the product did not run on this package's kernel"
-    torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=2e-2)
-    got32 = ops.linear(h, w, out_float32=True)
-    assert got32.dtype == torch.float32
-    torch.testing.assert_close(got32, want, atol=2e-3, rtol=2e-3)
-    # a token's result does not depend on the other tokens of the batch
-    alone = ops.linear(h[:20].contiguous(), w, out_float32=True) if M > 20 else None
-    if alone is not None:
-        assert torch.equal(alone, got32[:20])
-    # residual add: x += bf16(h w^T), then the norm of the new x
-    x = randn(M, N, seed=42, dtype=torch.float32)
-    norm_w = randn(N, seed=43, dtype=torch.float32, std=0.1) + 1.0
-    x_new = x.clone()
-    normed = ops.linear_add_rms_norm(h, w, x_new, norm_w, 1e-5)
-    x_want = x + want.bfloat16().float()
-    torch.testing.assert_close(x_new, x_want, atol=2e-2, rtol=2e-2)
-    ref = x_new * torch.rsqrt(x_new.pow(2).mean(-1, keepdim=True) + 1e-5) * norm_w
-    torch.testing.assert_close(normed.float(), ref, atol=3e-2, rtol=3e-2)
-    if N % 2 == 0:
-        I = N // 2
-        act = ops.gated_silu_linear(h, w)
-        g, u = want[:, :I].bfloat16().float(), want[:, I:].bfloat16().float()
-        torch.testing.assert_close(act.float(), g * torch.sigmoid(g) * u, atol=3e-2, rtol=3e-2)
-    assert ops.core.pl_gemm_stream_tc_timeouts() == 0
-
-
 @pytest.mark.parametrize("pair", [True, False])
 @pytest.mark.parametrize("M", [129, 256, 300, 2048])
 @pytest.mark.parametrize("N,K", [(2048, 2048), (2560, 2048), (520, 128), (2048, 5632), (1000, 64), (11264, 2048)])
@@ -556,6 +589,57 @@ def test_skinny_qkv_rope_write_equals_the_separate_kernels(ops, nh, nkv, d, q_le
     torch.testing.assert_close(fused[:, :nh * d].float(), plain[:, :nh * d].float(), atol=3e-2, rtol=3e-2)
     torch.testing.assert_close(kv_a.float(), kv_b.float(), atol=3e-2, rtol=3e-2)
     assert ((kv_a == 7.0) == (kv_b == 7.0)).all(), "the fused kernel must write exactly the same slots"
+
+
+@pytest.mark.parametrize("nh,nkv,d,H", [(32, 4, 64, 2048), (32, 8, 128, 4096)])
+@pytest.mark.parametrize("q_lens,k_lens", [([1], [300]), ([1] * 8, [5, 17, 600, 64, 1, 129, 1023, 48]), ([3, 2, 6], [40, 2, 300])])
+def test_skinny_qkv_rope_write_against_the_plain_rotation(ops, nh, nkv, d, H, q_lens, k_lens):
+    """The product with the rotary epilogue and the page write at the widths of the benchmarks,
+    held to the plain formulation (tests/plain_llama.py: projection in float32, rotate-half with
+    float32 angles), not to another path of the engine: the rotated queries it returns and the
+    keys and values it leaves in the cache, slot by slot."""
+    from paged_llm_b200.parts.rope import RotaryEncoding
+    ops.set_compute_dtype(torch.bfloat16)
+    theta, ps = 500000.0, 16
+    rope = RotaryEncoding({}, head_dim=d, theta=theta)
+    rope.prepare(1024, "cuda", ops)
+    ctx = make_ctx(ops, q_lens, k_lens, nh, nkv, None, d)
+    T = sum(q_lens)
+    h = randn(T, H, seed=31, dtype=torch.bfloat16)
+    w = randn((nh + 2 * nkv) * d, H, seed=32, dtype=torch.bfloat16, std=0.03)
+    pages = sum(-(-k // ps) for k in k_lens) + 3
+    g = torch.Generator().manual_seed(5)
+    perm = torch.randperm(pages, generator=g)
+    bt = torch.full((len(q_lens), max(-(-k // ps) for k in k_lens) + 1), -1, dtype=torch.int32)
+    o = 0
+    for s, k in enumerate(k_lens):
+        n = -(-k // ps)
+        bt[s, :n] = perm[o:o + n]
+        o += n
+    kv = torch.full((pages, 2, nkv, ps, d), 7.0, dtype=torch.bfloat16, device="cuda")
+    got = ops.qkv_rope_write(h, w, nh, nkv, d, rope, ctx, kv, bt.cuda(), write=True)
+    assert ops.core.pl_gemm_skinny_timeouts() == 0
+    # plain: q, k, v = h W^T in float32; q and k rotated at each token's position
+    y = h.float().cpu() @ w.float().cpu().T
+    pos = torch.cat([torch.arange(k - q, k) for q, k in zip(q_lens, k_lens)])
+    cos, sin = plain_llama.rotary_cos_sin(pos, plain_llama.inv_frequencies(d, theta, None))
+    q_want = plain_llama.apply_rotary(y[:, :nh * d].view(T, nh, d), cos, sin)
+    k_want = plain_llama.apply_rotary(y[:, nh * d:(nh + nkv) * d].view(T, nkv, d), cos, sin)
+    v_want = y[:, (nh + nkv) * d:].view(T, nkv, d)
+    scale = float(y.abs().max())
+    torch.testing.assert_close(got[:, :nh * d].float().cpu().view(T, nh, d), q_want, atol=1e-2 * scale, rtol=1.6e-2)
+    kv_cpu = kv.float().cpu()
+    written = torch.zeros(pages, ps, dtype=torch.bool)
+    t = 0
+    for s, (nq, lk) in enumerate(zip(q_lens, k_lens)):
+        for p_ in range(lk - nq, lk):
+            page, slot = int(bt[s, p_ // ps]), p_ % ps
+            torch.testing.assert_close(kv_cpu[page, 0, :, slot], k_want[t], atol=1e-2 * scale, rtol=1.6e-2)
+            torch.testing.assert_close(kv_cpu[page, 1, :, slot], v_want[t], atol=1e-2 * scale, rtol=1.6e-2)
+            written[page, slot] = True
+            t += 1
+    untouched = kv_cpu[:, 0, 0, :, 0] == 7.0
+    assert (untouched == ~written).all(), "exactly the slots of the step's tokens are written"
 
 
 @pytest.mark.parametrize("M", [1, 8, 11])

@@ -137,6 +137,90 @@ def test_toy_architecture_with_state(tmp_path, dtype):
     assert rp.cm.num_free_state_slots == rp.cm.num_state_slots and rp.runner.num_graph_steps == 0
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_stateful_toy_that_replays_graphs(tmp_path, dtype):
+    """The same toy with its running mean written on the device's metadata alone (`capturable`):
+    decode steps replay CUDA graphs, the engine launches steps ahead, and a forked request starts
+    from a copy of its parent's state.  Nothing in the package knows the mixer."""
+    from paged_llm_b200 import LLMEngine, SamplingParams
+    from paged_llm_b200.engine.replay import TraceReplayer
+    from paged_llm_b200.engine.sequence import Sequence
+    from paged_llm_b200.weights import write_model_folder
+    from tests.toy_parts import TOY, ToyConfig, plain_toy_logits
+
+    hf = {**TOY, "architectures": ["DeviceToyForCausalLM"]}
+    write_model_folder(str(tmp_path), ToyConfig.from_hf_dict(hf, architecture="DeviceToyForCausalLM"), seed=4, std=0.1,
+                       norm_std=0.05)
+    cfg, w = read_folder(tmp_path)
+    reqs = {"a": random_tokens(61, 50, 1), "b": random_tokens(61, 37, 2), "c": random_tokens(61, 64, 3)}
+    plain = {rid: plain_toy_logits(cfg, w, toks).numpy() for rid, toks in reqs.items()}
+    for make in (schedules.tail, lambda r: schedules.mixed(r, live=2, seed=4)):
+        steps, max_tokens = make(reqs)
+        rp = TraceReplayer(str(tmp_path), dtype, max_tokens, poison=float("nan"))
+        outputs = {rec["step"]: out for rec in steps if (out := rp.step(rec)) is not None}
+        got = schedules.collect(steps, outputs)
+        for rid in reqs:
+            assert_logits_close(got[rid], plain[rid], dtype, f"device toy/{rid}")
+        assert rp.cm.num_free_state_slots == rp.cm.num_state_slots
+        assert rp.runner.num_graph_steps > 0, "decode steps of a capturable stateful model replay graphs"
+
+    # through the engine: steps run ahead; greedy tokens follow the plain model
+    eng = LLMEngine(str(tmp_path), dtype=dtype, block_size=16, num_gpu_blocks=32, max_model_len=128, max_num_seqs=4)
+    prompts = [reqs["a"][:9], reqs["b"][:20]]
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))
+    assert eng.stats.num_steps_ahead > 0 and eng.runner.num_graph_steps > 0
+    for p, o in zip(prompts, outs):
+        seq = list(p)
+        for tok in o.token_ids:
+            ref = plain_toy_logits(cfg, w, seq)[-1].numpy()
+            assert ref.max() - ref[tok] <= (1e-4 if dtype == "float32" else 3e-2 * np.abs(ref).max())
+            seq.append(tok)
+
+    # fork: the child continues from a copy of the parent's state and pages
+    sched, cm, runner = eng.scheduler, eng.block_manager, eng.runner
+    base = reqs["c"][:21]
+    root = Sequence(base, SamplingParams(temperature=0.0, max_tokens=50, ignore_eos=True))
+    sched.add(root)
+    out = sched.schedule()
+    sched.update(out, runner.run(out))
+    child = Sequence(base, SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True))
+    cm.fork(root, child)
+    assert child.state_slot is not None and child.state_slot != root.state_slot
+    child.token_ids = base + [7]
+    child.status = root.status
+    sched.running.append(child)
+    sched.abort(root.seq_id)
+    while sched.has_unfinished:
+        out = sched.schedule()
+        sched.update(out, runner.run(out))
+    seq = base + [7]
+    for tok in child.output_token_ids[1:]:
+        ref = plain_toy_logits(cfg, w, seq)[-1].numpy()
+        assert ref.max() - ref[tok] <= (1e-4 if dtype == "float32" else 3e-2 * np.abs(ref).max())
+        seq.append(tok)
+    assert len(child.output_token_ids) == 5 and cm.num_free_state_slots == cm.num_state_slots
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_with_a_bias_by_distance_instead_of_rotation(tmp_path, dtype):
+    """A Llama whose attention rotates nothing and instead adds, per head, a slope times the
+    distance to the key, with a cap on the scores of its second layer: two parameters of the
+    attention part chosen by a spec of the test's own, against the plain formulation."""
+    from paged_llm_b200.engine.replay import TraceReplayer
+    from tests.toy_parts import biased_llama_case
+
+    hf, w, reqs, plain = biased_llama_case(tmp_path, dtype)
+    for make in (schedules.tail, lambda r: schedules.mixed(r, live=3, seed=6)):
+        steps, max_tokens = make(reqs)
+        rp = TraceReplayer(str(tmp_path), dtype, max_tokens, poison=float("nan"))
+        outputs = {rec["step"]: out for rec in steps if (out := rp.step(rec)) is not None}
+        got = schedules.collect(steps, outputs)
+        for rid, toks in reqs.items():
+            assert_logits_close(got[rid], plain(toks), dtype, f"biased/{rid}")
+    without = plain_llama.forward_logits(hf, w, reqs["a"]).numpy()
+    assert np.abs(without - plain(reqs["a"])).max() > 0.05 * np.abs(without).max(), "the modifiers must matter here"
+
+
 @pytest.mark.parametrize("which,dtype", [("A", "float32"), ("B", "float32"), ("B", "bfloat16")])
 def test_routed_toy_architecture(tmp_path, which, dtype):
     """A learned table of positions added by an embedding of the test's own, attention that

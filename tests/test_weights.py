@@ -130,3 +130,24 @@ def test_missing_files(tmp_path):
         json.dump(cfg.to_hf_dict(), f)
     with pytest.raises(FileNotFoundError, match="safetensors"):
         load_model(str(tmp_path), "float32", "cpu")
+
+
+def test_random_stub_needs_the_kernel_library_and_no_tensors_beside_it(tmp_path):
+    """A folder of config.json + random_weights.json (weights drawn on the device): refused
+    without the kernel library, with tensor files beside it, or with unknown keys."""
+    from paged_llm_b200.weights import write_random_stub
+    from paged_llm_b200.weights.random_init import read_random_stub, tensor_key
+    cfg = LlamaConfig.from_hf_dict(TINY_A)
+    d = write_random_stub(str(tmp_path / "stub"), cfg, seed=5, std=0.03)
+    assert read_random_stub(d) == {"seed": 5, "std": 0.03, "norm_std": 0.0}
+    assert read_random_stub(make_folder(tmp_path / "plain", TINY_A, TINY_A_INIT)) is None
+    with pytest.raises(ValueError, match="kernel library"):
+        load_model(d, "float32", "cpu")
+    save_file({"model.norm.weight": torch.ones(64)}, os.path.join(d, "model.safetensors"))
+    with pytest.raises(ValueError, match="both"):
+        load_model(d, "float32", "cpu")
+    with open(os.path.join(d, "random_weights.json"), "w") as f:
+        json.dump({"seed": 1, "sigma": 2}, f)
+    with pytest.raises(ValueError, match="expected the keys"):
+        read_random_stub(d)
+    assert tensor_key("a.weight") != tensor_key("b.weight") and 0 <= tensor_key("a.weight") < 2 ** 64

@@ -60,6 +60,53 @@ if "toy_running_mean" not in MIXERS:
     register_mixer("toy_running_mean")(RunningMeanMixer)
 
 
+class DeviceRunningMeanMixer(Mixer):
+    """The same running mean, written so that a step can be captured and replayed: it reads the
+    step's metadata on the device only (request of each token, first row of each request, state
+    slots, positions) and launches a fixed sequence of tensor operations whatever the batch holds.
+    state = sum of h over the request so far; the count is the token's position + 1.  Rows and
+    requests that pad a captured batch (request -1, slot -1) add nothing."""
+
+    capturable = True
+
+    def __init__(self, weights, hidden_size: int):
+        self.hidden_size = hidden_size
+        self.name = weights["proj"]
+        self.w = None
+
+    def cache_requirement(self):
+        return FixedState((self.hidden_size,))
+
+    def tensor_specs(self):
+        return {self.name: TensorSpec((self.hidden_size, self.hidden_size))}
+
+    def load(self, tensors):
+        self.w = tensors[self.name]
+
+    def forward(self, h, ctx, cache):
+        seq = ctx.token_seq.long()                             # [T], -1 for padding rows
+        real = seq >= 0
+        seq = seq.clamp(min=0)
+        cu = ctx.cu_seqlens_q.long()                           # [S + 1]
+        slots = ctx.state_slots.long()                         # [S], -1 for padding requests
+        owned = slots >= 0
+        slots = slots.clamp(min=0)
+        state = cache.state
+        csum = (h.float() * real[:, None]).cumsum(0)           # over all rows of the step
+        first = cu[seq]                                        # first row of the token's request
+        before = torch.where((first > 0)[:, None], csum[(first - 1).clamp(min=0)], torch.zeros_like(csum))
+        run = csum - before + state[slots[seq]]                # the request's sum up to and including the token
+        out = (run / (ctx.positions.float() + 1)[:, None]).to(h.dtype)
+        last = (cu[1:] - 1).clamp(min=0)
+        grew = owned & (cu[1:] > cu[:-1])
+        state.index_add_(0, slots, torch.where(grew[:, None], run[last] - state[slots], torch.zeros_like(run[last])))
+        return ctx.ops.linear(out.contiguous(), self.w)
+
+
+if "toy_running_mean_device" not in MIXERS:
+    register_mixer("toy_running_mean_device")(DeviceRunningMeanMixer)
+
+
 @dataclass(frozen=True)
 class ToyConfig(ModelConfig):
     intermediate_size: int = 0
@@ -79,7 +126,7 @@ class ToyConfig(ModelConfig):
                 "num_heads": self.num_heads, "head_dim": self.head_dim}
 
 
-def toy_spec(cfg: ToyConfig) -> ModelSpec:
+def toy_spec(cfg: ToyConfig, mean_mixer: str = "toy_running_mean") -> ModelSpec:
     """Layers alternate running-mean and attention mixers; the schedule runs layer 1
     (attention) a second time at the end, reading the cache of its first run."""
     h = cfg.hidden_size
@@ -87,7 +134,7 @@ def toy_spec(cfg: ToyConfig) -> ModelSpec:
     for i in range(cfg.num_hidden_layers):
         p = f"toy.layers.{i}."
         if i % 2 == 0:
-            mixer = PartSpec("toy_running_mean", dict(hidden_size=h), {"proj": p + "mix.proj.weight"})
+            mixer = PartSpec(mean_mixer, dict(hidden_size=h), {"proj": p + "mix.proj.weight"})
         else:
             mixer = PartSpec("paged_attention", dict(hidden_size=h, num_heads=cfg.num_heads, num_kv_heads=1,
                                                      head_dim=cfg.head_dim, position="rotary"),
@@ -110,6 +157,9 @@ def toy_spec(cfg: ToyConfig) -> ModelSpec:
 
 if "ToyForCausalLM" not in ARCHITECTURES:
     register_architecture("ToyForCausalLM", ToyConfig, toy_spec)
+if "DeviceToyForCausalLM" not in ARCHITECTURES:       # the same model with the capturable running mean
+    register_architecture("DeviceToyForCausalLM", ToyConfig,
+                          lambda cfg: toy_spec(cfg, mean_mixer="toy_running_mean_device"))
 
 TOY = {"architectures": ["ToyForCausalLM"], "vocab_size": 61, "hidden_size": 48, "num_hidden_layers": 3,
        "intermediate_size": 40, "num_heads": 3, "head_dim": 16, "max_position_embeddings": 256,
@@ -345,3 +395,54 @@ def plain_routed_toy_logits(cfg: dict, w: dict, tokens) -> torch.Tensor:
                                                    w[e + "down_proj.weight"])[0]
         x = x + f
     return pl.rms_norm(x, w["rt.norm.weight"], cfg["eps"]) @ w["rt.head.weight"].T
+
+
+# --------------------------------------------------------------------------- a Llama with score modifiers
+
+def biased_llama_case(folder, dtype: str = "float32"):
+    """A Llama (the third tiny configuration) whose attention rotates nothing and instead adds,
+    per head, a slope times the distance to the key, with a cap on the scores of its second
+    layer: parameters of the attention part, chosen by a spec of the test's own.  Writes the
+    model folder; returns (config dict, float32 weights, requests, plain logits function)."""
+    from paged_llm_b200.config import LlamaConfig
+    from paged_llm_b200.models.llama import llama_spec
+    from paged_llm_b200.weights import write_model_folder
+    from tests import plain_llama
+    from tests.tiny import TINY_C, random_tokens, read_folder
+
+    heads = TINY_C["num_attention_heads"]
+    slopes = [2.0 ** -(1 + 6.0 * h / heads) for h in range(heads)]
+    caps = (None, 0.8)
+
+    def spec(cfg):
+        s = llama_spec(cfg)
+        for layer, cap in zip(s.layers, caps):
+            layer.mixer.params.update(position=None, position_slopes=slopes, score_cap=cap)
+        return s
+    if "BiasedLlama" not in ARCHITECTURES:
+        register_architecture("BiasedLlama", LlamaConfig, spec)
+    cfg = LlamaConfig.from_hf_dict({**TINY_C, "architectures": ["BiasedLlama"]}, architecture="BiasedLlama")
+    write_model_folder(str(folder), cfg, seed=8, std=0.15, dtype=dtype)
+    hf, w = read_folder(folder)
+    w = {k: v.float() for k, v in w.items()}
+    c = plain_llama.read_config(hf)
+    reqs = {"a": random_tokens(hf["vocab_size"], 90, 1), "b": random_tokens(hf["vocab_size"], 150, 2),
+            "c": random_tokens(hf["vocab_size"], 33, 3)}
+
+    def plain(toks):
+        T = len(toks)
+        x = w["model.embed_tokens.weight"][torch.tensor(toks)]
+        for i, cap in enumerate(caps):
+            p = f"model.layers.{i}."
+            h = plain_llama.rms_norm(x, w[p + "input_layernorm.weight"], c["eps"])
+            q = (h @ w[p + "self_attn.q_proj.weight"].T).view(T, c["heads"], c["head_dim"])
+            k = (h @ w[p + "self_attn.k_proj.weight"].T).view(T, c["kv_heads"], c["head_dim"])
+            v = (h @ w[p + "self_attn.v_proj.weight"].T).view(T, c["kv_heads"], c["head_dim"])
+            o = plain_llama.causal_attention(q, k, v, c["head_dim"] ** -0.5, softcap=cap, slopes=slopes)
+            x = x + o.reshape(T, -1) @ w[p + "self_attn.o_proj.weight"].T
+            h = plain_llama.rms_norm(x, w[p + "post_attention_layernorm.weight"], c["eps"])
+            x = x + plain_llama.gated_mlp(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
+                                          w[p + "mlp.down_proj.weight"])
+        return (plain_llama.rms_norm(x, w["model.norm.weight"], c["eps"]) @ w["lm_head.weight"].T).numpy()
+
+    return hf, w, reqs, plain
