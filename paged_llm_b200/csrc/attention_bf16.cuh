@@ -61,6 +61,23 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Rotates eight pairs (x[i], x[i + d/2]), i = i0..i0+7, of a head at position `pos`: lo and hi hold
+// the two halves' elements as bfloat16; the angles come from the float32 table [positions][d/2]
+// (cos, sin).  A position beyond the table is left unrotated (the engine refuses such a step earlier).
+__device__ __forceinline__ void rotate_pair(uint4& lo, uint4& hi, const float2* table, int table_len, int pos, int d, int i0) {
+    if (pos < 0 || pos >= table_len) return;
+    __nv_bfloat162* a = reinterpret_cast<__nv_bfloat162*>(&lo);
+    __nv_bfloat162* b = reinterpret_cast<__nv_bfloat162*>(&hi);
+    const float4* cs = reinterpret_cast<const float4*>(table + (size_t)pos * (d / 2) + i0);      // two (cos, sin) per float4
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float4 t = __ldg(cs + k);
+        const float2 x = __bfloat1622float2(a[k]), y = __bfloat1622float2(b[k]);
+        a[k] = __floats2bfloat162_rn(x.x * t.x - y.x * t.y, x.y * t.z - y.y * t.w);
+        b[k] = __floats2bfloat162_rn(y.x * t.x + x.x * t.y, y.y * t.z + x.y * t.w);
+    }
+}
+
 template <int DPAD, int MW, int NW, int KPW, int STAGES = 2>
 struct AttnShape {
     static constexpr int BM = 16 * MW, BN = KPW * NW, PITCH = DPAD + 8, THREADS = 32 * MW * NW;
@@ -74,8 +91,14 @@ struct AttnShape {
 // MOD: the score modifiers of AttnParams (cap, bias by distance) are applied; the kernel without
 // them is the one the Llama decoder runs and carries none of their code.
 // STAGES: key tiles in flight (a ring of that many K and V stages).
-template <int DPAD, int MW, int NW, int KPW, bool CLUSTER = false, bool MOD = false, int STAGES = 2>
+// ROPE (cluster form only): q, k, v arrive as the projection left them.  The queries are rotated as
+// they are loaded (xiyiji/paged-llm llama.py:117-128: pairs i, i + d/2, float32 angles from the
+// table), the step's own keys are rotated, written to their page slots together with the values
+// (kv_cache.py:42-45) and taken from registers instead of from the cache: the separate kernel for
+// rotary positions and the cache write is not needed.
+template <int DPAD, int MW, int NW, int KPW, bool CLUSTER = false, bool MOD = false, int STAGES = 2, bool ROPE = false>
 __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
+    static_assert(!ROPE || CLUSTER, "rotary positions inside the kernel: cluster form only");
     using Shape = AttnShape<DPAD, MW, NW, KPW, STAGES>;
     constexpr int BM = Shape::BM, BN = Shape::BN, PITCH = Shape::PITCH, THREADS = Shape::THREADS;
     constexpr int CH = DPAD / 8;                          // 16-byte chunks per row
@@ -104,7 +127,11 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
     const __nv_bfloat16* kv = (const __nv_bfloat16*)p.kv;
     const int* bt = p.block_table + (size_t)it.seq * p.bt_stride;
     const size_t v_off = (size_t)p.nkv * p.ps * d;
-
+    // The step's own keys (the last nq of the request) are written by the kernel in front, or, with
+    // ROPE, made here: then the tiles below stop in front of them and they come as a tile of their own.
+    const int own_lo = CLUSTER ? it.lk - it.nq : 0x7fffffff;
+    const int main_hi = ROPE ? min(it.key_hi, max(own_lo, it.key_lo)) : it.key_hi;
+    int hi_cur = main_hi;                                  // keys at or behind it are not part of the tile at hand
 
     // One key tile: every thread first looks up the pages of all its rows (independent loads
     // that travel together), then issues the copies.
@@ -119,7 +146,7 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
             const int e = tid + i * THREADS;
             const int j = e / CH, c8 = e - j * CH;
             const int n = kt + j;
-            const bool ok = e < BN * CH && n < it.key_hi && n < skip_from && c8 * 8 < d;
+            const bool ok = e < BN * CH && n < main_hi && n < skip_from && c8 * 8 < d;
             const int pi = p.ps_shift >= 0 ? n >> p.ps_shift : n / p.ps;
             pg[i] = ok ? bt[pi] : -1;
         }
@@ -129,7 +156,7 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
             if (e >= BN * CH) break;
             const int j = e / CH, c8 = e - j * CH;
             const int n = kt + j;
-            if (n >= skip_from && n < it.key_hi) continue;        // keys past the range are still zero-filled
+            if (n >= skip_from && n < main_hi) continue;          // keys past the range are still zero-filled
             const int po = p.ps_shift >= 0 ? n & (p.ps - 1) : n % p.ps;
             const bool ok = pg[i] >= 0;
             const __nv_bfloat16* src = ok ? kv + ((((size_t)pg[i] * 2) * p.nkv + kvh) * p.ps + po) * d + c8 * 8 : kv;
@@ -157,18 +184,17 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
         for (int e = 0; e < 4; ++e) oacc[j][e] = 0.f;
     const float scale_log2 = p.scale * LOG2E;
 
-    const int n_tiles = (it.key_hi - it.key_lo + BN - 1) / BN;
+    const int n_tiles = (main_hi - it.key_lo + BN - 1) / BN;
     // The first keys are on their way while Q is fetched.  A cluster block has not waited for the
     // kernel in front yet: the keys and values of this step's own tokens, which that kernel
     // writes, are left out of the first copy and fetched after the wait, in a group of their own
     // that the loop waits for together with the tile.
-    const int own_lo = CLUSTER ? it.lk - it.nq : 0x7fffffff;
     if (n_tiles > 0) load_tile(0, it.key_lo, own_lo);
     else cp_async_commit();
     if (CLUSTER) {
         pdl_wait();
-        const int new_lo = max(own_lo, it.key_lo), new_hi = min(it.key_hi, it.key_lo + BN);
-        if (n_tiles > 0 && new_lo < new_hi) {
+        const int new_lo = max(own_lo, it.key_lo), new_hi = min(main_hi, it.key_lo + BN);
+        if (!ROPE && n_tiles > 0 && new_lo < new_hi) {
             for (int e = tid; e < (new_hi - new_lo) * CH; e += THREADS) {
                 const int j = new_lo - it.key_lo + e / CH, c8 = e % CH;
                 const int n = it.key_lo + j;
@@ -190,26 +216,41 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
         if (t < n_tiles) load_tile(t, it.key_lo + t * BN);
         else cp_async_commit();
     }
-    for (int e = tid; e < BM * CH; e += THREADS) {
-        const int r = e / CH, c8 = e - r * CH;
-        const int R = it.row_base + r;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (R < it.rows_total && c8 * 8 < d)
-            v = *reinterpret_cast<const uint4*>(q + (size_t)(it.q0 + R / G) * p.q_stride + (kvh * G + R % G) * d + c8 * 8);
-        *reinterpret_cast<uint4*>(Qs + r * PITCH + c8 * 8) = v;
+    if (ROPE) {
+        // chunk c8 of the first half of a head with its partner in the second half; columns from d on are zero
+        const int hc = d / 16;                               // chunks per half
+        for (int e = tid; e < BM * hc; e += THREADS) {
+            const int r = e / hc, c8 = e - r * hc;
+            const int R = it.row_base + r;
+            uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+            if (R < it.rows_total) {
+                const __nv_bfloat16* src = q + (size_t)(it.q0 + R / G) * p.q_stride + (kvh * G + R % G) * d + c8 * 8;
+                lo = *reinterpret_cast<const uint4*>(src);
+                hi = *reinterpret_cast<const uint4*>(src + d / 2);
+                rotate_pair(lo, hi, p.rope_table, p.rope_len, it.lk - it.nq + R / G, d, c8 * 8);
+            }
+            *reinterpret_cast<uint4*>(Qs + r * PITCH + c8 * 8) = lo;
+            *reinterpret_cast<uint4*>(Qs + r * PITCH + d / 2 + c8 * 8) = hi;
+        }
+        const int padc = CH - 2 * hc;
+        for (int e = tid; e < BM * padc; e += THREADS)
+            *reinterpret_cast<uint4*>(Qs + (e / padc) * PITCH + d + (e % padc) * 8) = make_uint4(0, 0, 0, 0);
+    } else {
+        for (int e = tid; e < BM * CH; e += THREADS) {
+            const int r = e / CH, c8 = e - r * CH;
+            const int R = it.row_base + r;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (R < it.rows_total && c8 * 8 < d)
+                v = *reinterpret_cast<const uint4*>(q + (size_t)(it.q0 + R / G) * p.q_stride + (kvh * G + R % G) * d + c8 * 8);
+            *reinterpret_cast<uint4*>(Qs + r * PITCH + c8 * 8) = v;
+        }
     }
-    for (int t = 0; t < n_tiles; ++t) {
-        // tile t + STAGES - 1 goes into the stage that tile t - 1 left (all warps are past it: the
-        // barrier at the end of the iteration before); then all copies but those of the STAGES - 1
-        // newest groups are awaited, which completes tile t (and the step's own keys)
-        if (t + STAGES - 1 < n_tiles) load_tile((t + STAGES - 1) % STAGES, it.key_lo + (t + STAGES - 1) * BN);
-        else cp_async_commit();
-        cp_async_wait<STAGES - 1>();
-        __syncthreads();
-        const __nv_bfloat16* kst = Ks + (t % STAGES) * BN * PITCH + wn * KPW * PITCH;
-        const __nv_bfloat16* vst = Vs + (t % STAGES) * BN * PITCH + wn * KPW * PITCH;
-        const int kbase = it.key_lo + t * BN + wn * KPW;
-        if (kbase < it.key_hi) {                               // uniform per warp
+    // scores, softmax and weighted values of the keys [tile_lo, tile_lo + BN) that lie in `stage`
+    auto process_tile = [&](int stage, int tile_lo) {
+        const __nv_bfloat16* kst = Ks + stage * BN * PITCH + wn * KPW * PITCH;
+        const __nv_bfloat16* vst = Vs + stage * BN * PITCH + wn * KPW * PITCH;
+        const int kbase = tile_lo + wn * KPW;
+        if (kbase < hi_cur) {                                  // uniform per warp
             float sacc[KPW / 8][4];
 #pragma unroll
             for (int j = 0; j < KPW / 8; ++j)
@@ -230,7 +271,7 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
             // scale, mask, running maximum.  A tile whose keys all lie at or before the first
             // row's position (and inside the window and the range) needs no mask.
             const int pos_min_warp = __reduce_min_sync(0xffffffffu, min(pos[0], pos[1]));    // -1 if a row is padding
-            const bool full_tile = !modified && p.window <= 0 && kbase + KPW <= it.key_hi && kbase + KPW - 1 <= pos_min_warp;
+            const bool full_tile = !modified && p.window <= 0 && kbase + KPW <= hi_cur && kbase + KPW - 1 <= pos_min_warp;
             float mx[2] = {-INFINITY, -INFINITY};
             if (full_tile) {
 #pragma unroll
@@ -248,7 +289,7 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
                     for (int e = 0; e < 4; ++e) {
                         const int n = kbase + 8 * j + 2 * t4 + (e & 1);
                         const int pr = pos[e >> 1];
-                        const bool vis = n < it.key_hi && n <= pr && (p.window <= 0 || n > pr - p.window);
+                        const bool vis = n < hi_cur && n <= pr && (p.window <= 0 || n > pr - p.window);
                         const float s = !vis ? -INFINITY
                                         : modified ? attn_score(p, sacc[j][e], slope[e >> 1], n, pr) * LOG2E
                                                    : sacc[j][e] * scale_log2;
@@ -297,6 +338,61 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
                 }
             }
         }
+    };
+
+    for (int t = 0; t < n_tiles; ++t) {
+        // tile t + STAGES - 1 goes into the stage that tile t - 1 left (all warps are past it: the
+        // barrier at the end of the iteration before); then all copies but those of the STAGES - 1
+        // newest groups are awaited, which completes tile t (and the step's own keys)
+        if (t + STAGES - 1 < n_tiles) load_tile((t + STAGES - 1) % STAGES, it.key_lo + (t + STAGES - 1) * BN);
+        else cp_async_commit();
+        cp_async_wait<STAGES - 1>();
+        __syncthreads();
+        process_tile(t % STAGES, it.key_lo + t * BN);
+        __syncthreads();
+    }
+    if (ROPE && it.key_hi > main_hi) {
+        // The step's own keys of this block's range, as a last tile in stage 0: rotated keys and values
+        // straight from the projection, also written to their page slots; the rest of the first warp's
+        // rows is zeroed (a masked score still multiplies its value row).
+        const int own0 = main_hi, n_own = it.key_hi - main_hi;            // at most BM keys
+        const int hc = d / 16, padc = CH - 2 * hc;
+        for (int e = tid; e < KPW * hc; e += THREADS) {
+            const int j = e / hc, c8 = e - j * hc;
+            uint4 klo = make_uint4(0, 0, 0, 0), khi = klo, vlo = klo, vhi = klo;
+            if (j < n_own) {
+                const int n = own0 + j;                                    // position of the key
+                const __nv_bfloat16* row = q + (size_t)(it.q0 + n - (it.lk - it.nq)) * p.q_stride;
+                const __nv_bfloat16* ks = row + (size_t)(p.nh + kvh) * d + c8 * 8;
+                const __nv_bfloat16* vs = row + (size_t)(p.nh + p.nkv + kvh) * d + c8 * 8;
+                klo = *reinterpret_cast<const uint4*>(ks);
+                khi = *reinterpret_cast<const uint4*>(ks + d / 2);
+                vlo = *reinterpret_cast<const uint4*>(vs);
+                vhi = *reinterpret_cast<const uint4*>(vs + d / 2);
+                rotate_pair(klo, khi, p.rope_table, p.rope_len, n, d, c8 * 8);
+                const int pi = p.ps_shift >= 0 ? n >> p.ps_shift : n / p.ps;
+                const int po = p.ps_shift >= 0 ? n & (p.ps - 1) : n % p.ps;
+                const int pg = bt[pi];
+                if (pg >= 0 && (p.num_pages <= 0 || pg < p.num_pages)) {
+                    __nv_bfloat16* dst = const_cast<__nv_bfloat16*>(kv) + ((((size_t)pg * 2) * p.nkv + kvh) * p.ps + po) * d + c8 * 8;
+                    *reinterpret_cast<uint4*>(dst) = klo;
+                    *reinterpret_cast<uint4*>(dst + d / 2) = khi;
+                    *reinterpret_cast<uint4*>(dst + v_off) = vlo;
+                    *reinterpret_cast<uint4*>(dst + v_off + d / 2) = vhi;
+                }
+            }
+            *reinterpret_cast<uint4*>(Ks + j * PITCH + c8 * 8) = klo;
+            *reinterpret_cast<uint4*>(Ks + j * PITCH + d / 2 + c8 * 8) = khi;
+            *reinterpret_cast<uint4*>(Vs + j * PITCH + c8 * 8) = vlo;
+            *reinterpret_cast<uint4*>(Vs + j * PITCH + d / 2 + c8 * 8) = vhi;
+        }
+        for (int e = tid; e < KPW * padc; e += THREADS) {
+            *reinterpret_cast<uint4*>(Ks + (e / padc) * PITCH + d + (e % padc) * 8) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(Vs + (e / padc) * PITCH + d + (e % padc) * 8) = make_uint4(0, 0, 0, 0);
+        }
+        __syncthreads();
+        hi_cur = it.key_hi;
+        if (wn == 0) process_tile(0, own0);
         __syncthreads();
     }
 
@@ -479,13 +575,13 @@ int launch_attn_bf16(const AttnParams& p, cudaStream_t stream) {
 }
 
 // The cluster form of the small shape: p.n_work requests, p.cluster blocks per (request, kv head).
-template <int DPAD, int KPW, bool MOD = false, int STAGES = 2>
+template <int DPAD, int KPW, bool MOD = false, int STAGES = 2, int NW = 4, bool ROPE = false>
 int launch_attn_cluster(const AttnParams& p, cudaStream_t stream) {
-    using Shape = AttnShape<DPAD, 1, 4, KPW, STAGES>;
-    // the merge of the warps reuses the K/V stages ([4][BM][DPAD] float32); behind it, this block's partial
-    constexpr size_t merge = (size_t)Shape::Q_BYTES + 4 * Shape::BM * DPAD * 4;
+    using Shape = AttnShape<DPAD, 1, NW, KPW, STAGES>;
+    // the merge of the warps reuses the K/V stages ([NW][BM][DPAD] float32); behind it, this block's partial
+    constexpr size_t merge = (size_t)Shape::Q_BYTES + NW * Shape::BM * DPAD * 4;
     constexpr size_t smem = (Shape::SMEM_BYTES > merge ? Shape::SMEM_BYTES : merge) + Shape::BM * (DPAD + 2) * 4;
-    auto kernel = attn_bf16_kernel<DPAD, 1, 4, KPW, true, MOD, STAGES>;
+    auto kernel = attn_bf16_kernel<DPAD, 1, NW, KPW, true, MOD, STAGES, ROPE>;
     static bool attr_set[kAttnMaxDevices] = {};
     int dev = 0;
     PL_CUDA(cudaGetDevice(&dev));
@@ -543,25 +639,46 @@ PL_EXPORT int PL_CAT(pl_attention_bf16_d, PL_DPAD)(const AttnParams* params, cud
     PL_REQUIRE(p.q_stride % 8 == 0 && p.out_stride % 2 == 0, "attention_bf16: row strides must keep 16-byte alignment");
     PL_REQUIRE(((uintptr_t)p.q & 15) == 0 && ((uintptr_t)p.kv & 15) == 0, "attention_bf16: q and kv must be 16-byte aligned");
     PL_REQUIRE(p.softcap >= 0.f, "attention_bf16: softcap=%f must not be negative", (double)p.softcap);
-    // Shapes of the decode kernel, by measurement (B200; bytes in flight per SM are what counts, so the
-    // shared memory a block takes decides): head sizes up to 64 walk 128 keys per tile, but 64 keys in
-    // a ring of three tiles where the work list says that the ranges are long (is_small == 2: three
-    // blocks per SM, 18 against 26 us at 8 requests x 4,096 keys); head size 128 walks 64 keys per tile
-    // in all forms (three blocks per SM instead of one: 1.7 times the speed); head size 256 keeps 64
-    // keys and two stages, which is what fits.
+    // Shapes of the decode kernel, by measurement (B200; with so few warps per SM the dependent chain of a
+    // warp and the shared memory a block takes decide): head sizes up to 64 walk 128 keys per tile, but 64
+    // keys in a ring of three tiles where the work list says that the ranges are long (is_small == 2:
+    // three blocks per SM, 18 against 26 us at 8 requests x 4,096 keys); head size 128 walks 64 keys per
+    // tile in all forms (three blocks per SM instead of one: 1.7 times the speed); head size 256 keeps
+    // 64 keys and two stages, which is what fits.
     constexpr int KPW_CLUSTER = PL_DPAD <= 64 ? 32 : 16;
     if (p.softcap > 0.f || p.slopes != nullptr) {
+        PL_REQUIRE(p.rope_table == nullptr, "attention_bf16: score modifiers and rotary positions inside the kernel "
+                                            "do not combine");
         // the score modifiers live in instantiations of their own of the mma.sync kernel (the tcgen05
         // kernels step aside for them)
         if (p.cluster > 0) return launch_attn_cluster<PL_DPAD, KPW_CLUSTER, true>(p, stream);
         if (p.is_small) return launch_attn_bf16<PL_DPAD, 1, 4, KPW_CLUSTER, true>(p, stream);
         return launch_attn_bf16<PL_DPAD, PL_LARGE_MW, 1, 64, true>(p, stream);
     }
-    if (p.cluster > 0) return launch_attn_cluster<PL_DPAD, KPW_CLUSTER>(p, stream);
-#if PL_DPAD <= 64
-    if (p.is_small == 2) return launch_attn_bf16<PL_DPAD, 1, 4, 16, false, 3>(p, stream);
+    if (p.rope_table != nullptr) {
+        // rotary positions and the cache write inside the kernel: the cluster form only (the caller knows)
+        PL_REQUIRE(p.cluster > 0, "attention_bf16: rotary positions inside the kernel need the cluster form");
+        PL_REQUIRE(p.d % 16 == 0 && p.rope_len > 0, "attention_bf16: bad rotary table");
+#if PL_DPAD == 64
+        return launch_attn_cluster<PL_DPAD, 16, false, 2, 8, true>(p, stream);
+#else
+        return launch_attn_cluster<PL_DPAD, KPW_CLUSTER, false, 2, 4, true>(p, stream);
 #endif
+    }
+#if PL_DPAD == 64
+    // eight warps of 16 keys each on a tile of 128 keys: shorter dependent chains per warp and twice the
+    // warps per SM (13.5 against 14.2 us at 64 requests x 520 keys, 6.8 against 7.7 at 8, 5.1 against 5.8 at 1)
+    if (p.cluster > 0) return launch_attn_cluster<PL_DPAD, 16, false, 2, 8>(p, stream);
+    if (p.is_small == 2) return launch_attn_bf16<PL_DPAD, 1, 4, 16, false, 3>(p, stream);
+    if (p.is_small) return launch_attn_bf16<PL_DPAD, 1, 8, 16>(p, stream);
+#elif PL_DPAD < 64
+    if (p.cluster > 0) return launch_attn_cluster<PL_DPAD, KPW_CLUSTER>(p, stream);
+    if (p.is_small == 2) return launch_attn_bf16<PL_DPAD, 1, 4, 16, false, 3>(p, stream);
     if (p.is_small) return launch_attn_bf16<PL_DPAD, 1, 4, KPW_CLUSTER>(p, stream);
+#else
+    if (p.cluster > 0) return launch_attn_cluster<PL_DPAD, KPW_CLUSTER>(p, stream);
+    if (p.is_small) return launch_attn_bf16<PL_DPAD, 1, 4, KPW_CLUSTER>(p, stream);
+#endif
 #if PL_DPAD == 64 || PL_DPAD == 128
     // prefill tiles of head sizes 64 and 128 run on tcgen05 with tensor-memory accumulators
     static const bool no_tc = getenv("PAGED_LLM_B200_NO_TCGEN05") != nullptr;

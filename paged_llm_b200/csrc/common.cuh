@@ -121,6 +121,12 @@ struct AttnParams {
     float softcap;          // > 0: s = softcap * tanh(s / softcap)
     const float* slopes;    // [nh] or null: s += slopes[head] * (key position - query position), a bias that grows
                             // with the distance to the key; applied after the cap
+    // Rotary positions inside the kernel (bfloat16 cluster form only; null: q, k, v are rotated and stored
+    // already).  `q` then is the projection's output [T, (nh + 2 nkv) d] (q heads, k heads, v heads): queries
+    // and the step's own keys are rotated over the whole head (pairs i, i + d/2) with the angles of this
+    // table [rope_len, d/2] of (cos, sin), and the own keys and values are written to their page slots.
+    const float2* rope_table;
+    int rope_len;
 };
 
 // The score of one (query row, key) pair from the raw dot product, in natural-log units.

@@ -266,6 +266,16 @@ class ModelRunner:
         watermarks afterwards."""
         if not items:
             return None
+        pin = getattr(self.ops, "pin_stream", None)
+        if pin is None:
+            return self._step(items)
+        pin()
+        try:
+            return self._step(items)
+        finally:
+            self.ops.unpin_stream()
+
+    def _step(self, items: list[StepItem]) -> torch.Tensor | None:
         self.storage.apply_copies(self.cm.take_pending_copies(), self.ops)
         if self.cm.num_state_slots:
             # state of fixed size: a request that starts (again) begins from zeros, a forked one from its
@@ -442,9 +452,12 @@ class ModelRunner:
         saved_state = self.storage.save_state() if self.cm.num_state_slots else None
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
+        repin = getattr(self.ops, "pin_stream", lambda: None)
         with torch.cuda.stream(side):
+            repin()
             for _ in range(2):                       # warm-up: library workspaces, lazy module loads
                 self.model.forward(ctx)
+        repin()
         torch.cuda.current_stream().wait_stream(side)
         if saved_state is not None:
             self.storage.restore_state(saved_state)
@@ -457,8 +470,10 @@ class ModelRunner:
         gc.disable()
         try:
             with torch.cuda.graph(graph):
+                repin()                              # the capture runs on a stream of its own
                 logits = self.model.forward(ctx)
         finally:
+            repin()
             if gc_was_on:
                 gc.enable()
         launches = getattr(self.ops, "launches", 0) - before

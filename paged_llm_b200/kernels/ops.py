@@ -44,7 +44,7 @@ class AttnParams(ctypes.Structure):
         ("q_stride", c_int), ("out_stride", c_int), ("bt_stride", c_int), ("n_work", c_int), ("max_splits", c_int),
         ("nh", c_int), ("nkv", c_int), ("d", c_int), ("ps", c_int), ("window", c_int), ("is_small", c_int),
         ("scale", c_float), ("ps_shift", c_int), ("counters", c_void_p), ("num_pages", c_int), ("cluster", c_int),
-        ("softcap", c_float), ("slopes", c_void_p),
+        ("softcap", c_float), ("slopes", c_void_p), ("rope_table", c_void_p), ("rope_len", c_int),
     ]
 
 
@@ -100,6 +100,7 @@ class CudaOps:
         self.compute_dtype = torch.bfloat16
         self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self._scratch: list[torch.Tensor] = []
+        self._pinned_stream = None
         self._attn_lib = None
         self._attn_fn = None
         self.launches = 0                 # kernels of this package launched so far
@@ -117,6 +118,8 @@ class CudaOps:
         self.gemm_tc_pair = (os.environ.get("PAGED_LLM_B200_NO_GEMM_TC_PAIR") is None
                              and build.module_available("gemm_tc_pair"))
         self.cluster_attention = os.environ.get("PAGED_LLM_B200_NO_CLUSTER") is None   # decode attention as clusters
+        # decode steps of more than 16 tokens: rotary positions and the cache write inside the attention kernel
+        self.rope_in_attention = os.environ.get("PAGED_LLM_B200_NO_ROPE_IN_ATTENTION") is None
         self._argmax_ws = None            # (packed winners, arrival counters) of the multi-block argmax
         self._argmax_keep: list = []
         self._attn_counters = None        # arrival counters of the split merge inside the attention kernel
@@ -133,7 +136,18 @@ class CudaOps:
 
     @property
     def _stream(self):
+        if self._pinned_stream is not None:
+            return self._pinned_stream
         return c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def pin_stream(self) -> None:
+        """Looks the current stream up once and launches on it until `unpin_stream` (asking torch for the
+        current stream costs more than the rest of a launch; the step function pins it for the length of a
+        step and again wherever it changes the stream itself)."""
+        self._pinned_stream = c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def unpin_stream(self) -> None:
+        self._pinned_stream = None
 
     @staticmethod
     def _p(t: torch.Tensor | None):
@@ -422,11 +436,40 @@ class CudaOps:
         lib = load_module(f"attn_bf16_d{b}")
         return lib, getattr(lib, f"pl_attention_bf16_d{b}")
 
-    def paged_attention(self, qkv, nh, nkv, d, kv, block_table, ctx, scale, window, softcap=None, slopes=None):
+    def _runs_as_clusters(self, plan, ctx, nh: int, nkv: int, bf16: bool) -> bool:
+        """Whether this step's attention takes the cluster form of the decode kernel: every request
+        is a small item (a decode step), in bfloat16, with contexts short enough."""
+        return bool(bf16 and self.cluster_attention and plan.n_small and not plan.n_large
+                    and max(ctx.host.q_lens) * (nh // nkv) <= self.SMALL_ROWS and not plan.long_context)
+
+    def qkv_attention(self, h, w_qkv, nh, nkv, d, position, ctx, kv, block_table, scale, window, write=True,
+                      softcap=None, slopes=None) -> torch.Tensor:
+        """The mixer's whole front: fused q/k/v projection, rotary positions on q and k, k and v written
+        to the cache, attention over the pages.  Returns [T, nh * d].  It is `qkv_rope_write` followed by
+        `paged_attention`, but for a decode step of more than 16 tokens (the projection is a library
+        product then, without an epilogue) rotation and cache write happen inside the attention
+        kernel instead of in a kernel of their own."""
+        M = h.shape[0]
+        plan = ctx.attention_plans.get((nh // nkv, nkv, window, d))
+        inside = (plan is not None and write and softcap is None and slopes is None and position is not None
+                  and position.pairing == "half" and position.rotary_dim == d and M == ctx.num_tokens
+                  and not self._skinny_ok(h, (nh + 2 * nkv) * d) and self.compute_dtype == torch.bfloat16
+                  and kv.dtype == torch.bfloat16 and self._runs_as_clusters(plan, ctx, nh, nkv, True)
+                  and self.rope_in_attention)
+        if inside:
+            qkv = self.linear(h, w_qkv)
+            return self.paged_attention(qkv, nh, nkv, d, kv, block_table, ctx, scale, window, rope=position)
+        qkv = self.qkv_rope_write(h, w_qkv, nh, nkv, d, position, ctx, kv, block_table, write=write)
+        return self.paged_attention(qkv, nh, nkv, d, kv, block_table, ctx, scale, window, softcap=softcap, slopes=slopes)
+
+    def paged_attention(self, qkv, nh, nkv, d, kv, block_table, ctx, scale, window, softcap=None, slopes=None,
+                        rope=None):
         """Attention of the step's tokens over the paged cache.  `softcap` (scores become
         softcap * tanh(score / softcap)) and `slopes` (a float32 tensor [nh]: head h adds
         slopes[h] * (key position - query position) to its scores) modify the scores; both off
-        by default."""
+        by default.  `rope` (a prepared rotary encoding; only where the step runs as clusters, see
+        `qkv_attention`): qkv is the unrotated projection, and the kernel rotates q and the step's own
+        keys and writes those keys and values to the cache itself."""
         T = ctx.num_tokens
         plan = ctx.attention_plans[(nh // nkv, nkv, window, d)]
         out = torch.empty((T, nh * d), dtype=qkv.dtype, device=self.device)
@@ -451,8 +494,13 @@ class CudaOps:
         else:
             lib, fn = self.core, self.core.pl_attention_f32
         p.cluster = 0
-        if (bf16 and self.cluster_attention and plan.n_small and not plan.n_large
-                and max(ctx.host.q_lens) * (nh // nkv) <= self.SMALL_ROWS and not plan.long_context):
+        if rope is not None:
+            if not self._runs_as_clusters(plan, ctx, nh, nkv, bf16) or softcap or slopes is not None:
+                raise KernelError("rotary positions inside the attention kernel: only for decode steps that run as "
+                                  "clusters, without score modifiers")
+            assert qkv.shape[1] == (nh + 2 * nkv) * d and rope.table.is_contiguous() and rope.rotary_dim == d
+            p.rope_table, p.rope_len = rope.table.data_ptr(), rope.table.shape[0]
+        if self._runs_as_clusters(plan, ctx, nh, nkv, bf16):
             # every request is a small item: the splits of a (request, kv head) are the blocks of
             # a thread-block cluster that merge through distributed shared memory
             p.work, p.n_work, p.is_small, p.cluster = 0, ctx.num_seqs, 1, min(plan.max_splits, self.MAX_CLUSTER)

@@ -73,13 +73,9 @@ class PagedAttention(Mixer):
     def forward(self, h, ctx, cache):
         ops = ctx.ops
         block_table = ctx.block_tables[cache.group]
-        qkv = ops.qkv_rope_write(h, self.w_qkv, self.num_heads, self.num_kv_heads, self.head_dim, self.position,
-                                 ctx, cache.kv, block_table, write=cache.owner)
         if self.position_slopes is not None and self._slopes is None:
-            self._slopes = torch.tensor(self.position_slopes, dtype=torch.float32, device=qkv.device)
-        extra = {}
-        if self.score_cap is not None or self._slopes is not None:
-            extra = dict(softcap=self.score_cap, slopes=self._slopes)
-        o = ops.paged_attention(qkv, self.num_heads, self.num_kv_heads, self.head_dim, cache.kv,
-                                block_table, ctx, self.scale, self.window, **extra)
+            self._slopes = torch.tensor(self.position_slopes, dtype=torch.float32, device=cache.kv.device)
+        o = ops.qkv_attention(h, self.w_qkv, self.num_heads, self.num_kv_heads, self.head_dim, self.position, ctx,
+                              cache.kv, block_table, self.scale, self.window, write=cache.owner,
+                              softcap=self.score_cap, slopes=self._slopes)
         return LazyLinear(o, self.w_o)

@@ -269,6 +269,62 @@ def test_decode_attention_as_clusters_and_from_the_work_list(ops, cluster, windo
         torch.testing.assert_close(out[cu[s]:cu[s + 1]], want, atol=tol(dtype), rtol=tol(dtype), msg=f"request {s}")
 
 
+@pytest.mark.parametrize("nh,nkv,d,H", [(32, 4, 64, 256), (32, 8, 128, 512), (6, 2, 48, 96), (4, 4, 16, 64)])
+@pytest.mark.parametrize("q_lens,k_lens,window", [([1] * 20, [5, 17, 600, 64, 1, 129, 1023, 48, 300, 2, 33, 16, 700, 90, 250, 31, 32, 128, 257, 400], None),
+                                                  ([1] * 64, [520] * 64, None), ([2, 1, 2] * 7, [300, 2, 129] * 7, None),
+                                                  ([1] * 17, [90, 400, 3] * 5 + [1000, 7], 50)])
+def test_decode_step_with_rotation_inside_the_attention_kernel(ops, nh, nkv, d, H, q_lens, k_lens, window):
+    """A decode step of more than 16 tokens: the projection is a library product, and rotary
+    positions and the cache write happen inside the attention kernel (`qkv_attention`).  Held to
+    the plain formulation: float32 projection, rotate-half, attention over the rotated keys; and
+    the cache must hold the step's rotated keys and values afterwards, and nothing else new."""
+    from paged_llm_b200.parts.rope import RotaryEncoding
+    if max(q_lens) * (nh // nkv) > 16:
+        q_lens = [1] * len(q_lens)
+    dtype, ps, theta = torch.bfloat16, 16, 10000.0
+    ops.set_compute_dtype(dtype)
+    rope = RotaryEncoding({}, head_dim=d, theta=theta)
+    rope.prepare(1024, "cuda", ops)
+    _, kv, bt, keys, vals = paged_case(q_lens, k_lens, nh, nkv, d, ps, dtype, seed=3)
+    T = sum(q_lens)
+    h = randn(T, H, seed=41, dtype=dtype)
+    w = randn((nh + 2 * nkv) * d, H, seed=42, dtype=dtype, std=H ** -0.5)
+    y = (h.float().cpu() @ w.float().cpu().T).to(dtype).float()           # the projection rounds to bfloat16
+    pos = torch.cat([torch.arange(k - q, k) for q, k in zip(q_lens, k_lens)])
+    cos, sin = plain_llama.rotary_cos_sin(pos, plain_llama.inv_frequencies(d, theta, None))
+    q_rot = plain_llama.apply_rotary(y[:, :nh * d].view(T, nh, d), cos, sin).to(dtype).float()
+    k_rot = plain_llama.apply_rotary(y[:, nh * d:(nh + nkv) * d].view(T, nkv, d), cos, sin).to(dtype).float()
+    v_new = y[:, (nh + nkv) * d:].view(T, nkv, d)
+    # the slots of the step's own tokens hold poison until the step writes them
+    kv = kv.clone()
+    t = 0
+    for s, (nq, L) in enumerate(zip(q_lens, k_lens)):
+        for n in range(L - nq, L):
+            kv[bt[s, n // ps], :, :, n % ps] = float("nan")
+            keys[s][n], vals[s][n] = k_rot[t], v_new[t]
+            t += 1
+    ctx = make_ctx(ops, q_lens, k_lens, nh, nkv, window, d)
+    plan = ctx.attention_plans[(nh // nkv, nkv, window, d)]
+    assert ops._runs_as_clusters(plan, ctx, nh, nkv, True), "this test is about the cluster form"
+    kv_dev = kv.cuda()
+    before = ops.launches
+    out = ops.qkv_attention(h, w, nh, nkv, d, rope, ctx, kv_dev, bt.cuda(), d ** -0.5, window).float().cpu()
+    assert ops.launches - before == 1, "one kernel of this package beside the library product"
+    cu = ctx.host.cu
+    for s, (nq, L) in enumerate(zip(q_lens, k_lens)):
+        qs = torch.zeros(L, nh, d)
+        qs[L - nq:] = q_rot[cu[s]:cu[s + 1]]
+        want = plain_llama.causal_attention(qs, keys[s], vals[s], d ** -0.5, window=window)[L - nq:].reshape(nq, nh * d)
+        torch.testing.assert_close(out[cu[s]:cu[s + 1]], want, atol=tol(dtype), rtol=tol(dtype), msg=f"request {s}")
+    got_kv = kv_dev.float().cpu()
+    for s, (nq, L) in enumerate(zip(q_lens, k_lens)):
+        for n in range(L - nq, L):
+            torch.testing.assert_close(got_kv[bt[s, n // ps], 0, :, n % ps], keys[s][n], atol=tol(dtype), rtol=tol(dtype))
+            torch.testing.assert_close(got_kv[bt[s, n // ps], 1, :, n % ps], vals[s][n], atol=tol(dtype), rtol=tol(dtype))
+    same = torch.isnan(kv.float()) | (got_kv == kv.float())
+    assert same.all(), "only the slots of the step's own tokens may change"
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("window", [1, 7, 16, 100])
 @pytest.mark.parametrize("nh,nkv,d", [(4, 2, 32), (8, 2, 64), (6, 3, 128)])

@@ -68,6 +68,11 @@ class TorchOps:
         self.rope_kv_write(qkv, nh, nkv, d, position, ctx, kv, block_table, write=write)
         return qkv
 
+    def qkv_attention(self, h, w_qkv, nh, nkv, d, position, ctx, kv, block_table, scale, window, write=True,
+                      softcap=None, slopes=None):
+        qkv = self.qkv_rope_write(h, w_qkv, nh, nkv, d, position, ctx, kv, block_table, write=write)
+        return self.paged_attention(qkv, nh, nkv, d, kv, block_table, ctx, scale, window, softcap=softcap, slopes=slopes)
+
     def gather_rows(self, x, idx):
         return x[idx.long()].clone()
 
