@@ -273,6 +273,32 @@ def device_decode_loop(engine, batch: int, steps: int, warmup: int, prompt_len: 
     return ms, launches, ctx_mid
 
 
+def decode_kernel_times(engine, batch: int, steps: int, warmup: int, prompt_len: int) -> dict:
+    """Device time of every kernel inside replayed decode steps (torch's profiler, i.e. CUPTI activity
+    records of the real step, not serialised launches): name -> [launches per step, mean microseconds].
+    Kernels launched with programmatic dependent launch overlap, so the sum can exceed the step."""
+    import collections
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    device_decode_loop(engine, batch, steps, warmup, prompt_len)            # graphs captured, caches warm
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        _, launches, _ = device_decode_loop(engine, batch, steps, warmup, prompt_len)
+        torch.cuda.synchronize()
+    events = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA),
+                    key=lambda e: e.time_range.start)
+    # the decode steps are the tail of the record: per step the package's kernels, the library's, and two copies
+    per_step = collections.Counter()
+    tail = events[-int(round(launches + 4)) * steps:]
+    total = collections.defaultdict(float)
+    for e in tail:
+        name = e.name.split("(")[0].replace("void ", "").replace("(anonymous namespace)::", "")[:64]
+        per_step[name] += 1
+        total[name] += e.time_range.end - e.time_range.start
+    return {k: [round(per_step[k] / steps, 1), round(total[k] / per_step[k], 2)]
+            for k in sorted(total, key=lambda k: -total[k])[:14]}
+
+
 def e2e_decode(engine, batch: int, steps: int, warmup: int, prompt_len: int):
     """The same decode steps through the public `LLMEngine.step()`: token ids
     come back to the host every step."""
@@ -481,7 +507,9 @@ def run_ours(args) -> dict:
         ms, launches, ctx_mid = device_decode_loop(engine, B, args.steps, args.warmup, prompt_len)
         step_bytes = engine.model.weight_bytes_per_step() + B * ctx_mid * (engine.kv_cache.page_bytes() // BLOCK_SIZE)
         gbs = step_bytes / (ms * 1e-3) / 1e9
-        return {"only": "decode", "size": args.size, "batch": B, "context": ctx_mid, "ms_per_step": round(ms, 4),
+        extra = {"kernel_times": decode_kernel_times(engine, B, min(args.steps, 8), args.warmup, prompt_len)} \
+            if args.kernel_times else {}
+        return {**extra, "only": "decode", "size": args.size, "batch": B, "context": ctx_mid, "ms_per_step": round(ms, 4),
                 "tokens_per_s": round(B * 1000.0 / ms, 1), "launches_per_step": launches,
                 "layers": cfg.num_hidden_layers, "layers_full": full_layers, "gb_per_s": round(gbs, 1),
                 "frac": round(gbs / peaks["hbm_gbs"], 4), "peaks_source": peaks["source"]}
@@ -617,6 +645,8 @@ def main() -> int:
                     help="with --only prefill: length of the prompt (one step) instead of 2,048")
     ap.add_argument("--size", choices=sorted(SIZES), default="tinyllama-1.1b")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the named size (reported in config)")
+    ap.add_argument("--kernel-times", action="store_true",
+                    help="with --only decode: add the device time of every kernel inside the replayed steps")
     ap.add_argument("--only", choices=["decode", "prefill", "ragged", "mixed", "validate"], default=None,
                     help="run only the decode loop, only the prefill step, the ragged serving workload through "
                          "LLMEngine.generate, one mixed step (--batch decoding requests of --context tokens beside one "
