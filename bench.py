@@ -292,7 +292,8 @@ def decode_kernel_times(engine, batch: int, steps: int, warmup: int, prompt_len:
     tail = events[-int(round(launches + 4)) * steps:]
     total = collections.defaultdict(float)
     for e in tail:
-        name = e.name.split("(")[0].replace("void ", "").replace("(anonymous namespace)::", "")[:64]
+        name = e.name.replace("(anonymous namespace)::", "").replace("<unnamed>::", "").replace("void ", "")
+        name = name.split("(")[0][:72]
         per_step[name] += 1
         total[name] += e.time_range.end - e.time_range.start
     return {k: [round(per_step[k] / steps, 1), round(total[k] / per_step[k], 2)]
