@@ -272,7 +272,9 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
             }
             // scale, mask, running maximum.  A tile whose keys all lie at or before the first
             // row's position (and inside the window and the range) needs no mask.
-            const int pos_min_warp = __reduce_min_sync(0xffffffffu, min(pos[0], pos[1]));    // -1 if a row is padding
+            // (rows that pad the tile carry zero queries and are never stored: they need no mask)
+            const int pos_min_warp = __reduce_min_sync(0xffffffffu, min(pos[0] < 0 ? 0x7fffffff : pos[0],
+                                                                        pos[1] < 0 ? 0x7fffffff : pos[1]));
             const bool full_tile = !modified && p.window <= 0 && kbase + KPW <= hi_cur && kbase + KPW - 1 <= pos_min_warp;
             float mx[2] = {-INFINITY, -INFINITY};
             if (full_tile) {
@@ -322,12 +324,16 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
                 pa[j >> 1][(j & 1) * 2 + 0] = pack_bf16(pv[0], pv[1]);
                 pa[j >> 1][(j & 1) * 2 + 1] = pack_bf16(pv[2], pv[3]);
             }
+            // the accumulator is rescaled only if a row's maximum moved in this warp (a factor of exactly 1
+            // changes nothing): after the first tiles of a long context it seldom does
+            if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
 #pragma unroll
-            for (int j = 0; j < DPAD / 8; ++j) {
-                oacc[j][0] *= alpha[0];
-                oacc[j][1] *= alpha[0];
-                oacc[j][2] *= alpha[1];
-                oacc[j][3] *= alpha[1];
+                for (int j = 0; j < DPAD / 8; ++j) {
+                    oacc[j][0] *= alpha[0];
+                    oacc[j][1] *= alpha[0];
+                    oacc[j][2] *= alpha[1];
+                    oacc[j][3] *= alpha[1];
+                }
             }
 #pragma unroll
             for (int k2 = 0; k2 < KPW / 16; ++k2) {
@@ -582,7 +588,9 @@ int launch_attn_bf16(const AttnParams& p, cudaStream_t stream) {
 template <int DPAD, int KPW, bool MOD = false, int STAGES = 2, int NW = 4, bool ROPE = false, bool WP = false>
 int launch_attn_cluster(const AttnParams& p, cudaStream_t stream) {
     using Shape = AttnShape<DPAD, 1, NW, KPW, STAGES>;
-    // the merge of the warps reuses the K/V stages ([NW][BM][DPAD] float32); behind it, this block's partial
+    // the merge of the warps reuses the K/V stages ([NW][BM][DPAD] float32); behind it, this block's partial.
+    // (Letting the partial share the stages too would fit a third block of head size 128 on an SM; measured,
+    // the decode step at Llama-3-8B sizes and batch 64 got 4 % slower by it: 512 blocks fall badly on 444 places.)
     constexpr size_t merge = (size_t)Shape::Q_BYTES + NW * Shape::BM * DPAD * 4;
     constexpr size_t smem = (Shape::SMEM_BYTES > merge ? Shape::SMEM_BYTES : merge) + Shape::BM * (DPAD + 2) * 4;
     auto kernel = attn_bf16_kernel<DPAD, 1, NW, KPW, true, MOD, STAGES, ROPE, WP>;
