@@ -432,6 +432,25 @@ def mixed_step(engine, batch: int, portion: int, context: int, iters: int = 5, w
     return statistics.median(times)
 
 
+def chunked_prefill(engine, tokens: int, iters: int = 3, warmup: int = 2):
+    """One prompt of `tokens` tokens through the public `LLMEngine.generate` with one output token: the
+    scheduler cuts it into portions of `max_num_batched_tokens`.  Median wall-clock milliseconds."""
+    import torch
+    from paged_llm_b200.config import SamplingParams
+
+    vocab = engine.model_config.vocab_size
+    times = []
+    for i in range(warmup + iters):
+        prompt = prompts_for(vocab, 1, tokens, seed=20 + i)[0]
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        engine.generate([prompt], SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True))
+        torch.cuda.synchronize()
+        if i >= warmup:
+            times.append((time.perf_counter() - t0) * 1e3)
+    return statistics.median(times)
+
+
 def validate(args) -> dict:
     """The float32 validation run at the benchmark's layer sizes: the same trace (a 2,048-token
     portion, 32 decoded tokens, portions of changing size, a mixed batch) through the bfloat16 engine
@@ -496,7 +515,8 @@ def run_ours(args) -> dict:
             seqs = args.batch + 2
         engine = LLMEngine(folder, EngineConfig(
             dtype="bfloat16", block_size=BLOCK_SIZE, max_model_len=max_len, max_num_seqs=max(seqs, 64),
-            max_num_batched_tokens=max(2048, pre_tokens), enable_prefix_caching=False,
+            max_num_batched_tokens=args.chunk if args.only == "prefill" and args.chunk else max(2048, pre_tokens),
+            enable_prefix_caching=False,
             num_gpu_blocks=seqs * (-(-max_len // BLOCK_SIZE)) + 64))
     B = args.batch
     if args.only == "ragged":            # 64 ragged requests under a 2,048-token budget, end to end
@@ -523,6 +543,13 @@ def run_ours(args) -> dict:
                 "tokens_per_s": round((portion + B) * 1000.0 / ms, 1),
                 "tflops": round(flops / (ms * 1e-3) / 1e12, 1),
                 "frac": round(flops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"], 4), "peaks_source": peaks["source"]}
+    if args.only == "prefill" and args.chunk:
+        ms = chunked_prefill(engine, pre_tokens, iters=max(1, args.steps), warmup=args.warmup)
+        tflops = step_flops(cfg, pre_tokens) / (ms * 1e-3) / 1e12
+        return {"only": "prefill", "size": args.size, "tokens": pre_tokens, "portions_of": args.chunk, "ms": round(ms, 3),
+                "through": "LLMEngine.generate, one output token, wall clock", "layers": cfg.num_hidden_layers,
+                "layers_full": full_layers, "tokens_per_s": round(pre_tokens * 1000.0 / ms, 1), "tflops": round(tflops, 1),
+                "frac": round(tflops / peaks["bf16_tflops"], 4), "peaks_source": peaks["source"]}
     if args.only == "prefill":
         pre_ms = prefill_once(engine, pre_tokens, iters=max(1, args.steps), warmup=args.warmup)
         tflops = step_flops(cfg, pre_tokens) / (pre_ms * 1e-3) / 1e12
@@ -646,6 +673,8 @@ def main() -> int:
                     help="with --only prefill: length of the prompt (one step) instead of 2,048")
     ap.add_argument("--size", choices=sorted(SIZES), default="tinyllama-1.1b")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the named size (reported in config)")
+    ap.add_argument("--chunk", type=int, default=None,
+                    help="with --only prefill: the prompt goes through LLMEngine.generate in portions of this many tokens")
     ap.add_argument("--kernel-times", action="store_true",
                     help="with --only decode: add the device time of every kernel inside the replayed steps")
     ap.add_argument("--only", choices=["decode", "prefill", "ragged", "mixed", "validate"], default=None,

@@ -272,6 +272,8 @@ def test_decode_attention_as_clusters_and_from_the_work_list(ops, cluster, windo
 @pytest.mark.parametrize("nh,nkv,d,H", [(32, 4, 64, 256), (32, 8, 128, 512), (6, 2, 48, 96), (4, 4, 16, 64)])
 @pytest.mark.parametrize("q_lens,k_lens,window", [([1] * 20, [5, 17, 600, 64, 1, 129, 1023, 48, 300, 2, 33, 16, 700, 90, 250, 31, 32, 128, 257, 400], None),
                                                   ([1] * 64, [520] * 64, None), ([2, 1, 2] * 7, [300, 2, 129] * 7, None),
+                                                  # two new tokens whose keys fall on both sides of a cluster rank's edge
+                                                  ([2] * 18, [65, 33, 97, 129, 2, 3, 64, 66, 34, 200, 161, 95, 96, 31, 32, 1000, 500, 193], None),
                                                   ([1] * 17, [90, 400, 3] * 5 + [1000, 7], 50)])
 def test_decode_step_with_rotation_inside_the_attention_kernel(ops, nh, nkv, d, H, q_lens, k_lens, window):
     """A decode step of more than 16 tokens: the projection is a library product, and rotary
