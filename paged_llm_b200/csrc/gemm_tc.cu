@@ -1,5 +1,6 @@
-// The many-token tcgen05 product (gemm_tc.cuh) with every block fetching its own tiles.
-#include "gemm_tc.cuh"
+// The many-token tcgen05 products: gemm_tc.cuh with every block fetching its own tiles, and gemm_tc_duo.cuh
+// (pairs of blocks on one tile).
+#include "gemm_tc_duo.cuh"
 
 namespace {
 
@@ -27,4 +28,10 @@ PL_EXPORT int pl_gemm_tc_timeouts() {
 PL_EXPORT int pl_gemm_tc(const void* X, int ldx, const void* W, void* Y, int ldy, float* resid, int M, int N, int K, int epi,
                          cudaStream_t stream) {
     return gemm_tc_launch<SingleIO>(X, ldx, W, Y, ldy, resid, M, N, K, epi, stream);
+}
+
+// The same interface, run by pairs of blocks (tcgen05.mma.cta_group::2) on tiles of 256 tokens.
+PL_EXPORT int pl_gemm_tc_duo(const void* X, int ldx, const void* W, void* Y, int ldy, float* resid, int M, int N, int K,
+                             int epi, cudaStream_t stream) {
+    return gemm_tc_duo_launch(X, ldx, W, Y, ldy, resid, M, N, K, epi, stream);
 }

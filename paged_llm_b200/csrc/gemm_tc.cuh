@@ -55,6 +55,93 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// The epilogue of one thread: row `tok` of the tile of feature tile `nt`, whose accumulator starts at `acc`
+// (this thread's lane of tensor memory).
+__device__ __forceinline__ void tc_drain_row(const TcParams& p, uint32_t acc, int tok, int nt) {
+    if (p.epi == TC_SILU) {
+        const int j0 = nt * 128;
+#pragma unroll 1
+        for (int cb = 0; cb < 4; ++cb) {
+            float g[32], u[32];
+            tmem_ld32(acc + cb * 32, g);
+            tmem_ld32(acc + 128 + cb * 32, u);
+            if (tok < p.M) {
+                __nv_bfloat16* y = (__nv_bfloat16*)p.Y + (size_t)tok * p.ldy + j0 + cb * 32;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        float o[2];
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const float gate = __bfloat162float(__float2bfloat16_rn(g[q * 8 + 2 * i + e]));
+                            const float up = __bfloat162float(__float2bfloat16_rn(u[q * 8 + 2 * i + e]));
+                            o[e] = gate / (1.0f + __expf(-gate)) * up;
+                        }
+                        w[i] = pack_bf16x2(o[0], o[1]);
+                    }
+                    if (j0 + cb * 32 + q * 8 + 8 <= p.I)
+                        *reinterpret_cast<uint4*>(y + q * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                    else
+                        for (int i = 0; i < 8; ++i)
+                            if (j0 + cb * 32 + q * 8 + i < p.I)
+                                y[q * 8 + i] = __ushort_as_bfloat16((unsigned short)((w[i >> 1] >> ((i & 1) * 16)) & 0xffff));
+                }
+            }
+        }
+    } else {
+        const int n0 = nt * TC_BN;
+#pragma unroll 1
+        for (int cb = 0; cb < 8; ++cb) {
+            float v[32];
+            tmem_ld32(acc + cb * 32, v);
+            if (tok >= p.M) continue;
+            const int n = n0 + cb * 32;
+            if (p.epi == TC_BF16) {
+                __nv_bfloat16* y = (__nv_bfloat16*)p.Y + (size_t)tok * p.ldy + n;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    if (n + q * 8 + 8 <= p.N)
+                        *reinterpret_cast<uint4*>(y + q * 8) =
+                            make_uint4(pack_bf16x2(v[q * 8], v[q * 8 + 1]), pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]),
+                                       pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]), pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]));
+                    else
+                        for (int i = 0; i < 8; ++i)
+                            if (n + q * 8 + i < p.N) y[q * 8 + i] = __float2bfloat16_rn(v[q * 8 + i]);
+                }
+            } else if (p.epi == TC_F32) {
+                float* y = (float*)p.Y + (size_t)tok * p.ldy + n;
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    if (n + q * 4 + 4 <= p.N)
+                        *reinterpret_cast<float4*>(y + q * 4) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+                    else
+                        for (int i = 0; i < 4; ++i)
+                            if (n + q * 4 + i < p.N) y[q * 4 + i] = v[q * 4 + i];
+                }
+            } else {
+                // the branch is rounded to bfloat16 first, as a separate product would store it
+                float* x = p.resid + (size_t)tok * p.N + n;
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    if (n + q * 4 + 4 <= p.N) {
+                        float4 r = *reinterpret_cast<float4*>(x + q * 4);
+                        r.x += __bfloat162float(__float2bfloat16_rn(v[q * 4]));
+                        r.y += __bfloat162float(__float2bfloat16_rn(v[q * 4 + 1]));
+                        r.z += __bfloat162float(__float2bfloat16_rn(v[q * 4 + 2]));
+                        r.w += __bfloat162float(__float2bfloat16_rn(v[q * 4 + 3]));
+                        *reinterpret_cast<float4*>(x + q * 4) = r;
+                    } else {
+                        for (int i = 0; i < 4; ++i)
+                            if (n + q * 4 + i < p.N) x[q * 4 + i] += __bfloat162float(__float2bfloat16_rn(v[q * 4 + i]));
+                    }
+                }
+            }
+        }
+    }
+}
+
 // IO says how the W tile of a stage comes in and how a stage is given back:
 //   IO::CLUSTER            blocks per cluster (1, or 2 blocks that share every W tile)
 //   IO::load_w(dst, map, k, row_a, row_b, bar, rank)   the 256 rows of W behind the tile, as two boxes of 128
@@ -159,89 +246,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(TcParams p, cons
             mbar_wait(&acc_full[b], (n_tile >> 1) & 1);
             __syncwarp();
             fence_after_sync();
-            const uint32_t acc = trow + b * TC_BN;
-            if (p.epi == TC_SILU) {
-                const int j0 = nt * 128;
-#pragma unroll 1
-                for (int cb = 0; cb < 4; ++cb) {
-                    float g[32], u[32];
-                    tmem_ld32(acc + cb * 32, g);
-                    tmem_ld32(acc + 128 + cb * 32, u);
-                    if (tok < p.M) {
-                        __nv_bfloat16* y = (__nv_bfloat16*)p.Y + (size_t)tok * p.ldy + j0 + cb * 32;
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            uint32_t w[4];
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                float o[2];
-#pragma unroll
-                                for (int e = 0; e < 2; ++e) {
-                                    const float gate = __bfloat162float(__float2bfloat16_rn(g[q * 8 + 2 * i + e]));
-                                    const float up = __bfloat162float(__float2bfloat16_rn(u[q * 8 + 2 * i + e]));
-                                    o[e] = gate / (1.0f + __expf(-gate)) * up;
-                                }
-                                w[i] = pack_bf16x2(o[0], o[1]);
-                            }
-                            if (j0 + cb * 32 + q * 8 + 8 <= p.I)
-                                *reinterpret_cast<uint4*>(y + q * 8) = make_uint4(w[0], w[1], w[2], w[3]);
-                            else
-                                for (int i = 0; i < 8; ++i)
-                                    if (j0 + cb * 32 + q * 8 + i < p.I)
-                                        y[q * 8 + i] = __ushort_as_bfloat16((unsigned short)((w[i >> 1] >> ((i & 1) * 16)) & 0xffff));
-                        }
-                    }
-                }
-            } else {
-                const int n0 = nt * TC_BN;
-#pragma unroll 1
-                for (int cb = 0; cb < 8; ++cb) {
-                    float v[32];
-                    tmem_ld32(acc + cb * 32, v);
-                    if (tok >= p.M) continue;
-                    const int n = n0 + cb * 32;
-                    if (p.epi == TC_BF16) {
-                        __nv_bfloat16* y = (__nv_bfloat16*)p.Y + (size_t)tok * p.ldy + n;
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            if (n + q * 8 + 8 <= p.N)
-                                *reinterpret_cast<uint4*>(y + q * 8) =
-                                    make_uint4(pack_bf16x2(v[q * 8], v[q * 8 + 1]), pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]),
-                                               pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]), pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]));
-                            else
-                                for (int i = 0; i < 8; ++i)
-                                    if (n + q * 8 + i < p.N) y[q * 8 + i] = __float2bfloat16_rn(v[q * 8 + i]);
-                        }
-                    } else if (p.epi == TC_F32) {
-                        float* y = (float*)p.Y + (size_t)tok * p.ldy + n;
-#pragma unroll
-                        for (int q = 0; q < 8; ++q) {
-                            if (n + q * 4 + 4 <= p.N)
-                                *reinterpret_cast<float4*>(y + q * 4) = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
-                            else
-                                for (int i = 0; i < 4; ++i)
-                                    if (n + q * 4 + i < p.N) y[q * 4 + i] = v[q * 4 + i];
-                        }
-                    } else {
-                        // the branch is rounded to bfloat16 first, as a separate product would store it
-                        float* x = p.resid + (size_t)tok * p.N + n;
-#pragma unroll
-                        for (int q = 0; q < 8; ++q) {
-                            if (n + q * 4 + 4 <= p.N) {
-                                float4 r = *reinterpret_cast<float4*>(x + q * 4);
-                                r.x += __bfloat162float(__float2bfloat16_rn(v[q * 4]));
-                                r.y += __bfloat162float(__float2bfloat16_rn(v[q * 4 + 1]));
-                                r.z += __bfloat162float(__float2bfloat16_rn(v[q * 4 + 2]));
-                                r.w += __bfloat162float(__float2bfloat16_rn(v[q * 4 + 3]));
-                                *reinterpret_cast<float4*>(x + q * 4) = r;
-                            } else {
-                                for (int i = 0; i < 4; ++i)
-                                    if (n + q * 4 + i < p.N) x[q * 4 + i] += __bfloat162float(__float2bfloat16_rn(v[q * 4 + i]));
-                            }
-                        }
-                    }
-                }
-            }
+            tc_drain_row(p, trow + b * TC_BN, tok, nt);
             // this accumulator is in registers or stored: the product warp may write it again
             fence_before_sync();
             tc_arrive(&acc_empty[b]);

@@ -578,23 +578,23 @@ def test_skinny_gated_silu(ops, M, I, K):
     torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=2e-2)
 
 
-@pytest.mark.parametrize("pair", [True, False])
+@pytest.mark.parametrize("form", ["duo", "pair", "single"])
 @pytest.mark.parametrize("M", [129, 256, 300, 2048])
 @pytest.mark.parametrize("N,K", [(2048, 2048), (2560, 2048), (520, 128), (2048, 5632), (1000, 64), (11264, 2048)])
-def test_gemm_tc_product(ops, M, N, K, pair):
-    """More than 128 tokens: the tcgen05 product with 128 x 256 tiles and its epilogues against
-    float32 arithmetic on the same bfloat16 inputs."""
+def test_gemm_tc_product(ops, M, N, K, form):
+    """More than 128 tokens: the tcgen05 product (a block per 128 x 256 tile, pairs that share W tiles, two
+    blocks on one 256 x 256 tile) and its epilogues against float32 arithmetic on the same bfloat16 inputs."""
     if M == 2048 and K != 2048:
         pytest.skip("the largest M only at the benchmark's K")
     from paged_llm_b200.csrc import build
-    if pair and not build.module_available("gemm_tc_pair"):
+    if form == "pair" and not build.module_available("gemm_tc_pair"):
         pytest.skip("the paired form is not in this checkout")
     ops.set_compute_dtype(torch.bfloat16)
     h = randn(M, K, seed=50 + M % 97, dtype=torch.bfloat16)
     w = randn(N, K, seed=51 + N % 89, dtype=torch.bfloat16, std=K ** -0.5)
     want = h.float() @ w.float().T
     was, ops.gemm_tc_for = ops.gemm_tc_for, {"silu", "add", "plain"}
-    was_pair, ops.gemm_tc_pair = ops.gemm_tc_pair, pair
+    was_form, ops.gemm_tc_form = ops.gemm_tc_form, form
     was_min, ops.gemm_tc_min_tokens = ops.gemm_tc_min_tokens, 129
     try:
         before = ops.launches
@@ -616,11 +616,11 @@ def test_gemm_tc_product(ops, M, N, K, pair):
             g, u = want[:, :I].bfloat16().float(), want[:, I:].bfloat16().float()
             torch.testing.assert_close(act.float(), g * torch.sigmoid(g) * u, atol=3e-2, rtol=3e-2)
         assert ops.core.pl_gemm_tc_timeouts() == 0
-        if pair:
+        if form == "pair":
             from paged_llm_b200.kernels.ops import load_module
             assert load_module("gemm_tc_pair").pl_gemm_tc_pair_timeouts() == 0
     finally:
-        ops.gemm_tc_for, ops.gemm_tc_pair, ops.gemm_tc_min_tokens = was, was_pair, was_min
+        ops.gemm_tc_for, ops.gemm_tc_form, ops.gemm_tc_min_tokens = was, was_form, was_min
 
 
 @pytest.mark.parametrize("nh,nkv,d", [(32, 4, 64), (4, 2, 16), (3, 3, 32), (6, 2, 48)])
