@@ -17,6 +17,7 @@
 
 namespace {
 
+// measured on the gate/up product at 2,048 tokens: 4 stages 2 % slower per prefill, 5 to 7 the same
 constexpr int DUO_STAGES = 6;
 constexpr int DUO_A_BYTES = 128 * 128, DUO_B_BYTES = 128 * 128, DUO_STAGE_BYTES = DUO_A_BYTES + DUO_B_BYTES;
 constexpr size_t DUO_SMEM = (size_t)DUO_STAGES * DUO_STAGE_BYTES + 1024;
