@@ -55,6 +55,17 @@ __device__ __forceinline__ void duo_commit(uint64_t* bar) {
         : "memory");
 }
 
+// The order of tiles: bands of DUO_BAND token tiles (pairs of 128), feature tile by feature tile within a
+// band, so that the pairs running at a time share few rows of X and few rows of W (both stay in L2).
+constexpr int DUO_BAND = 8;
+__device__ __forceinline__ void duo_tile(int tile, int m_pairs, int n_tiles, int& nt, int& mp) {
+    const int per_band = DUO_BAND * n_tiles;
+    const int band = tile / per_band, in_band = tile - band * per_band;
+    const int rows = min(DUO_BAND, m_pairs - band * DUO_BAND);
+    nt = in_band / rows;
+    mp = band * DUO_BAND + (in_band - nt * rows);
+}
+
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_duo_kernel(TcParams p, const __grid_constant__ CUtensorMap x_map,
                                                                     const __grid_constant__ CUtensorMap w_map) {
     extern __shared__ unsigned char smem_unaligned[];
@@ -103,7 +114,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_duo_kernel(TcParams p, 
             bool alive = true;
             int it = 0;
             for (int tile = first; tile < tiles && alive; tile += stride) {
-                const int nt = tile / m_pairs, mt = (tile - nt * m_pairs) * 2 + (int)rank;
+                int nt, mp;
+                duo_tile(tile, m_pairs, p.n_tiles, nt, mp);
+                const int mt = mp * 2 + (int)rank;
                 // this block's half of the 256 rows of W: the first 128 (gate rows) or the second (up rows)
                 const int w_row = p.epi == TC_SILU ? (leader ? nt * 128 : p.I + nt * 128) : nt * 256 + (int)rank * 128;
                 for (int ks = 0; ks < k_steps; ++ks, ++it) {
@@ -156,7 +169,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_duo_kernel(TcParams p, 
         int n_tile = 0;
         for (int tile = first; tile < tiles; tile += stride, ++n_tile) {
             const int b = n_tile & 1;
-            const int nt = tile / m_pairs, mt = (tile - nt * m_pairs) * 2 + (int)rank;
+            int nt, mp;
+            duo_tile(tile, m_pairs, p.n_tiles, nt, mp);
+            const int mt = mp * 2 + (int)rank;
             // all lanes leave together: the loads of tensor memory below are warp-wide
             const bool ready = mbar_wait(&acc_full[b], (n_tile >> 1) & 1);
             if (!__all_sync(0xffffffffu, ready)) break;

@@ -579,13 +579,15 @@ def test_skinny_gated_silu(ops, M, I, K):
 
 
 @pytest.mark.parametrize("form", ["duo", "pair", "single"])
-@pytest.mark.parametrize("M", [129, 256, 300, 2048])
+@pytest.mark.parametrize("M", [129, 256, 300, 2048, 2500])
 @pytest.mark.parametrize("N,K", [(2048, 2048), (2560, 2048), (520, 128), (2048, 5632), (1000, 64), (11264, 2048)])
 def test_gemm_tc_product(ops, M, N, K, form):
     """More than 128 tokens: the tcgen05 product (a block per 128 x 256 tile, pairs that share W tiles, two
     blocks on one 256 x 256 tile) and its epilogues against float32 arithmetic on the same bfloat16 inputs."""
     if M == 2048 and K != 2048:
-        pytest.skip("the largest M only at the benchmark's K")
+        pytest.skip("2,048 tokens only at the benchmark's K")
+    if M == 2500 and (N, K) not in ((520, 128), (2560, 2048)):
+        pytest.skip("more than eight pairs of token tiles (two bands of the tile order) at two shapes only")
     from paged_llm_b200.csrc import build
     if form == "pair" and not build.module_available("gemm_tc_pair"):
         pytest.skip("the paired form is not in this checkout")
