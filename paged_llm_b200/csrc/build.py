@@ -37,9 +37,6 @@ MODULES: dict[str, list[str]] = {
     "core": ["common.cu", "elementwise.cu", "gemm_f32.cu", "gemm_skinny.cu", "gemm_tc.cu", "attention_f32.cu",
              "sampling.cu"],
     **{f"attn_bf16_d{d}": ["common.cu", f"attention_bf16_d{d}.cu"] for d in HEAD_DIM_BUILDS},
-    # the many-token tcgen05 product with blocks in pairs that share W tiles (optional: the package runs without
-    # this file, see module_available)
-    "gemm_tc_pair": ["common.cu", "gemm_tc_pair.cu"],
     # decode attention whose scratch is a static array of the library (see attention_decode_static.h)
     "attn_static": ["common.cu", "attention_decode_static.cu"],
 }

@@ -1,16 +1,20 @@
-// The many-token product of gemm_tc.cuh with the two blocks of a cluster on one tile of 256 tokens
+// The many-token product (see gemm_tc.cuh) with the two blocks of a cluster on one tile of 256 tokens
 // x 256 features (tcgen05.mma.cta_group::2): each block keeps its own 128 tokens of X and one half
 // of the 256 rows of W behind the tile, the tensor cores of both SMs read both halves of W, and each
-// block's tensor memory holds the accumulator of its own 128 tokens (all 256 features).  A stage is
-// then 32 KB per block instead of 48 KB for the same 512 cycles of products, and six stages fit
-// where four did: enough 64-k steps on their way to cover the latency of a tile under load.
+// block's tensor memory holds the accumulators of its own 128 tokens (all 256 features, twice: one
+// is drained while the other is filled).  A stage of the TMA ring is 32 KB per block for 512 cycles
+// of products, six stages deep.  Blocks are persistent; tiles are taken in bands (duo_tile).
 //
-// Roles per block: one thread brings this block's X and W boxes in (TMA with .cta_group::2, which
-// lets the copy signal the barrier of the other block); one thread of the first block of the pair
-// issues the products for both and commits on the barriers of both (tcgen05.commit with a block
-// mask); four warps per block drain the accumulator of their own tokens (the epilogues of
-// gemm_tc.cuh) and tell the first block when it may be written again.  No TMA load here delivers to
-// more than one block.  Every wait is bounded; a thread that gave up once stops waiting at all.
+// Roles per block: one thread brings this block's X and W boxes in (cp.async.bulk.tensor.2d with
+// 128-byte swizzle and .cta_group::2, which lets the copy signal the barrier of the other block);
+// one thread of the first block of the pair issues the products for both and commits on the
+// barriers of both (tcgen05.commit with a block mask); four warps per block drain the accumulator
+// of their own tokens (tcgen05.ld, the epilogue's arithmetic, 16-byte stores) and tell the first
+// block when it may be written again.  No TMA load here delivers to more than one block.  Every
+// wait is bounded; a thread that gave up once stops waiting at all.
+//
+// Measured against a block per 128 x 256 tile with four stages of 48 KB (the form this replaced):
+// gate/up + SiLU-mul at 2,048 tokens 76.7 against 84.0 us, tensor pipe 65 against 61 % of active cycles.
 #pragma once
 
 #include "gemm_tc.cuh"

@@ -64,8 +64,7 @@ def load_module(name: str) -> ctypes.CDLL:
 
 # Every wait inside a kernel (on an mbarrier of a TMA ring or of tcgen05) is bounded; a wait that
 # gives up adds one to a counter of its module, which these exports read.
-_TIMEOUT_EXPORTS = ("pl_gemm_skinny_timeouts", "pl_gemm_tc_timeouts", "pl_gemm_tc_pair_timeouts",
-                    "pl_attention_tc_timeouts")
+_TIMEOUT_EXPORTS = ("pl_gemm_skinny_timeouts", "pl_gemm_tc_timeouts", "pl_attention_tc_timeouts")
 
 
 def _check(lib, rc: int) -> None:
@@ -105,7 +104,7 @@ class CudaOps:
         self._attn_fn = None
         self.launches = 0                 # kernels of this package launched so far
         self.use_skinny = True            # few-token products on this package's weight-streaming kernel
-        # Many tokens: this package's tcgen05 kernel (128 x 256 tiles, fused epilogues) where it is at least
+        # Many tokens: this package's tcgen05 kernel (pairs of blocks on 256 x 256 tiles, fused epilogues) where it is at least
         # as fast as the library product followed by the elementwise kernel.  Measured: the gate/up product
         # with SiLU-mul from 2,048 tokens on (77 us against 87 us, timed alone); the narrower products and fewer
         # tokens are faster through the library.  PAGED_LLM_B200_GEMM_TC lists the kinds ("silu", "add", "plain", "all",
@@ -114,14 +113,6 @@ class CudaOps:
         self.gemm_tc_min_tokens = 2048 if tc_for is None else 129
         tc_for = "silu" if tc_for is None else tc_for
         self.gemm_tc_for = {"silu", "add", "plain"} if tc_for == "all" else {t for t in tc_for.split(",") if t}
-        # Its forms: "duo" (two blocks on one tile of 256 tokens, tcgen05.mma.cta_group::2), "single" (a block per
-        # tile) and "pair" (blocks in pairs that share W tiles by a TMA load to both: a module of its own, which
-        # may be absent).
-        self.gemm_tc_form = os.environ.get("PAGED_LLM_B200_GEMM_TC_FORM", "duo")
-        if self.gemm_tc_form not in ("duo", "single", "pair"):
-            raise KernelError(f"PAGED_LLM_B200_GEMM_TC_FORM={self.gemm_tc_form!r}: one of duo, single, pair")
-        if self.gemm_tc_form == "pair" and not build.module_available("gemm_tc_pair"):
-            self.gemm_tc_form = "single"
         self.cluster_attention = os.environ.get("PAGED_LLM_B200_NO_CLUSTER") is None   # decode attention as clusters
         # decode steps of more than 16 tokens: rotary positions and the cache write inside the attention kernel
         self.rope_in_attention = os.environ.get("PAGED_LLM_B200_NO_ROPE_IN_ATTENTION") is None
@@ -276,13 +267,7 @@ class CudaOps:
     def _gemm_tc(self, h: torch.Tensor, w: torch.Tensor, out, resid, N: int, epi: int) -> None:
         M, K = h.shape
         assert h.stride(1) == 1 and h.stride(0) % 8 == 0
-        if self.gemm_tc_form == "pair":
-            lib = load_module("gemm_tc_pair")
-            fn = lib.pl_gemm_tc_pair
-        elif self.gemm_tc_form == "duo":
-            lib, fn = self.core, self.core.pl_gemm_tc_duo
-        else:
-            lib, fn = self.core, self.core.pl_gemm_tc
+        lib, fn = self.core, self.core.pl_gemm_tc
         _check(lib, fn(self._p(h), h.stride(0), self._p(w), self._p(out), out.shape[1] if out is not None else 0,
                        self._p(resid), M, N, K, epi, self._stream))
         self.launches += 1

@@ -578,25 +578,20 @@ def test_skinny_gated_silu(ops, M, I, K):
     torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=2e-2)
 
 
-@pytest.mark.parametrize("form", ["duo", "pair", "single"])
 @pytest.mark.parametrize("M", [129, 256, 300, 2048, 2500])
 @pytest.mark.parametrize("N,K", [(2048, 2048), (2560, 2048), (520, 128), (2048, 5632), (1000, 64), (11264, 2048)])
-def test_gemm_tc_product(ops, M, N, K, form):
-    """More than 128 tokens: the tcgen05 product (a block per 128 x 256 tile, pairs that share W tiles, two
-    blocks on one 256 x 256 tile) and its epilogues against float32 arithmetic on the same bfloat16 inputs."""
+def test_gemm_tc_product(ops, M, N, K):
+    """More than 128 tokens: the tcgen05 product (two blocks on one 256 x 256 tile) and its epilogues against
+    float32 arithmetic on the same bfloat16 inputs."""
     if M == 2048 and K != 2048:
         pytest.skip("2,048 tokens only at the benchmark's K")
     if M == 2500 and (N, K) not in ((520, 128), (2560, 2048)):
         pytest.skip("more than eight pairs of token tiles (two bands of the tile order) at two shapes only")
-    from paged_llm_b200.csrc import build
-    if form == "pair" and not build.module_available("gemm_tc_pair"):
-        pytest.skip("the paired form is not in this checkout")
     ops.set_compute_dtype(torch.bfloat16)
     h = randn(M, K, seed=50 + M % 97, dtype=torch.bfloat16)
     w = randn(N, K, seed=51 + N % 89, dtype=torch.bfloat16, std=K ** -0.5)
     want = h.float() @ w.float().T
     was, ops.gemm_tc_for = ops.gemm_tc_for, {"silu", "add", "plain"}
-    was_form, ops.gemm_tc_form = ops.gemm_tc_form, form
     was_min, ops.gemm_tc_min_tokens = ops.gemm_tc_min_tokens, 129
     try:
         before = ops.launches
@@ -618,11 +613,8 @@ def test_gemm_tc_product(ops, M, N, K, form):
             g, u = want[:, :I].bfloat16().float(), want[:, I:].bfloat16().float()
             torch.testing.assert_close(act.float(), g * torch.sigmoid(g) * u, atol=3e-2, rtol=3e-2)
         assert ops.core.pl_gemm_tc_timeouts() == 0
-        if form == "pair":
-            from paged_llm_b200.kernels.ops import load_module
-            assert load_module("gemm_tc_pair").pl_gemm_tc_pair_timeouts() == 0
     finally:
-        ops.gemm_tc_for, ops.gemm_tc_form, ops.gemm_tc_min_tokens = was, was_form, was_min
+        ops.gemm_tc_for, ops.gemm_tc_min_tokens = was, was_min
 
 
 @pytest.mark.parametrize("nh,nkv,d", [(32, 4, 64), (4, 2, 16), (3, 3, 32), (6, 2, 48)])
