@@ -300,6 +300,27 @@ def decode_kernel_times(engine, batch: int, steps: int, warmup: int, prompt_len:
             for k in sorted(total, key=lambda k: -total[k])[:14]}
 
 
+def prefill_kernel_times(engine, tokens: int) -> dict:
+    """The same for one prompt portion of `tokens` tokens: name -> [launches in the step, mean microseconds]."""
+    import collections
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    prefill_once(engine, tokens, iters=1, warmup=3)                          # graph captured, caches warm
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        prefill_once(engine, tokens, iters=1, warmup=0)
+        torch.cuda.synchronize()
+    count, total = collections.Counter(), collections.defaultdict(float)
+    for e in prof.events():
+        if e.device_type != torch.autograd.DeviceType.CUDA:
+            continue
+        name = e.name.replace("(anonymous namespace)::", "").replace("<unnamed>::", "").replace("void ", "")
+        name = name.split("(")[0][:72]
+        count[name] += 1
+        total[name] += e.time_range.end - e.time_range.start
+    return {k: [count[k], round(total[k] / count[k], 2)] for k in sorted(total, key=lambda k: -total[k])[:14]}
+
+
 def e2e_decode(engine, batch: int, steps: int, warmup: int, prompt_len: int):
     """The same decode steps through the public `LLMEngine.step()`: token ids
     come back to the host every step."""
@@ -556,7 +577,8 @@ def run_ours(args) -> dict:
     if args.only == "prefill":
         pre_ms = prefill_once(engine, pre_tokens, iters=max(1, args.steps), warmup=args.warmup)
         tflops = step_flops(cfg, pre_tokens) / (pre_ms * 1e-3) / 1e12
-        return {"only": "prefill", "size": args.size, "tokens": pre_tokens, "ms": round(pre_ms, 3),
+        extra = {"kernel_times": prefill_kernel_times(engine, pre_tokens)} if args.kernel_times else {}
+        return {**extra, "only": "prefill", "size": args.size, "tokens": pre_tokens, "ms": round(pre_ms, 3),
                 "layers": cfg.num_hidden_layers, "tflops": round(tflops, 1),
                 "frac": round(tflops / peaks["bf16_tflops"], 4), "peaks_source": peaks["source"]}
     weight_bytes = engine.model.weight_bytes_per_step()
@@ -679,7 +701,7 @@ def main() -> int:
     ap.add_argument("--chunk", type=int, default=None,
                     help="with --only prefill: the prompt goes through LLMEngine.generate in portions of this many tokens")
     ap.add_argument("--kernel-times", action="store_true",
-                    help="with --only decode: add the device time of every kernel inside the replayed steps")
+                    help="with --only decode or --only prefill: add the device time of every kernel inside the replayed steps")
     ap.add_argument("--only", choices=["decode", "prefill", "ragged", "mixed", "validate"], default=None,
                     help="run only the decode loop, only the prefill step, the ragged serving workload through "
                          "LLMEngine.generate, one mixed step (--batch decoding requests of --context tokens beside one "
