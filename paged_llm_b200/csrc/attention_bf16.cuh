@@ -111,12 +111,18 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
     pdl_launch_dependents();
     // A cluster block (a decode step) waits for the kernel in front only after it has asked for its
     // first keys: lengths, block tables and all keys but the step's own are older than the step.
-    if (!CLUSTER) pdl_wait();
+    if (!CLUSTER) {
+        pdl_wait();
+        attn_zero_padding<__nv_bfloat16>(p);
+    }
     // kv heads of an item side by side: the list's longest-first order holds over heads
     const AttnItem it = CLUSTER ? attn_cluster_item(p, blockIdx.x / (p.cluster * p.nkv), blockIdx.x % p.cluster, p.cluster)
                                 : attn_decode_item(p, blockIdx.x / p.nkv, BM, BN);
     if (!it.valid) {                 // the same for all blocks of a cluster
-        if (CLUSTER) pdl_wait();
+        if (CLUSTER) {
+            pdl_wait();
+            attn_zero_padding<__nv_bfloat16>(p);
+        }
         return;
     }
 
@@ -207,6 +213,7 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
     else cp_async_commit();
     if (CLUSTER) {
         pdl_wait();
+        attn_zero_padding<__nv_bfloat16>(p);
         // (with ROPE they are made further down instead)
         if (!ROPE && n_tiles > 0) load_tile(0, it.key_lo, 0x7fffffff, max(own_lo, it.key_lo));
         else cp_async_commit();

@@ -81,6 +81,18 @@ __device__ __forceinline__ AttnItem attn_cluster_item(const AttnParams& p, int s
     return it;
 }
 
+// Zeroes the rows of `out` that pad the step (see AttnParams::pad_to); block 0 only, after the wait for the
+// kernel in front (the buffer may be memory that kernel still reads under another name).
+template <typename T>
+__device__ __forceinline__ void attn_zero_padding(const AttnParams& p) {
+    if (blockIdx.x != 0 || blockIdx.y != 0 || p.pad_to <= 0) return;
+    const int row0 = p.cu_q[p.pad_seqs];
+    if (row0 < 0 || row0 >= p.pad_to) return;
+    T* o = (T*)p.out + (size_t)row0 * p.out_stride;
+    const size_t n = (size_t)(p.pad_to - row0) * p.out_stride;
+    for (size_t i = threadIdx.x; i < n; i += blockDim.x) o[i] = T(0);
+}
+
 // Partial result of (scratch row, head, split): [m, l, acc[0..d)] with m the
 // running maximum of the scaled scores (natural-log units) and acc, l not yet
 // divided.

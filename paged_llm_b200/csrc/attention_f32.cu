@@ -9,6 +9,7 @@ constexpr int F32_MAXD = 256;
 
 // grid: (items, kv heads); 128 threads = 4 warps, each owning 4 of the 16 rows.
 __global__ void __launch_bounds__(128) attn_f32_kernel(AttnParams p) {
+    attn_zero_padding<float>(p);
     const AttnItem it = attn_decode_item(p, blockIdx.x / p.nkv, F32_ROWS, F32_KEYS);
     if (!it.valid) return;
     extern __shared__ float smem[];

@@ -127,6 +127,11 @@ struct AttnParams {
     // table [rope_len, d/2] of (cos, sin), and the own keys and values are written to their page slots.
     const float2* rope_table;
     int rope_len;
+    // A decode step padded to the size of its captured graph: rows [cu_q[pad_seqs], pad_to) of `out` belong to no
+    // request (pad_seqs: the number of request slots, so cu_q[pad_seqs] is the number of real tokens, read on the
+    // device because a replayed graph sees other lengths).  The first block of the split-context kernels zeroes
+    // them, so that no fill kernel stands between two kernels of a layer.  pad_to == 0: nothing to do.
+    int pad_seqs, pad_to;
 };
 
 // The score of one (query row, key) pair from the raw dot product, in natural-log units.

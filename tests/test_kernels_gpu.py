@@ -444,6 +444,58 @@ def test_one_far_key_in_a_portion_and_in_a_long_context(ops, nq, L, targets, d):
         assert ops._attention_bf16(d)[0].pl_attention_tc_timeouts() == 0
 
 
+def padded_ctx(ops, k_lens, pad_to, nh, nkv, d):
+    """A decode step of len(k_lens) requests padded to `pad_to` request slots, as the runner packs it for a
+    captured graph: empty slots have no token (cu stays), no keys, and -1 as their token's request."""
+    from paged_llm_b200.engine.context import AttentionPlan, HostBatch
+    S = len(k_lens)
+    q_lens = [1] * S
+    host = HostBatch(q_lens, [k - 1 for k in k_lens], [-1] * S)
+    plan = ops.plan_attention(q_lens, k_lens, nh // nkv, nkv, None, d, pad_requests=pad_to, fixed_capacity=True)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a, np.int32)).cuda()
+    small = plan["small"].reshape(-1, 4)
+    ap = AttentionPlan(dev(small), None, dev(plan["splits"]), len(small), 0, plan["max_splits"],
+                       plan["num_small_tokens"], plan.get("long_context", False))
+    cu = np.full(pad_to + 1, S, np.int32)
+    cu[:S + 1] = np.arange(S + 1)
+    klen = np.zeros(pad_to, np.int32)
+    klen[:S] = k_lens
+    pos = np.zeros(pad_to, np.int32)
+    pos[:S] = [k - 1 for k in k_lens]
+    tseq = np.full(pad_to, -1, np.int32)
+    tseq[:S] = np.arange(S)
+    return types.SimpleNamespace(num_tokens=pad_to, num_seqs=pad_to, host=host, cu_seqlens_q=dev(cu),
+                                 seq_lens_k=dev(klen), positions=dev(pos), token_seq=dev(tseq),
+                                 attention_plans={(nh // nkv, nkv, None, d): ap})
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("k_lens,pad_to", [([300, 5, 77], 8), ([40] * 5, 8), ([6000, 5200], 4), ([33], 2)])
+def test_rows_that_pad_a_decode_step_come_back_zero(ops, dtype, k_lens, pad_to):
+    """A step padded to the size of its graph: the rows of the requests are what the unpadded step gives, the
+    rows behind them are zero although the buffer held NaN before (no fill kernel runs: the attention
+    kernel's first block zeroes them), for the cluster form, the work list (long contexts) and float32."""
+    nh, nkv, d, ps = 32, 4, 64, 16
+    ops.set_compute_dtype(dtype)
+    S = len(k_lens)
+    q, kv, bt, _, _ = paged_case([1] * S, k_lens, nh, nkv, d, ps, dtype, seed=len(k_lens))
+    kv, bt = kv.cuda(), bt.cuda()
+    bt_pad = torch.zeros((pad_to, bt.shape[1]), dtype=torch.int32, device="cuda")
+    bt_pad[:S] = bt
+    qkv = torch.full((pad_to, (nh + 2 * nkv) * d), float("nan"), dtype=dtype, device="cuda")
+    qkv[:S, :nh * d] = q.reshape(S, nh * d).cuda()
+    qkv[:S, nh * d:] = 0
+    want = ops.paged_attention(qkv[:S].contiguous(), nh, nkv, d, kv, bt, make_ctx(ops, [1] * S, k_lens, nh, nkv, None, d),
+                               d ** -0.5, None)
+    ctx = padded_ctx(ops, k_lens, pad_to, nh, nkv, d)
+    for _ in range(3):
+        poison = torch.full((pad_to, nh * d), float("nan"), dtype=dtype, device="cuda")
+        del poison                                        # the allocator hands this block to the kernel's output
+        out = ops.paged_attention(qkv, nh, nkv, d, kv, bt_pad, ctx, d ** -0.5, None)
+        assert torch.equal(out[S:], torch.zeros_like(out[S:])), "rows that pad the step are not zero"
+        torch.testing.assert_close(out[:S].float(), want.float(), atol=tol(dtype, 4), rtol=tol(dtype))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("pairing", ["half", "interleaved"])
 @pytest.mark.parametrize("nh,nkv,d,rd", [(4, 2, 16, 16), (3, 3, 32, 32), (6, 2, 48, 24), (32, 4, 64, 64)])
