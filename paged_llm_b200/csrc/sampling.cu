@@ -4,9 +4,12 @@
 // The filter is the reference's (xiyiji/paged-llm pagedllm/sampler.py:17-29):
 // logits / max(T, 1e-5); a token stays if fewer than top_k tokens are larger and
 // if the probability mass of the larger tokens is <= top_p.  Instead of a sort,
-// the two thresholds are found by a bit-wise search over the order-preserving
-// integer image of the floats (32 counting passes each); tokens that tie with a
-// threshold all stay.  The draw is argmax(logit/T + g), g = -log(-log u), which
+// the two thresholds are found by a radix search over the order-preserving
+// integer image of the floats: four passes of eight bits, each a histogram of the
+// row (counts for top-k, probability mass for top-p) and a suffix sum over its 256
+// bins; tokens that tie with a threshold all stay.  Mass is summed in fixed point
+// (2^-40 units in 64-bit integers), so the sums do not depend on the order in
+// which threads arrive.  The draw is argmax(logit/T + g), g = -log(-log u), which
 // samples the softmax of the kept tokens; u comes from a counter-based stream
 // u(seed, counter, token index) (splitmix64), so a request's draw does not
 // depend on the rest of the batch.
@@ -135,7 +138,6 @@ __global__ void sample_kernel(const float* __restrict__ logits, int* __restrict_
                               const float* __restrict__ top_ps, const unsigned long long* __restrict__ seeds,
                               const unsigned long long* __restrict__ counters) {
     __shared__ MaxIdx red_mi[32];
-    __shared__ float red_f[32];
     const int r = blockIdx.x;
     const float* row = logits + (size_t)r * row_stride;
     const float temp = temps[r];
@@ -154,41 +156,129 @@ __global__ void sample_kernel(const float* __restrict__ logits, int* __restrict_
     const float top_p = top_ps[r];
     uint32_t key_floor = 0;                                   // tokens with ordered_key >= key_floor stay
 
-    if ((top_k > 0 && top_k < V) || top_p < 1.0f) {
-        float mx = -INFINITY;
-        for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, row[i] * inv_t);
+    const bool use_k = top_k > 0 && top_k < V, use_p = top_p < 1.0f;
+    if (use_k || use_p) {
+        __shared__ unsigned int cnt[256], piece[3][256];
+        __shared__ unsigned long long mass[256], total_mass;
+        __shared__ unsigned int pick_k, pick_p, need_k, key_lo, key_hi;
+        __shared__ unsigned long long above_p, limit_p;
+        const int tid = threadIdx.x;
+        if (tid == 0) {
+            total_mass = 0ull;
+            need_k = (unsigned)top_k;
+            above_p = 0ull;
+            key_lo = 0xFFFFFFFFu;
+            key_hi = 0u;
+        }
+        __syncthreads();
         {
-            MaxIdx m = block_argmax(MaxIdx{mx, (int)threadIdx.x}, red_mi);
-            mx = m.v;
-        }
-        float z = 0.f;
-        for (int i = threadIdx.x; i < V; i += blockDim.x) z += expf(row[i] * inv_t - mx);
-        z = block_sum(z, red_f);
-        if (top_k > 0 && top_k < V) {
-            uint32_t res = 0;                                 // largest key with count(key >= res) >= k
-            for (int bit = 31; bit >= 0; --bit) {
-                const uint32_t cand = res | (1u << bit);
-                float cnt = 0.f;
-                for (int i = threadIdx.x; i < V; i += blockDim.x) cnt += ordered_key(row[i] * inv_t) >= cand ? 1.f : 0.f;
-                cnt = block_sum(cnt, red_f);
-                if (cnt >= (float)top_k) res = cand;
+            uint32_t lo = 0xFFFFFFFFu, hi = 0u;
+            for (int i = tid; i < V; i += blockDim.x) {
+                const uint32_t key = ordered_key(row[i] * inv_t);
+                lo = min(lo, key);
+                hi = max(hi, key);
             }
-            key_floor = res;
+            lo = __reduce_min_sync(0xffffffffu, lo);
+            hi = __reduce_max_sync(0xffffffffu, hi);
+            if ((tid & 31) == 0) {
+                atomicMin(&key_lo, lo);
+                atomicMax(&key_hi, hi);
+            }
         }
-        if (top_p < 1.0f) {
-            uint32_t res = 0xFFFFFFFFu;                       // smallest key with mass above it <= top_p
-            for (int bit = 31; bit >= 0; --bit) {
-                const uint32_t cand = res & ~(1u << bit);
-                float mass = 0.f;
-                for (int i = threadIdx.x; i < V; i += blockDim.x) {
-                    const float x = row[i] * inv_t;
-                    if (ordered_key(x) > cand) mass += expf(x - mx);
+        __syncthreads();
+        // The search runs over a row's own span of keys: a key becomes its distance from the largest one, shifted
+        // so that the span fills whole digits of eight bits, and turned around so that larger still means larger.
+        // Its leading digit then spreads over the bins (the leading bits of the keys themselves are almost all alike).
+        const uint32_t kmax = key_hi, span = key_hi - key_lo;
+        const int bits = span == 0u ? 1 : 32 - __clz(span), digits = (bits + 7) / 8, lsh = 8 * digits - bits;
+        const uint32_t full = digits == 4 ? 0xFFFFFFFFu : (1u << (8 * digits)) - 1u;
+        auto spread = [&](uint32_t key) { return full - ((kmax - key) << lsh); };
+        float mx;                                             // the float behind the largest key
+        {
+            const uint32_t bts = (kmax & 0x80000000u) ? (kmax & 0x7FFFFFFFu) : ~kmax;
+            mx = __uint_as_float(bts);
+        }
+        // exp(x - max) in units of 2^-33.  A bin's mass is gathered in three 32-bit counters of 11 bits of the
+        // value each (shared memory adds 32-bit integers natively, 64-bit ones by compare-and-swap: 3.4 times
+        // slower here); each stays below 2^32 for up to 2^21 tokens.
+        auto fixed_mass = [&](float x) { return __float2ull_rn(expf(x - mx) * 8589934592.0f); };
+        if (use_p) {
+            unsigned long long z = 0ull;
+            for (int i = tid; i < V; i += blockDim.x) z += fixed_mass(row[i] * inv_t);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) z += __shfl_xor_sync(0xffffffffu, z, o);
+            if ((tid & 31) == 0) atomicAdd(&total_mass, z);
+            __syncthreads();
+            if (tid == 0) limit_p = (unsigned long long)((double)top_p * (double)total_mass);
+        }
+        uint32_t prefix_k = 0, prefix_p = 0;                  // the digits found so far, most significant first
+        for (int digit = digits - 1; digit >= 0; --digit) {
+            const int shift = 8 * digit;
+            if (tid < 256) {
+                cnt[tid] = 0u;
+                piece[0][tid] = piece[1][tid] = piece[2][tid] = 0u;
+            }
+            __syncthreads();
+            for (int i = tid; i < V; i += blockDim.x) {
+                const float x = row[i] * inv_t;
+                const uint32_t key = spread(ordered_key(x));
+                const uint32_t high = digit == digits - 1 ? 0u : key >> (shift + 8);
+                const uint32_t bin = (key >> shift) & 255u;
+                if (use_k && high == prefix_k) atomicAdd(&cnt[bin], 1u);
+                if (use_p && high == prefix_p) {
+                    const unsigned long long q = fixed_mass(x);
+                    atomicAdd(&piece[0][bin], (unsigned)(q & 0x7FFull));
+                    atomicAdd(&piece[1][bin], (unsigned)((q >> 11) & 0x7FFull));
+                    atomicAdd(&piece[2][bin], (unsigned)(q >> 22));
                 }
-                mass = block_sum(mass, red_f);
-                if (mass <= top_p * z) res = cand;
             }
-            key_floor = max(key_floor, res);
+            __syncthreads();
+            if (tid < 256)
+                mass[tid] = (unsigned long long)piece[0][tid] + ((unsigned long long)piece[1][tid] << 11) +
+                            ((unsigned long long)piece[2][tid] << 22);
+            __syncthreads();
+            // inclusive suffix sums over the bins (bin b: everything in bins b..255), in place
+            for (int off = 1; off < 256; off <<= 1) {
+                unsigned int c = 0u;
+                unsigned long long m = 0ull;
+                if (tid < 256) {
+                    c = cnt[tid] + (tid + off < 256 ? cnt[tid + off] : 0u);
+                    m = mass[tid] + (tid + off < 256 ? mass[tid + off] : 0ull);
+                }
+                __syncthreads();
+                if (tid < 256) {
+                    cnt[tid] = c;
+                    mass[tid] = m;
+                }
+                __syncthreads();
+            }
+            if (tid < 256) {
+                // top-k: the largest bin with at least `need_k` tokens in it and above it
+                const unsigned int c_here = cnt[tid], c_above = tid < 255 ? cnt[tid + 1] : 0u;
+                if (use_k && c_here >= need_k && c_above < need_k) pick_k = (unsigned)tid | (c_above << 8);
+                // top-p: the smallest bin with no more than the allowed mass above it
+                const unsigned long long m_above = tid < 255 ? mass[tid + 1] : 0ull;
+                const unsigned long long m_above_lower = mass[tid];          // what lies above bin tid - 1
+                if (use_p && above_p + m_above <= limit_p && (tid == 0 || above_p + m_above_lower > limit_p))
+                    pick_p = (unsigned)tid;
+            }
+            __syncthreads();
+            if (use_k) prefix_k = (prefix_k << 8) | (pick_k & 255u);
+            if (use_p) prefix_p = (prefix_p << 8) | pick_p;
+            if (tid == 0) {
+                if (use_k) need_k -= pick_k >> 8;             // the tokens above the chosen bin are in
+                if (use_p) above_p += pick_p < 255u ? mass[pick_p + 1] : 0ull;
+            }
+            __syncthreads();
         }
+        // prefix_k: the largest (spread) key with at least top_k keys >= it; prefix_p: the smallest one with mass
+        // above it <= top_p (the reference's filter, pagedllm/sampler.py:22-29); back to keys of the row
+        auto unspread = [&](uint32_t floor2) {
+            const uint32_t dist = (full - floor2) >> lsh;
+            return dist >= kmax ? 0u : kmax - dist;
+        };
+        if (use_k) key_floor = unspread(prefix_k);
+        if (use_p) key_floor = max(key_floor, unspread(prefix_p));
     }
     const uint64_t seed = seeds[r], counter = counters[r];
     MaxIdx best{-INFINITY, 0x7fffffff};
@@ -207,7 +297,7 @@ PL_EXPORT int pl_sample(const float* logits, int* out, int rows, int V, long lon
                         const int* top_ks, const float* top_ps, const unsigned long long* seeds,
                         const unsigned long long* counters, cudaStream_t stream) {
     if (rows == 0) return 0;
-    PL_REQUIRE(rows > 0 && V > 0 && row_stride >= V, "sample: bad sizes rows=%d V=%d", rows, V);
+    PL_REQUIRE(rows > 0 && V > 0 && V < (1 << 21) && row_stride >= V, "sample: bad sizes rows=%d V=%d", rows, V);
     sample_kernel<<<rows, 1024, 0, stream>>>(logits, out, V, (size_t)row_stride, temps, top_ks, top_ps, seeds, counters);
     PL_LAUNCHED("sample");
     return 0;

@@ -120,6 +120,10 @@ class CudaOps:
         # long work-list ranges of decode attention in a ring of three 64-key tiles (head sizes up to 64)
         self.deep_list = os.environ.get("PAGED_LLM_B200_NO_DEEP_LIST") is None
         self._argmax_ws = None            # (packed winners, arrival counters) of the multi-block argmax
+        self._sample_dev = None           # the sampling parameters of a step on the device, and their pinned ring
+        self._sample_ring: list = []
+        self._sample_keep: list = []
+        self._sample_pos = 0
         self._argmax_keep: list = []
         self._attn_counters = None        # arrival counters of the split merge inside the attention kernel
         self._attn_counters_keep: list = []
@@ -567,11 +571,33 @@ class CudaOps:
         rows, V = logits.shape
         assert logits.dtype == torch.float32 and logits.stride(1) == 1
         dev = self.device
-        t = torch.from_numpy(np.ascontiguousarray(temps, np.float32)).to(dev)
-        k = torch.from_numpy(np.ascontiguousarray(top_k, np.int32)).to(dev)
-        pp = torch.from_numpy(np.ascontiguousarray(top_p, np.float32)).to(dev)
-        s = torch.from_numpy(np.ascontiguousarray(seeds, np.uint64).view(np.int64)).to(dev)
-        c = torch.from_numpy(np.ascontiguousarray(counters, np.uint64).view(np.int64)).to(dev)
+        # The five per-row arrays go up as one copy from pinned memory that does not wait for the step in front
+        # of it (five copies from pageable memory each waited for the device: 1.01 against 0.81 ms per step at
+        # batch 8).  Layout in 8-byte words: seeds [rows], counters [rows], then temps, top_p, top_k as 4-byte
+        # values.
+        words = 2 * rows + (3 * rows + 1) // 2
+        if self._sample_dev is None or self._sample_dev.numel() < words:
+            self._sample_keep.append(self._sample_dev)              # a kernel in flight may still read the old one
+            self._sample_dev = torch.empty(max(2 * words, 1024), dtype=torch.int64, device=dev)
+            self._sample_ring = [[torch.empty(max(2 * words, 1024), dtype=torch.int64, pin_memory=True), None]
+                                 for _ in range(4)]
+        slot = self._sample_ring[self._sample_pos % len(self._sample_ring)]
+        self._sample_pos += 1
+        if slot[1] is not None:
+            slot[1].synchronize()                                   # its last copy has left the buffer
+        host = slot[0].numpy()
+        host[:rows] = np.ascontiguousarray(seeds, np.uint64).view(np.int64)
+        host[rows:2 * rows] = np.ascontiguousarray(counters, np.uint64).view(np.int64)
+        tail = host[2 * rows:words].view(np.float32)
+        tail[:rows] = temps
+        tail[rows:2 * rows] = top_p
+        tail[2 * rows:3 * rows].view(np.int32)[:] = top_k
+        self.copy_h2d(self._sample_dev, slot[0], words * 8)
+        slot[1] = torch.cuda.Event()
+        slot[1].record()
+        s, c = self._sample_dev[:rows], self._sample_dev[rows:2 * rows]
+        tail_dev = self._sample_dev[2 * rows:words].view(torch.float32)
+        t, pp, k = tail_dev[:rows], tail_dev[rows:2 * rows], tail_dev[2 * rows:3 * rows].view(torch.int32)
         out = torch.empty(rows, dtype=torch.int32, device=dev)
         _check(self.core, self.core.pl_sample(self._p(logits), self._p(out), rows, V, c_longlong(logits.stride(0)),
                                               self._p(t), self._p(k), self._p(pp), self._p(s), self._p(c),

@@ -584,6 +584,37 @@ def test_sampling_matches_the_plain_draw(ops):
     assert again == got
 
 
+@pytest.mark.parametrize("V", [32000, 128256, 1031])
+def test_sampling_filters_of_a_large_vocabulary(ops, V):
+    """top-k and top-p over vocabularies of real size (the thresholds come from a radix search over the
+    row): every draw of many falls into the set the plain filter keeps, the most likely kept tokens are
+    all drawn, and the draws equal the plain draws but for near-ties."""
+    from tests.plain_sampling import sample_rows
+    n = 256
+    row = randn(1, V, seed=16, std=2.5)
+    row[0, 7] = row[0, 11]                                   # a tie inside the kept set
+    logits = row.expand(n, V).contiguous()
+    for temp, k, p in ((0.8, 50, 1.0), (1.0, 0, 0.9), (0.7, 40, 0.95), (1.5, 1000, 0.5), (1.0, 1, 1.0), (1.0, 0, 1e-6)):
+        kept = torch.isfinite(plain_llama.filter_logits(row[0].float().cpu(), temp, k if k else -1, p)).numpy()
+        temps, ks, ps = np.full(n, temp, np.float32), np.full(n, k, np.int32), np.full(n, p, np.float32)
+        seeds, counters = np.full(n, 9, np.uint64), np.arange(n, dtype=np.uint64)
+        got = ops.sample(logits, temps, ks, ps, seeds, counters).cpu().numpy()
+        assert kept[got].all(), f"T={temp} k={k} p={p}: a filtered token was drawn"
+        want = sample_rows(logits.cpu().numpy()[:32], temps, ks, ps, seeds, counters)
+        assert sum(int(g) == w for g, w in zip(got[:32], want)) >= 31, f"T={temp} k={k} p={p}"
+        if kept.sum() == 1:
+            assert (got == int(np.flatnonzero(kept)[0])).all()
+    # mixed rows: each row its own filter
+    temps = np.array([0.7, 1.0, 0.0, 1.3] * 64, np.float32)
+    ks = np.array([0, 5, 0, 50] * 64, np.int32)
+    ps = np.array([1.0, 0.3, 1.0, 0.8] * 64, np.float32)
+    seeds, counters = np.arange(n, dtype=np.uint64) * 31 + 1, np.arange(n, dtype=np.uint64) + 5
+    got = ops.sample(logits, temps, ks, ps, seeds, counters).tolist()
+    want = sample_rows(logits.cpu().numpy()[:64], temps, ks, ps, seeds, counters)
+    assert sum(g == w for g, w in zip(got[:64], want)) >= 63
+    assert ops.sample(logits, temps, ks, ps, seeds, counters).tolist() == got
+
+
 def test_sampling_distribution(ops):
     """Many draws with different counters follow the filtered softmax."""
     V, n = 40, 20000
