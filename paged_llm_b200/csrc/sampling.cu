@@ -133,6 +133,25 @@ PL_EXPORT int pl_argmax(const float* logits, int* out, int rows, int V, long lon
     return 0;
 }
 
+// f(i, row[i]) for every token of a row, by all threads of the block; 16-byte loads where the row allows.
+template <typename F>
+__device__ __forceinline__ void for_each_logit(const float* __restrict__ row, int V, bool vec, F f) {
+    if (vec) {
+        const int V4 = V & ~3;
+#pragma unroll 2
+        for (int i = threadIdx.x * 4; i < V4; i += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(row + i);
+            f(i, v.x);
+            f(i + 1, v.y);
+            f(i + 2, v.z);
+            f(i + 3, v.w);
+        }
+        for (int i = V4 + threadIdx.x; i < V; i += blockDim.x) f(i, row[i]);
+    } else {
+        for (int i = threadIdx.x; i < V; i += blockDim.x) f(i, row[i]);
+    }
+}
+
 __global__ void sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, size_t row_stride,
                               const float* __restrict__ temps, const int* __restrict__ top_ks,
                               const float* __restrict__ top_ps, const unsigned long long* __restrict__ seeds,
@@ -140,6 +159,7 @@ __global__ void sample_kernel(const float* __restrict__ logits, int* __restrict_
     __shared__ MaxIdx red_mi[32];
     const int r = blockIdx.x;
     const float* row = logits + (size_t)r * row_stride;
+    const bool vec = (row_stride & 3) == 0 && ((uintptr_t)logits & 15) == 0;
     const float temp = temps[r];
     if (temp < 1e-5f) {                                       // greedy row in a mixed batch
         MaxIdx best{-INFINITY, 0x7fffffff};
@@ -173,11 +193,11 @@ __global__ void sample_kernel(const float* __restrict__ logits, int* __restrict_
         __syncthreads();
         {
             uint32_t lo = 0xFFFFFFFFu, hi = 0u;
-            for (int i = tid; i < V; i += blockDim.x) {
-                const uint32_t key = ordered_key(row[i] * inv_t);
+            for_each_logit(row, V, vec, [&](int, float v) {
+                const uint32_t key = ordered_key(v * inv_t);
                 lo = min(lo, key);
                 hi = max(hi, key);
-            }
+            });
             lo = __reduce_min_sync(0xffffffffu, lo);
             hi = __reduce_max_sync(0xffffffffu, hi);
             if ((tid & 31) == 0) {
@@ -204,7 +224,7 @@ __global__ void sample_kernel(const float* __restrict__ logits, int* __restrict_
         auto fixed_mass = [&](float x) { return __float2ull_rn(expf(x - mx) * 8589934592.0f); };
         if (use_p) {
             unsigned long long z = 0ull;
-            for (int i = tid; i < V; i += blockDim.x) z += fixed_mass(row[i] * inv_t);
+            for_each_logit(row, V, vec, [&](int, float v) { z += fixed_mass(v * inv_t); });
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) z += __shfl_xor_sync(0xffffffffu, z, o);
             if ((tid & 31) == 0) atomicAdd(&total_mass, z);
@@ -219,19 +239,20 @@ __global__ void sample_kernel(const float* __restrict__ logits, int* __restrict_
                 piece[0][tid] = piece[1][tid] = piece[2][tid] = 0u;
             }
             __syncthreads();
-            for (int i = tid; i < V; i += blockDim.x) {
-                const float x = row[i] * inv_t;
+            for_each_logit(row, V, vec, [&](int, float v) {
+                const float x = v * inv_t;
                 const uint32_t key = spread(ordered_key(x));
                 const uint32_t high = digit == digits - 1 ? 0u : key >> (shift + 8);
                 const uint32_t bin = (key >> shift) & 255u;
                 if (use_k && high == prefix_k) atomicAdd(&cnt[bin], 1u);
                 if (use_p && high == prefix_p) {
-                    const unsigned long long q = fixed_mass(x);
-                    atomicAdd(&piece[0][bin], (unsigned)(q & 0x7FFull));
-                    atomicAdd(&piece[1][bin], (unsigned)((q >> 11) & 0x7FFull));
-                    atomicAdd(&piece[2][bin], (unsigned)(q >> 22));
+                    const unsigned long long q = fixed_mass(x);         // zero for the far tail: nothing to add
+                    const unsigned p0 = (unsigned)(q & 0x7FFull), p1 = (unsigned)((q >> 11) & 0x7FFull), p2 = (unsigned)(q >> 22);
+                    if (p0) atomicAdd(&piece[0][bin], p0);
+                    if (p1) atomicAdd(&piece[1][bin], p1);
+                    if (p2) atomicAdd(&piece[2][bin], p2);
                 }
-            }
+            });
             __syncthreads();
             if (tid < 256)
                 mass[tid] = (unsigned long long)piece[0][tid] + ((unsigned long long)piece[1][tid] << 11) +
@@ -282,13 +303,13 @@ __global__ void sample_kernel(const float* __restrict__ logits, int* __restrict_
     }
     const uint64_t seed = seeds[r], counter = counters[r];
     MaxIdx best{-INFINITY, 0x7fffffff};
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float x = row[i] * inv_t;
-        if (ordered_key(x) < key_floor) continue;
+    for_each_logit(row, V, vec, [&](int i, float v) {
+        const float x = v * inv_t;
+        if (ordered_key(x) < key_floor) return;
         const float u = uniform01(seed, counter, (uint64_t)i);
         const float score = x - logf(-logf(u));
         if (score > best.v || (score == best.v && i < best.i) || best.i == 0x7fffffff) best = MaxIdx{score, i};
-    }
+    });
     best = block_argmax(best, red_mi);
     if (threadIdx.x == 0) out[r] = best.i == 0x7fffffff ? 0 : best.i;
 }
