@@ -74,3 +74,4 @@ class StepContext:
     host: HostBatch
     attention_plans: dict = field(default_factory=dict)    # (group size, window) -> AttentionPlan
     logits_all: bool = False        # logits are wanted at every token, in order (decode steps): no row gather
+    padded: bool = False            # built for a captured graph of mixed items: token rows and lists have spare capacity

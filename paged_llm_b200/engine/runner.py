@@ -15,6 +15,7 @@ replayed from CUDA graphs, one per batch-size bucket, unless `enforce_eager`.
 from __future__ import annotations
 
 import gc
+import os
 from dataclasses import dataclass
 
 import numpy as np
@@ -23,6 +24,7 @@ import torch
 from ..cache.manager import CacheManager
 from ..cache.storage import CacheStorage
 from ..config.engine import EngineConfig
+from ..kernels.plan import PlanCapacityError
 from .context import AttentionPlan, HostBatch, StepContext
 from .sequence import Sequence
 
@@ -65,6 +67,7 @@ class _Graph:
         self.strides = None
         self.plan_tag = None
         self.plan_shapes = None      # per plan key: (sizes of its three sections, max_splits, long_context) as captured
+        self.wanted = 0              # rows of `logits` that the last replay asked for (graphs of mixed items)
 
 
 class _Staging:
@@ -96,6 +99,7 @@ class ModelRunner:
         self._portion_seen: dict[tuple, int] = {}
         self.use_graphs = ((not config.enforce_eager) and self.device.type == "cuda"
                            and getattr(ops, "supports_graphs", False) and getattr(model, "capturable", True))
+        self.mixed_graphs = self.use_graphs and os.environ.get("PAGED_LLM_B200_NO_MIXED_GRAPHS") is None
         self.num_graph_steps = 0
         self.num_eager_steps = 0
         self.graph_launches = 0            # kernels of this package launched by graph replays
@@ -105,9 +109,12 @@ class ModelRunner:
         self.next_ids_override: torch.Tensor | None = None
 
     # ------------------------------------------------------------------ metadata
-    def _gather(self, items: list[StepItem], pad_to: int | None = None, table_stride: int | None = None):
+    def _gather(self, items: list[StepItem], pad_to: int | None = None, table_stride: int | None = None,
+                pad_mixed: tuple[int, int] | None = None):
         """Host side of a step: numpy sections and the HostBatch.  With `pad_to`
-        (graph replay) token and request counts are padded to the bucket."""
+        (replay of a decode graph) token and request counts are padded to the bucket; with
+        `pad_mixed` = (tokens, requests) (replay of a graph of mixed items) tokens, requests,
+        wanted rows and the attention work lists are padded to the capacity of any such step."""
         S = len(items)
         q_lens = [it.num_new_tokens for it in items]
         starts = [it.seq.num_computed_tokens for it in items]
@@ -149,6 +156,11 @@ class ModelRunner:
                 o += n
         S_pad = pad_to or S
         T_pad = pad_to or T
+        if pad_mixed is not None:
+            T_pad, S_pad = pad_mixed
+            if T > T_pad or S > S_pad or len(want) > S_pad:
+                raise PlanCapacityError(f"{T} tokens, {S} requests, {len(want)} wanted rows for a graph of "
+                                        f"{T_pad} tokens and {S_pad} requests")
         host = HostBatch(q_lens, starts, [(-1 if it.seq.state_slot is None else it.seq.state_slot) for it in items],
                          [it.seq.seq_id for it in items])
         cu = np.zeros(S_pad + 1, np.int32)
@@ -169,7 +181,7 @@ class ModelRunner:
         pk.add("cu", cu)
         pk.add("klen", klen)
         pk.add("slots", slots)
-        L_pad = pad_to or len(want)
+        L_pad = pad_to or (S_pad if pad_mixed is not None else len(want))
         lidx = np.zeros(max(L_pad, 1), np.int32)
         lidx[:len(want)] = want
         pk.add("lidx", lidx)
@@ -186,14 +198,19 @@ class ModelRunner:
             pk.add(f"bt{g}", bt)
         plans = {}
         for key in self.plan_keys:
-            plan = self.ops.plan_attention(q_lens, host.k_lens, *key, pad_requests=S_pad,
-                                           fixed_capacity=pad_to is not None)
+            if pad_mixed is not None:
+                plan = self.ops.plan_attention(q_lens, host.k_lens, *key, pad_requests=S_pad, fixed_capacity=True,
+                                               pad_tokens=T_pad)
+            else:
+                plan = self.ops.plan_attention(q_lens, host.k_lens, *key, pad_requests=S_pad,
+                                               fixed_capacity=pad_to is not None)
             plans[key] = plan
             pk.add(f"small{key}", plan["small"])
             pk.add(f"large{key}", plan["large"])
             pk.add(f"splits{key}", plan["splits"])
         return pk, host, dict(T=T_pad, S=S_pad, L=len(want), L_pad=L_pad, strides=strides, plans=plans,
-                              max_q=max(q_lens), logits_all=(L_pad == T_pad and want == list(range(len(want)))))
+                              max_q=max(q_lens), padded=pad_mixed is not None,
+                              logits_all=(pad_mixed is None and L_pad == T_pad and want == list(range(len(want)))))
 
     def _table_row(self, seq: Sequence, g: int) -> np.ndarray:
         """The request's block table of group g as an array, rebuilt only when the cache
@@ -254,7 +271,8 @@ class ModelRunner:
             input_ids=view("ids"), positions=view("pos"), token_seq=view("tseq"), cu_seqlens_q=view("cu"),
             seq_lens_k=view("klen"), state_slots=view("slots"), logits_indices=view("lidx", max(info["L_pad"], 1)),
             block_tables=tables, layer_caches=self.storage.layer_caches, page_size=self.page_size,
-            max_q_len=info["max_q"], host=host, attention_plans=plans, logits_all=info["logits_all"])
+            max_q_len=info["max_q"], host=host, attention_plans=plans, logits_all=info["logits_all"],
+            padded=info.get("padded", False))
 
     # ------------------------------------------------------------------ the step
     @torch.no_grad()
@@ -286,7 +304,11 @@ class ModelRunner:
         override, self.next_ids_override = self.next_ids_override, None
         key = self._graph_key(items)
         if key is not None:
-            return self._graph_step(items, key, override)
+            try:
+                return self._graph_step(items, key, override)
+            except PlanCapacityError:
+                if key[0] != "mixed":
+                    raise                # (a step that does not fit its mixed graph's capacity runs as launches)
         pk, host, info = self._gather(items)
         dev = self._upload(pk)
         self._override_ids(dev, override)
@@ -296,6 +318,12 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ CUDA graphs for decode
     MAX_PORTION_GRAPHS = 4
+    # Steps of mixed items (portions beside decoded tokens, several short prompts) of few tokens take less time
+    # on the device than their launches take on the host (about 220 launches, 3 ms): they replay a graph per
+    # 64 tokens, captured with spare capacity for requests, wanted rows and attention work items.
+    MIXED_GRAPH_TOKENS = 512
+    MIXED_GRAPH_SEQS = 64
+    MAX_MIXED_GRAPHS = 8
 
     def _graph_key(self, items: list[StepItem]):
         """The captured graph this step can replay, or None.  Decode-only steps (every request
@@ -330,6 +358,16 @@ class ModelRunner:
                 captured = sum(1 for k in self._graphs if k[0] == "portion")
                 if captured < self.MAX_PORTION_GRAPHS and (n == self.config.max_num_batched_tokens or seen >= 2):
                     return key
+        T = sum(it.num_new_tokens for it in items)
+        if (self.mixed_graphs and T <= self.MIXED_GRAPH_TOKENS and len(items) <= self.MIXED_GRAPH_SEQS
+                and sum(len(it.want) for it in items) <= self.MIXED_GRAPH_SEQS):
+            key = ("mixed", -(-T // 64) * 64)
+            if key in self._graphs:
+                return key
+            seen = self._portion_seen.get(key, 0) + 1
+            self._portion_seen[key] = seen
+            if seen >= 2 and sum(1 for k in self._graphs if k[0] == "mixed") < self.MAX_MIXED_GRAPHS:
+                return key
         return None
 
     def _table_stride(self) -> int:
@@ -346,13 +384,17 @@ class ModelRunner:
             pass                                        # the packed metadata of the last step was patched in place
         else:
             pad = key[1] if key[0] == "decode" else None
-            pk, host, info = self._gather(items, pad_to=pad, table_stride=self._table_stride())
+            mixed = (key[1], self.MIXED_GRAPH_SEQS) if key[0] == "mixed" else None
+            pk, host, info = self._gather(items, pad_to=pad, table_stride=self._table_stride(), pad_mixed=mixed)
             if entry is None:
                 entry = self._capture(key, pk, host, info)
                 entry.plan_shapes = self._plan_shapes(info["plans"])
             if pk.size != entry.size or self._plan_shapes(info["plans"]) != entry.plan_shapes:
+                if mixed is not None:
+                    raise PlanCapacityError(f"the plan of this step differs from the one graph {key} was captured with")
                 raise RuntimeError("metadata layout or attention plan changed between capture and replay of "
                                    f"graph {key}: the captured kernels would read it wrongly")
+            entry.wanted = info["L"]
             packed = np.zeros(pk.size, np.int32)
             for _, off, data in pk.sections:
                 packed[off:off + data.size] = data
@@ -371,6 +413,8 @@ class ModelRunner:
         self.graph_launches += entry.launches
         if entry.logits is None:
             return None
+        if key[0] == "mixed":
+            return entry.logits[:entry.wanted] if entry.wanted else None
         return entry.logits[:len(items)] if key[0] == "decode" else entry.logits
 
     @staticmethod

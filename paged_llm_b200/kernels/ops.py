@@ -416,12 +416,13 @@ class CudaOps:
                                         self.MAX_CLUSTER if self.cluster_attention else 0, self.CLUSTER_KEYS, max_context)
 
     def plan_attention(self, q_lens, k_lens, group_size, num_kv_heads, window, head_dim, pad_requests=None,
-                       fixed_capacity=False) -> dict:
+                       fixed_capacity=False, pad_tokens=None) -> dict:
         return planning.plan_attention(
             q_lens, k_lens, group_size, num_kv_heads, window, small_rows=self.SMALL_ROWS,
             large_rows=self._large_rows(head_dim), min_split_keys=self.MIN_SPLIT_KEYS, num_sms=self.num_sms,
             max_splits=self.MAX_SPLITS, pad_requests=pad_requests, fixed_capacity=fixed_capacity,
-            cluster_max=self.MAX_CLUSTER if self.cluster_attention else 0, long_keys=self.CLUSTER_KEYS)
+            cluster_max=self.MAX_CLUSTER if self.cluster_attention else 0, long_keys=self.CLUSTER_KEYS,
+            pad_tokens=pad_tokens)
 
     def _scratch_for(self, floats: int) -> torch.Tensor:
         """Scratch for split partials.  Grown by allocating anew and keeping the
@@ -474,7 +475,7 @@ class CudaOps:
         out = torch.empty((T, nh * d), dtype=qkv.dtype, device=self.device)
         p = AttnParams()
         real = sum(ctx.host.q_lens)
-        if T > real:
+        if T > real or getattr(ctx, "padded", False):
             # Rows that pad the step to the size of its graph.  The split-context kernels zero them themselves
             # (a fill kernel between two kernels of a layer would keep them from overlapping: 0.97 against 0.92 ms
             # per step at 12 requests); a step with large items too is not padded in practice and gets the fill.

@@ -78,13 +78,27 @@ def _plan_decode(S, S_pad, k_lens, num_kv_heads, min_split_keys, num_sms, max_sp
             "long_context": long_context}
 
 
+class PlanCapacityError(ValueError):
+    """A step does not fit the fixed capacity its plan was asked for."""
+
+
+def large_capacity(num_tokens: int, group_size: int, small_rows: int, large_rows: int) -> int:
+    """An upper bound of the row tiles of the large items of any step of `num_tokens` tokens: every tile but a
+    request's last is full, and a request with a large item has more than `small_rows` rows."""
+    rows = num_tokens * group_size
+    return rows // large_rows + rows // (small_rows + 1) + 1
+
+
 def plan_attention(q_lens, k_lens, group_size: int, num_kv_heads: int, window: int | None, *, small_rows: int,
                    large_rows: int, min_split_keys: int, num_sms: int, max_splits: int = 32,
                    pad_requests: int | None = None, fixed_capacity: bool = False, cluster_max: int = 0,
-                   long_keys: int = 0) -> dict:
+                   long_keys: int = 0, pad_tokens: int | None = None) -> dict:
+    """`pad_tokens` (with `fixed_capacity`, for a step of mixed items that replays a captured graph): both lists
+    get the capacity of any step of that many tokens and `pad_requests` requests, filled up with items of
+    request -1 that the kernels skip."""
     S = len(q_lens)
     S_pad = pad_requests or S
-    if S and max(q_lens) == 1 and group_size <= small_rows and not window:
+    if pad_tokens is None and S and max(q_lens) == 1 and group_size <= small_rows and not window:
         return _plan_decode(S, S_pad, k_lens, num_kv_heads, min_split_keys, num_sms, max_splits, fixed_capacity,
                             cluster_max, long_keys)
     small_ids = [s for s in range(S) if q_lens[s] * group_size <= small_rows]
@@ -117,14 +131,25 @@ def plan_attention(q_lens, k_lens, group_size: int, num_kv_heads: int, window: i
     small_arr = np.array(small, np.int32).reshape(-1, 4)
     if fixed_capacity:
         cap = S_pad * want
+        if len(small_arr) > cap:
+            raise PlanCapacityError(f"{len(small_arr)} small items for a capacity of {cap}")
         pad = np.full((cap - len(small_arr), 4), -1, np.int32)
         small_arr = np.concatenate([small_arr, pad]) if len(pad) else small_arr
     large_arr = np.array([(s, t, 0, 1) for _, s, t in large], np.int32).reshape(-1, 4)
+    small_tokens = int(scratch_base) if not fixed_capacity else int(S_pad)
+    if pad_tokens is not None and fixed_capacity:
+        cap = large_capacity(pad_tokens, group_size, small_rows, large_rows)
+        if len(large_arr) > cap or sum(q_lens) > pad_tokens:
+            raise PlanCapacityError(f"{len(large_arr)} large items for a capacity of {cap}")
+        large_arr = np.concatenate([large_arr, np.full((cap - len(large_arr), 4), -1, np.int32)])
+        small_tokens = int(S_pad) * max(1, small_rows // group_size)       # a small item may bring several tokens
+        if scratch_base > small_tokens:
+            raise PlanCapacityError(f"{scratch_base} tokens of small items for {small_tokens} scratch rows")
     return {
         "small": small_arr.reshape(-1),
         "large": large_arr.reshape(-1),
         "splits": splits.reshape(-1),
         "max_splits": int(want),
-        "num_small_tokens": int(scratch_base) if not fixed_capacity else int(S_pad),
+        "num_small_tokens": small_tokens,
         "long_context": False,
     }

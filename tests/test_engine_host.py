@@ -436,3 +436,27 @@ def test_fork_gives_the_child_a_copy_of_the_state(tmp_path):
         toks.append(tok)
     sched.abort(root.seq_id)
     assert cm.num_free_state_slots == cm.num_state_slots and cm.num_free_blocks == 32
+
+
+def test_plan_of_a_mixed_step_with_fixed_capacity():
+    """The work lists of a step of mixed items that replays a graph: their sizes depend on the token and request
+    capacity only, items beyond the step's own are request -1, and a step that does not fit is refused."""
+    from paged_llm_b200.kernels.plan import PlanCapacityError, large_capacity, plan_attention
+    kw = dict(small_rows=16, large_rows=128, min_split_keys=128, num_sms=148, pad_requests=64, fixed_capacity=True,
+              pad_tokens=256)
+    sizes = set()
+    for q_lens, k_lens in (([1, 1, 100], [30, 500, 100]), ([2] * 20 + [7, 9], [50] * 20 + [7, 300]), ([200], [1200]),
+                           ([1] * 64, [9] * 64)):
+        plan = plan_attention(q_lens, k_lens, 8, 4, None, **kw)
+        small, large = plan["small"].reshape(-1, 4), plan["large"].reshape(-1, 4)
+        sizes.add((small.shape[0], large.shape[0], plan["max_splits"], plan["num_small_tokens"]))
+        assert large.shape[0] == large_capacity(256, 8, 16, 128)
+        real_large = large[large[:, 0] >= 0]
+        want_tiles = sum(-(-q * 8 // 128) for q in q_lens if q * 8 > 16)
+        assert len(real_large) == want_tiles and (large[len(real_large):, 0] == -1).all()
+        real_small = small[small[:, 0] >= 0]
+        assert sorted(set(real_small[:, 0].tolist())) == [s for s, q in enumerate(q_lens) if q * 8 <= 16]
+        assert plan["num_small_tokens"] >= sum(q for q in q_lens if q * 8 <= 16)
+    assert len(sizes) == 1, "the capacity must not depend on the step's items"
+    with pytest.raises(PlanCapacityError):
+        plan_attention([300], [300], 8, 4, None, **kw)                     # more tokens than the graph holds

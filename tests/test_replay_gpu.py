@@ -118,8 +118,34 @@ def test_repeated_portions_replay_a_graph(folders, dtype):
         steps.append({"step": i, "entries": [{"id": "a", "tokens": toks[64 * i:64 * (i + 1)], "want": [63]}], "end": []})
     steps.append({"step": 5, "entries": [{"id": "a", "tokens": toks[320:], "want": list(range(7))}], "end": ["a"]})
     outputs, rp = replay(folders["C"], dtype, steps, 384)
-    assert rp.runner.num_graph_steps == 4 and ("portion", 64, 1) in rp.runner._graphs
+    # (the portions from the second on; the tail of 7 tokens may replay a graph of small mixed steps as well)
+    assert rp.runner.num_graph_steps >= 4 and ("portion", 64, 1) in rp.runner._graphs
     want = plain_logits(folders["C"], toks)
     got = np.concatenate([outputs[i] for i in range(6)])
     rows = [64 * i + 63 for i in range(5)] + list(range(320, 327))
     assert_logits_close(got, want[rows], dtype, "portion graph")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_small_mixed_steps_replay_graphs(folders, name, dtype):
+    """Steps of mixed items of few tokens (portions beside decoded tokens, cut anywhere) replay graphs captured
+    with spare capacity for tokens, requests, wanted rows and attention work items: the same logits as the
+    plain model and as the run that launches every kernel, in both precisions."""
+    hf, _ = TINIES[name]
+    reqs = requests_for(hf["vocab_size"], LENGTHS[name], seed=ord(name) + 1)
+    steps, max_tokens = schedules.mixed(reqs)
+    block = 8 if name == "B" else 16
+    outputs, rp = replay(folders[name], dtype, steps, max_tokens, block_size=block)
+    mixed = [k for k in rp.runner._graphs if k[0] == "mixed"]
+    assert mixed and rp.runner.num_graph_steps > len(steps) // 3, "the mixed steps did not replay graphs"
+    got = schedules.collect(steps, outputs)
+    for rid, toks in reqs.items():
+        assert_logits_close(got[rid], plain_logits(folders[name], toks), dtype, f"mixed graphs/{name}/{rid}")
+    eager, rp_e = replay(folders[name], dtype, steps, max_tokens, block_size=block, enforce_eager=True)
+    assert rp_e.runner.num_graph_steps == 0
+    for k in outputs:
+        if dtype == "float32":
+            np.testing.assert_allclose(outputs[k], eager[k], rtol=0, atol=2e-5 * max(1.0, float(np.abs(eager[k]).max())))
+        else:
+            assert_bf16_close_to_f32(outputs[k], eager[k], f"graph against launches, step {k}")

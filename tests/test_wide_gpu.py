@@ -179,5 +179,7 @@ def test_decode_steps_of_many_requests(folders, n_requests):
         for k in got16:
             assert_bf16_close_to_f32(got16[k], eager[k], f"graph against eager, step {k}")
     else:
-        assert rp.runner.num_graph_steps == 0
+        # more requests than the largest bucket: the decode steps run as launches (the short prompts in front of
+        # them may replay graphs of small mixed steps)
+        assert not any(k[0] == "decode" for k in rp.runner._graphs)
     compare_three_ways(folders("T"), f"decode{n_requests}", reqs, steps, got32, got16)

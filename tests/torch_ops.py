@@ -115,9 +115,10 @@ class TorchOps:
 
     # ---- attention -------------------------------------------------------------
     def plan_attention(self, q_lens, k_lens, group_size, num_kv_heads, window, head_dim, pad_requests=None,
-                       fixed_capacity=False):
+                       fixed_capacity=False, pad_tokens=None):
         return plan_attention(q_lens, k_lens, group_size, num_kv_heads, window, small_rows=16, large_rows=64,
-                              min_split_keys=128, num_sms=4, pad_requests=pad_requests, fixed_capacity=fixed_capacity)
+                              min_split_keys=128, num_sms=4, pad_requests=pad_requests, fixed_capacity=fixed_capacity,
+                              pad_tokens=pad_tokens)
 
     def paged_attention(self, qkv, nh, nkv, d, kv, block_table, ctx, scale, window, softcap=None, slopes=None):
         self._count("paged_attention")
