@@ -100,6 +100,8 @@ class ModelRunner:
         self.use_graphs = ((not config.enforce_eager) and self.device.type == "cuda"
                            and getattr(ops, "supports_graphs", False) and getattr(model, "capturable", True))
         self.mixed_graphs = self.use_graphs and os.environ.get("PAGED_LLM_B200_NO_MIXED_GRAPHS") is None
+        # request capacity of those graphs: the engine's limit, rounded up to a batch bucket
+        self.MIXED_GRAPH_SEQS = next((b for b in self.GRAPH_BUCKETS if b >= config.max_num_seqs), self.GRAPH_BUCKETS[-1])
         self.num_graph_steps = 0
         self.num_eager_steps = 0
         self.graph_launches = 0            # kernels of this package launched by graph replays
@@ -321,8 +323,8 @@ class ModelRunner:
     # Steps of mixed items (portions beside decoded tokens, several short prompts) of few tokens take less time
     # on the device than their launches take on the host (about 220 launches, 3 ms): they replay a graph per
     # 64 tokens, captured with spare capacity for requests, wanted rows and attention work items.
-    MIXED_GRAPH_TOKENS = 512
-    MIXED_GRAPH_SEQS = 64
+    MIXED_GRAPH_TOKENS = 512         # beyond about 600 tokens such a step takes the device longer than the host
+    MIXED_GRAPH_SEQS = 64            # (set per runner from max_num_seqs)
     MAX_MIXED_GRAPHS = 8
 
     def _graph_key(self, items: list[StepItem]):
