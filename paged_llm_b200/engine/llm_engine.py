@@ -318,8 +318,8 @@ class LLMEngine:
 
     def warm_up(self, max_batch: int | None = None) -> int:
         """Captures the decode graphs of the batch-size buckets up to `max_batch` (default:
-        `max_num_seqs`) by running throw-away requests of one prompt token, so that no request
-        pays for a capture later (15-150 ms each when a bucket is first seen).  Not in the
+        `max_num_seqs`) and the graphs of small mixed steps by running throw-away requests, so that
+        no request pays for a capture later (15-150 ms each when a bucket is first seen).  Not in the
         reference.  Returns the number of graphs held afterwards; the cache is as before."""
         if self.has_unfinished_requests:
             raise RuntimeError("warm_up needs an idle engine")
@@ -335,6 +335,24 @@ class LLMEngine:
                     self.step()
                 for i in ids:
                     self._seqs.pop(i, None)
+            # the graphs of small mixed steps: two prompts that fill a bucket of tokens together, twice each (a
+            # graph is captured when its bucket comes the second time), with tokens of their own so that no
+            # prefix is found in the cache
+            if getattr(self.runner, "mixed_graphs", False) and self.config.max_num_seqs >= 2:
+                one = SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True)
+                vocab = self.model_config.vocab_size
+                limit = min(self.runner.MIXED_GRAPH_TOKENS, self.config.max_num_batched_tokens,
+                            self.config.max_model_len - 2)
+                for n, t in enumerate(range(64, limit + 1, 64)):
+                    if sum(1 for k in self.runner._graphs if k[0] == "mixed") >= self.runner.MAX_MIXED_GRAPHS:
+                        break
+                    for again in range(2):
+                        tok = (2 * n + again + 1) % vocab
+                        ids = [self.add_request([tok] * (t - 1), one), self.add_request([tok], one)]
+                        while self.has_unfinished_requests:
+                            self.step()
+                        for i in ids:
+                            self._seqs.pop(i, None)
         finally:
             self.stats = stats
         return len(self.runner._graphs)

@@ -87,13 +87,15 @@ def test_greedy_generation_bfloat16_follows_the_plain_model(folders):
 def test_warm_up_captures_the_decode_graphs(folders):
     from paged_llm_b200 import LLMEngine, SamplingParams
     eng = LLMEngine(folders["A"], dtype="float32", block_size=16, num_gpu_blocks=32, max_model_len=128, max_num_seqs=8)
-    assert eng.warm_up() == 4 and set(eng.runner._graphs) == {("decode", b) for b in (1, 2, 4, 8)}
+    # the decode buckets up to max_num_seqs, and the one bucket of small mixed steps that fits max_model_len=128
+    want = {("decode", b) for b in (1, 2, 4, 8)} | {("mixed", 64)}
+    assert eng.warm_up() == len(want) and set(eng.runner._graphs) == want
     assert eng.block_manager.num_free_blocks == 32 and eng.stats.num_steps == 0
     hf, _ = TINIES["A"]
     prompt = random_tokens(hf["vocab_size"], 9, 3)
     out = eng.generate([prompt], SamplingParams(temperature=0.0, max_tokens=6))[0]
     assert out.token_ids == plain_greedy(folders["A"], prompt, 6)
-    assert len(eng.runner._graphs) == 4
+    assert set(eng.runner._graphs) == want
 
 
 def test_decoding_across_the_context_classes(folders):
