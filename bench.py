@@ -529,7 +529,9 @@ def run_ours(args) -> dict:
         pre_tokens = args.prefill_tokens if args.only in ("prefill", "mixed") and args.prefill_tokens else PREFILL_TOKENS
         max_len = max(prompt_len + args.steps + args.warmup + DECODE_LEN, pre_tokens) + 64
         if args.only == "ragged":
-            max_len = RAGGED_PROMPTS[1] + RAGGED_OUTPUTS[1] + 64
+            p_hi = int(args.prompt_range.split(",")[1]) if args.prompt_range else RAGGED_PROMPTS[1]
+            o_hi = int(args.output_range.split(",")[1]) if args.output_range else RAGGED_OUTPUTS[1]
+            max_len = max(p_hi, 512) + max(o_hi, 32) + 64          # (the untimed first requests are up to 512 + 32 long)
         seqs = max(args.batch, 64) if prompt_len == PROMPT_LEN else args.batch
         if args.only == "mixed":
             max_len = max(max_len, prompt_len + 64, pre_tokens + 64)
@@ -545,9 +547,13 @@ def run_ours(args) -> dict:
         ragged_generate(engine, 8, (128, 512), (16, 32), seed=1)          # untimed: first-use costs
         # untimed too: the same workload with other lengths and tokens, so that the graphs of its batch buckets
         # and context classes exist (a server runs for longer than its first two seconds)
-        ragged_generate(engine, 64, RAGGED_PROMPTS, RAGGED_OUTPUTS, seed=1)
+        n_req = args.requests
+        p_range = tuple(int(v) for v in args.prompt_range.split(",")) if args.prompt_range else RAGGED_PROMPTS
+        o_range = tuple(int(v) for v in args.output_range.split(",")) if args.output_range else RAGGED_OUTPUTS
+        ragged_generate(engine, n_req, p_range, o_range, seed=1)
         return {"only": "ragged", "size": args.size, "layers": cfg.num_hidden_layers,
-                **ragged_generate(engine, 64, RAGGED_PROMPTS, RAGGED_OUTPUTS, seed=0)}
+                "prompt_range": list(p_range), "output_range": list(o_range),
+                **ragged_generate(engine, n_req, p_range, o_range, seed=0)}
     if args.only == "decode":            # a short run of one part, for profilers and other context lengths
         ms, launches, ctx_mid = device_decode_loop(engine, B, args.steps, args.warmup, prompt_len)
         step_bytes = engine.model.weight_bytes_per_step() + B * ctx_mid * (engine.kv_cache.page_bytes() // BLOCK_SIZE)
@@ -700,6 +706,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the named size (reported in config)")
     ap.add_argument("--chunk", type=int, default=None,
                     help="with --only prefill: the prompt goes through LLMEngine.generate in portions of this many tokens")
+    ap.add_argument("--requests", type=int, default=64, help="with --only ragged: number of requests")
+    ap.add_argument("--prompt-range", default=None, help="with --only ragged: LO,HI prompt lengths (default 128,4096)")
+    ap.add_argument("--output-range", default=None, help="with --only ragged: LO,HI output lengths (default 64,512)")
     ap.add_argument("--kernel-times", action="store_true",
                     help="with --only decode or --only prefill: add the device time of every kernel inside the replayed steps")
     ap.add_argument("--only", choices=["decode", "prefill", "ragged", "mixed", "validate"], default=None,
