@@ -137,6 +137,8 @@ def test_small_mixed_steps_replay_graphs(folders, name, dtype):
     steps, max_tokens = schedules.mixed(reqs)
     block = 8 if name == "B" else 16
     outputs, rp = replay(folders[name], dtype, steps, max_tokens, block_size=block)
+    if not rp.runner.mixed_graphs:
+        pytest.skip("graphs of small mixed steps are switched off")
     mixed = [k for k in rp.runner._graphs if k[0] == "mixed"]
     assert mixed and rp.runner.num_graph_steps > len(steps) // 3, "the mixed steps did not replay graphs"
     got = schedules.collect(steps, outputs)
