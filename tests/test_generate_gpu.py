@@ -303,3 +303,42 @@ def test_command_line(folders):
     for w in want:
         assert str(w) in proc.stdout, proc.stdout
     assert "steps=" in proc.stdout and "preemptions=0" in proc.stdout
+
+
+def test_random_arrivals_with_graphs_and_as_launches(folders):
+    """Sixty requests of random lengths arriving in random order between steps, with a small token budget and few
+    pages, so that most steps are mixed ones and some requests are preempted: greedy tokens in float32 with every
+    kind of graph (decode buckets, recurring portions, small mixed steps) against the engine that launches every
+    kernel, and against the plain model for a few of them."""
+    import random
+    from paged_llm_b200 import LLMEngine, SamplingParams
+    hf, _ = TINIES["A"]
+    rng = random.Random(4)
+    work = [(random_tokens(hf["vocab_size"], rng.randint(1, 60), 100 + i), rng.randint(1, 24)) for i in range(60)]
+    arrive = sorted(rng.randint(0, 40) for _ in work)          # the step before which each request arrives
+    results = {}
+    for eager in (False, True):
+        eng = LLMEngine(folders["A"], dtype="float32", block_size=16, num_gpu_blocks=24, max_model_len=128,
+                        max_num_seqs=8, max_num_batched_tokens=64, enforce_eager=eager)
+        ids, step, nxt, done = {}, 0, 0, {}
+        while nxt < len(work) or eng.has_unfinished_requests:
+            while nxt < len(work) and arrive[nxt] <= step:
+                prompt, n = work[nxt]
+                ids[eng.add_request(prompt, SamplingParams(temperature=0.0, max_tokens=n, ignore_eos=True))] = nxt
+                nxt += 1
+            for o in eng.step():
+                if o.new_token is not None:
+                    done.setdefault(ids[o.seq_id], []).append(o.new_token)
+            step += 1
+        results[eager] = done
+        assert eng.block_manager.num_free_blocks == 24
+        if not eager:
+            kinds = {k[0] for k in eng.runner._graphs}
+            assert "decode" in kinds and (not eng.runner.mixed_graphs or "mixed" in kinds), kinds
+            assert eng.runner.num_graph_steps > eng.runner.num_eager_steps
+        else:
+            assert eng.runner.num_graph_steps == 0
+    assert results[False] == results[True]
+    for i in (0, 17, 59):
+        prompt, n = work[i]
+        assert results[True][i] == plain_greedy(folders["A"], prompt, n)
