@@ -472,6 +472,39 @@ def chunked_prefill(engine, tokens: int, iters: int = 3, warmup: int = 2):
     return statistics.median(times)
 
 
+def sampling_times(args) -> dict:
+    """Microseconds per call of the sampler's kernels on `--batch` rows of a vocabulary of the named size: the
+    calls are issued back to back (each with its one copy of parameters from pinned memory) and timed with CUDA
+    events, so a call that takes the device less than the host takes to issue it shows the host's time."""
+    import numpy as np
+    import torch
+    from paged_llm_b200.kernels.ops import CudaOps
+
+    ops = CudaOps(torch.device("cuda:0"))
+    rows, vocab = args.batch, SIZES[args.size]["vocab_size"]
+    logits = torch.randn(rows, vocab, device="cuda") * 2.0
+
+    def timed(fn, n=50):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(n):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        return round(start.elapsed_time(end) / n * 1e3, 1)
+
+    out = {"only": "sample", "size": args.size, "rows": rows, "vocab": vocab, "unit": "us per call",
+           "argmax": timed(lambda: ops.argmax(logits))}
+    for name, k, p in (("temperature", 0, 1.0), ("top_k_50", 50, 1.0), ("top_p_0.9", 0, 0.9), ("top_k_50_top_p_0.9", 50, 0.9)):
+        arrays = (np.full(rows, 0.7, np.float32), np.full(rows, k, np.int32), np.full(rows, p, np.float32),
+                  np.arange(rows, dtype=np.uint64), np.arange(rows, dtype=np.uint64))
+        out[name] = timed(lambda: ops.sample(logits, *arrays))
+    return out
+
+
 def validate(args) -> dict:
     """The float32 validation run at the benchmark's layer sizes: the same trace (a 2,048-token
     portion, 32 decoded tokens, portions of changing size, a mixed batch) through the bfloat16 engine
@@ -523,6 +556,8 @@ def run_ours(args) -> dict:
     peaks = load_peaks()
     if args.only == "validate":
         return validate(args)
+    if args.only == "sample":
+        return sampling_times(args)
     with tempfile.TemporaryDirectory() as folder:
         cfg, full_layers = make_model(folder, args.size, args.layers)
         prompt_len = args.context if args.only in ("decode", "mixed") and args.context else PROMPT_LEN
@@ -711,10 +746,11 @@ def main() -> int:
     ap.add_argument("--output-range", default=None, help="with --only ragged: LO,HI output lengths (default 64,512)")
     ap.add_argument("--kernel-times", action="store_true",
                     help="with --only decode or --only prefill: add the device time of every kernel inside the replayed steps")
-    ap.add_argument("--only", choices=["decode", "prefill", "ragged", "mixed", "validate"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "ragged", "mixed", "validate", "sample"], default=None,
                     help="run only the decode loop, only the prefill step, the ragged serving workload through "
                          "LLMEngine.generate, one mixed step (--batch decoding requests of --context tokens beside one "
-                         "portion of --prefill-tokens), or the float32 validation run, and print a short line")
+                         "portion of --prefill-tokens), the float32 validation run, or the sampler's kernels on --batch rows, and print "
+                         "a short line")
     args = ap.parse_args()
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
         if int(os.environ.get("RANK", "0")) == 0:

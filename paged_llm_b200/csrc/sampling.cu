@@ -226,8 +226,8 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float* __restrict__ 
 
     const bool use_k = top_k > 0 && top_k < V, use_p = top_p < 1.0f;
     if (use_k || use_p) {
-        __shared__ unsigned int cnt_all[256];
-        __shared__ unsigned long long mass[256];
+        __shared__ unsigned int cnt_all[256], warp_cnt[8];
+        __shared__ unsigned long long mass[256], warp_mass[8];
         __shared__ unsigned int pick_k, pick_p, need_k;
         __shared__ unsigned long long above_p, limit_p;
         if (tid == 0) {
@@ -325,16 +325,35 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float* __restrict__ 
                 mass[tid] = p0 + (p1 << 11) + (p2 << 22);
             }
             __syncthreads();
-            // inclusive suffix sums over the bins (bin b: everything in bins b..255), in place
-            for (int off = 1; off < 256; off <<= 1) {
+            // inclusive suffix sums over the bins (bin b: everything in bins b..255), in place: by shuffles inside
+            // the eight warps that hold the bins, then the totals of the warps behind
+            {
                 unsigned int c = 0u;
                 unsigned long long m = 0ull;
+                const int lane = tid & 31, w = tid >> 5;
                 if (tid < 256) {
-                    c = cnt_all[tid] + (tid + off < 256 ? cnt_all[tid + off] : 0u);
-                    m = mass[tid] + (tid + off < 256 ? mass[tid + off] : 0ull);
+                    c = cnt_all[tid];
+                    m = mass[tid];
+#pragma unroll
+                    for (int off = 1; off < 32; off <<= 1) {
+                        const unsigned int c2 = __shfl_down_sync(0xffffffffu, c, off);
+                        const unsigned long long m2 = __shfl_down_sync(0xffffffffu, m, off);
+                        if (lane + off < 32) {
+                            c += c2;
+                            m += m2;
+                        }
+                    }
+                    if (lane == 0) {
+                        warp_cnt[w] = c;
+                        warp_mass[w] = m;
+                    }
                 }
                 __syncthreads();
                 if (tid < 256) {
+                    for (int k = w + 1; k < 8; ++k) {
+                        c += warp_cnt[k];
+                        m += warp_mass[k];
+                    }
                     cnt_all[tid] = c;
                     mass[tid] = m;
                 }
