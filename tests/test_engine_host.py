@@ -273,12 +273,12 @@ class PlanningOps(TorchOps):
                                self.CLUSTER_KEYS, max_context)
 
     def plan_attention(self, q_lens, k_lens, group_size, num_kv_heads, window, head_dim, pad_requests=None,
-                       fixed_capacity=False):
+                       fixed_capacity=False, pad_tokens=None):
         from paged_llm_b200.kernels.plan import plan_attention
         return plan_attention(q_lens, k_lens, group_size, num_kv_heads, window, small_rows=16, large_rows=64,
                               min_split_keys=self.MIN_SPLIT_KEYS, num_sms=self.num_sms, max_splits=self.MAX_SPLITS,
                               pad_requests=pad_requests, fixed_capacity=fixed_capacity,
-                              cluster_max=self.MAX_CLUSTER, long_keys=self.CLUSTER_KEYS)
+                              cluster_max=self.MAX_CLUSTER, long_keys=self.CLUSTER_KEYS, pad_tokens=pad_tokens)
 
 
 def runner_with_two_plan_keys(folder, max_tokens=8192):
@@ -460,3 +460,41 @@ def test_plan_of_a_mixed_step_with_fixed_capacity():
     assert len(sizes) == 1, "the capacity must not depend on the step's items"
     with pytest.raises(PlanCapacityError):
         plan_attention([300], [300], 8, 4, None, **kw)                     # more tokens than the graph holds
+
+
+def test_small_mixed_steps_get_a_graph_key_and_metadata_of_one_size(folders):
+    """Steps of mixed items: the key is the bucket of 64 tokens (from the second time on), every step of a bucket
+    packs metadata of the same size whatever its items, padding is what the kernels skip (request -1, no keys),
+    and a step that does not fit is refused so that it runs as launches."""
+    from paged_llm_b200.kernels.plan import PlanCapacityError
+    rp, runner = runner_with_two_plan_keys(folders["A"], max_tokens=64 * 1024)
+    runner.mixed_graphs = True
+
+    def items_of(specs):
+        out = []
+        for context, new, want in specs:
+            seq = Sequence([1] * (context + new), SamplingParams())
+            seq.num_computed_tokens = context
+            seq.block_tables = [list(range(-(-(context + new) // 16)))]
+            out.append(StepItem(seq, new, want))
+        return out
+
+    a = items_of([(300, 1, (0,)), (20, 1, (0,)), (0, 90, (89,))])              # 92 tokens: bucket 128
+    b = items_of([(0, 100, ()), (0, 7, (6,)), (700, 2, (1,)), (5, 1, (0,))])   # 110 tokens: bucket 128
+    c = items_of([(0, 200, (199,)), (50, 1, (0,))])                            # bucket 256
+    assert runner._graph_key(a) is None, "a bucket is captured when it comes the second time"
+    assert runner._graph_key(b) == ("mixed", 128) and runner._graph_key(c) is None
+    assert runner._graph_key(items_of([(0, 600, (599,)), (50, 1, (0,))])) is None          # more than 512 tokens
+    sizes = set()
+    for items in (a, b):
+        pk, host, info = runner._gather(items, table_stride=runner._table_stride(), pad_mixed=(128, runner.MIXED_GRAPH_SEQS))
+        sizes.add((pk.size, str(runner._plan_shapes(info["plans"]))))
+        sec = {name: data for name, _, data in pk.sections}
+        T, S = sum(i.num_new_tokens for i in items), len(items)
+        assert info["T"] == 128 and info["S"] == runner.MIXED_GRAPH_SEQS and info["padded"] and not info["logits_all"]
+        assert (sec["tseq"][T:] == -1).all() and (sec["tseq"][:T] >= 0).all()
+        assert (sec["cu"][S:] == T).all() and (sec["klen"][S:] == 0).all()
+        assert sec["lidx"].size == runner.MIXED_GRAPH_SEQS and info["L"] == sum(len(i.want) for i in items)
+    assert len(sizes) == 1, "every step of a bucket must pack metadata of the same layout"
+    with pytest.raises(PlanCapacityError):
+        runner._gather(c, table_stride=runner._table_stride(), pad_mixed=(128, runner.MIXED_GRAPH_SEQS))
