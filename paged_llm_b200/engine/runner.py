@@ -321,11 +321,13 @@ class ModelRunner:
     # ------------------------------------------------------------------ CUDA graphs for decode
     MAX_PORTION_GRAPHS = 4
     # Steps of mixed items (portions beside decoded tokens, several short prompts) of few tokens take less time
-    # on the device than their launches take on the host (about 220 launches, 3 ms): they replay a graph per
-    # 64 tokens, captured with spare capacity for requests, wanted rows and attention work items.
-    MIXED_GRAPH_TOKENS = 512         # beyond about 600 tokens such a step takes the device longer than the host
+    # on the device than their launches take on the host (about 220 launches, 3 ms), or little more: they replay a
+    # graph per 64 tokens, captured with spare capacity for requests, wanted rows and attention work items.
+    # (measured beside 63 decoding requests, ms per step as a graph / as launches: 448 tokens 2.46 / 3.43, 768 tokens
+    # 2.99 / 3.47, 960 tokens 3.39 / 3.70; beyond that the device takes so much longer than the host that launches do)
+    MIXED_GRAPH_TOKENS = 1024
     MIXED_GRAPH_SEQS = 64            # (set per runner from max_num_seqs)
-    MAX_MIXED_GRAPHS = 8
+    MAX_MIXED_GRAPHS = 16
 
     def _graph_key(self, items: list[StepItem]):
         """The captured graph this step can replay, or None.  Decode-only steps (every request

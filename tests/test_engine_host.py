@@ -484,7 +484,7 @@ def test_small_mixed_steps_get_a_graph_key_and_metadata_of_one_size(folders):
     c = items_of([(0, 200, (199,)), (50, 1, (0,))])                            # bucket 256
     assert runner._graph_key(a) is None, "a bucket is captured when it comes the second time"
     assert runner._graph_key(b) == ("mixed", 128) and runner._graph_key(c) is None
-    assert runner._graph_key(items_of([(0, 600, (599,)), (50, 1, (0,))])) is None          # more than 512 tokens
+    assert runner._graph_key(items_of([(0, 1100, (1099,)), (50, 1, (0,))])) is None        # more than 1,024 tokens
     sizes = set()
     for items in (a, b):
         pk, host, info = runner._gather(items, table_stride=runner._table_stride(), pad_mixed=(128, runner.MIXED_GRAPH_SEQS))

@@ -173,7 +173,8 @@ def test_decode_steps_of_many_requests(folders, n_requests):
     got16, rp = replay(folders("T"), "bfloat16", steps, max_tokens, max_num_seqs=n_requests)
     if n_requests <= rp.runner.GRAPH_BUCKETS[-1]:
         bucket = next(b for b in rp.runner.GRAPH_BUCKETS if b >= n_requests)
-        assert any(k[:2] == ("decode", bucket) for k in rp.runner._graphs) and rp.runner.num_graph_steps == 3
+        # (the three decode steps; a step of prompts in front of them may replay a graph of small mixed steps too)
+        assert any(k[:2] == ("decode", bucket) for k in rp.runner._graphs) and rp.runner.num_graph_steps >= 3
         eager, rp_e = replay(folders("T"), "bfloat16", steps, max_tokens, max_num_seqs=n_requests, enforce_eager=True)
         assert rp_e.runner.num_graph_steps == 0
         for k in got16:
