@@ -70,6 +70,10 @@ class _Graph:
         self.wanted = 0              # rows of `logits` that the last replay asked for (graphs of mixed items)
 
 
+class _NoMemoryForGraph(RuntimeError):
+    """Capturing a graph ran out of device memory."""
+
+
 class _Staging:
     """One pinned host buffer of the metadata ring, with the event of its last copy."""
 
@@ -97,6 +101,7 @@ class ModelRunner:
         self._dev_meta = None
         self._graphs: dict[tuple, object] = {}
         self._portion_seen: dict[tuple, int] = {}
+        self._no_graph: set[tuple] = set()        # keys whose capture ran out of memory
         self.use_graphs = ((not config.enforce_eager) and self.device.type == "cuda"
                            and getattr(ops, "supports_graphs", False) and getattr(model, "capturable", True))
         self.mixed_graphs = self.use_graphs and os.environ.get("PAGED_LLM_B200_NO_MIXED_GRAPHS") is None
@@ -311,6 +316,8 @@ class ModelRunner:
             except PlanCapacityError:
                 if key[0] != "mixed":
                     raise                # (a step that does not fit its mixed graph's capacity runs as launches)
+            except _NoMemoryForGraph:
+                pass                     # (no room to capture this graph: its steps run as launches from now on)
         pk, host, info = self._gather(items)
         dev = self._upload(pk)
         self._override_ids(dev, override)
@@ -337,6 +344,10 @@ class ModelRunner:
         and again)."""
         if not self.use_graphs:          # (off too when a part of the model is not capturable)
             return None
+        key = self._graph_key_of(items)
+        return None if key in self._no_graph else key
+
+    def _graph_key_of(self, items: list[StepItem]):
         if all(it.num_new_tokens == 1 and it.want == (0,) for it in items):
             if len(items) > self.GRAPH_BUCKETS[-1]:
                 return None
@@ -391,7 +402,16 @@ class ModelRunner:
             mixed = (key[1], self.MIXED_GRAPH_SEQS) if key[0] == "mixed" else None
             pk, host, info = self._gather(items, pad_to=pad, table_stride=self._table_stride(), pad_mixed=mixed)
             if entry is None:
-                entry = self._capture(key, pk, host, info)
+                try:
+                    entry = self._capture(key, pk, host, info)
+                except (torch.OutOfMemoryError, RuntimeError) as err:
+                    if not isinstance(err, torch.OutOfMemoryError) and "out of memory" not in str(err).lower():
+                        raise
+                    # a graph keeps its activations for good; when the device has no room left for them the
+                    # step still fits as launches (whose buffers come and go): this key is not tried again
+                    self._no_graph.add(key)
+                    torch.cuda.empty_cache() if self.device.type == "cuda" else None
+                    raise _NoMemoryForGraph(key) from None
                 entry.plan_shapes = self._plan_shapes(info["plans"])
             if pk.size != entry.size or self._plan_shapes(info["plans"]) != entry.plan_shapes:
                 if mixed is not None:

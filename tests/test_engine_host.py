@@ -498,3 +498,22 @@ def test_small_mixed_steps_get_a_graph_key_and_metadata_of_one_size(folders):
     assert len(sizes) == 1, "every step of a bucket must pack metadata of the same layout"
     with pytest.raises(PlanCapacityError):
         runner._gather(c, table_stride=runner._table_stride(), pad_mixed=(128, runner.MIXED_GRAPH_SEQS))
+
+
+def test_a_graph_that_does_not_fit_the_memory_is_given_up_for_launches(folders, monkeypatch):
+    """Capturing a graph that runs out of device memory: the step runs as launches, the key is not tried
+    again, other keys still are."""
+    rp = TraceReplayer(folders["A"], "float32", 256, device="cpu", ops=TorchOps(), block_size=16)
+    runner = rp.runner
+    runner.use_graphs = True
+    calls = []
+
+    def no_room(key, *a, **k):
+        calls.append(key)
+        raise torch.OutOfMemoryError("CUDA out of memory (made up by the test)")
+    monkeypatch.setattr(runner, "_capture", no_room)
+    for step in range(3):
+        out = rp.step({"step": step, "entries": [{"id": "a", "tokens": [5 + step], "want": [0]}], "end": []})
+        assert out is not None and np.isfinite(out).all()
+    assert calls == [("decode", 1)] and ("decode", 1) in runner._no_graph and runner.num_graph_steps == 0
+    assert runner.num_eager_steps == 3
