@@ -341,7 +341,9 @@ class ModelRunner:
         brings one token) replay a graph per batch-size bucket.  A step that is one portion of
         one request replays a graph per portion length, captured when that length is the token
         budget or comes a second time (a prompt cut by the budget brings the same length again
-        and again)."""
+        and again).  Any other step of up to MIXED_GRAPH_TOKENS tokens replays a graph per 64
+        tokens, captured when its bucket comes a second time.  A key whose capture ran out of
+        device memory is not offered again."""
         if not self.use_graphs:          # (off too when a part of the model is not capturable)
             return None
         key = self._graph_key_of(items)
