@@ -184,3 +184,42 @@ def test_decode_steps_of_many_requests(folders, n_requests):
         # them may replay graphs of small mixed steps)
         assert not any(k[0] == "decode" for k in rp.runner._graphs)
     compare_three_ways(folders("T"), f"decode{n_requests}", reqs, steps, got32, got16)
+
+
+def test_random_serving_workload_for_a_few_seconds(folders):
+    """Five seconds of requests arriving at random at the benchmark's widths: prompts of 1 to 1,500 tokens (half of
+    them behind one of three shared prefixes), 1 to 200 output tokens, greedy / temperature / top-k / top-p, 48
+    request slots, a budget of 1,024 tokens and so few pages that requests are preempted.  Nothing raises, no page
+    is lost, no bounded wait in a kernel gives up, and nearly every step replays a graph."""
+    import random
+    import time
+    from paged_llm_b200 import EngineConfig, LLMEngine, SamplingParams
+    hf, _ = WIDES["T"]
+    vocab = hf["vocab_size"]
+    eng = LLMEngine(folders("T"), EngineConfig(dtype="bfloat16", block_size=16, max_model_len=2048, max_num_seqs=48,
+                                               max_num_batched_tokens=1024, enable_prefix_caching=True,
+                                               num_gpu_blocks=1200))
+    eng.warm_up()
+    rng = random.Random(1)
+    prefixes = [[rng.randrange(vocab) for _ in range(rng.randint(16, 750))] for _ in range(3)]
+    t_end, n_req, tokens = time.time() + 5.0, 0, 0
+    while time.time() < t_end or eng.has_unfinished_requests:
+        if time.time() < t_end and rng.random() < 0.2:
+            for _ in range(rng.randint(1, 4)):
+                body = [rng.randrange(vocab) for _ in range(rng.randint(1, 750))]
+                prompt = rng.choice(prefixes) + body if rng.random() < 0.5 else body
+                kind = rng.random()
+                how = dict(temperature=0.0) if kind < 0.5 else dict(temperature=0.8, seed=n_req) if kind < 0.7 else \
+                    dict(temperature=0.9, top_k=rng.choice([0, 5, 50]), top_p=rng.choice([1.0, 0.9, 0.5]), seed=n_req)
+                eng.add_request(prompt[:1500], SamplingParams(max_tokens=rng.randint(1, 200), ignore_eos=True, **how))
+                n_req += 1
+        for out in eng.step():
+            if out.new_token is not None:
+                assert 0 <= out.new_token < vocab
+                tokens += 1
+    eng.block_manager.check_invariants([])
+    assert eng.block_manager.num_free_blocks == eng.block_manager.num_blocks, "pages were lost"
+    assert eng.ops.kernel_timeouts() == 0
+    assert n_req > 100 and tokens > 10 * n_req and eng.stats.num_preemptions > 0
+    assert eng.runner.num_graph_steps > 20 * max(1, eng.runner.num_eager_steps), (
+        eng.runner.num_graph_steps, eng.runner.num_eager_steps)
